@@ -1,0 +1,186 @@
+/*
+ * peregrine_b200 -- C ABI of the B200 (sm_100a) quantized-inference path.
+ *
+ * This is the boundary a host-language binding (Rust `extern "C"`, ctypes, cgo)
+ * links against.  Each entry point names the function of the reference
+ * (etam103/peregrine, paths relative to that project) whose work it takes
+ * over.  The reference's seam for a GPU backend is its `metal` cargo feature:
+ * device buffers cached inside `QuantizedTensor` (src/quant.rs:19-22,172-191),
+ * per-call upload of the activations and an unsynchronised device result
+ * (src/quant.rs:195-218), dispatch in `Tensor::matmul_quantized`
+ * (src/tensor.rs:1382-1408).  The same shape is kept here.
+ *
+ * Conventions
+ *   - Every function returns 0 (PG_OK) or a negative pg_status.  Nothing
+ *     aborts, traps or throws across the boundary; `pg_last_error()` returns a
+ *     thread-local message for the last failure on the calling thread.  The
+ *     reference panics (assert!/expect) where these return PG_ERR_INVALID.
+ *   - Pointers named d_* are device pointers on the context's GPU; all others
+ *     are host pointers.  Plain pointers and sizes only.
+ *   - Work is enqueued on the context's stream and is NOT synchronised unless
+ *     the name ends in `_host` (those copy results back and block), matching
+ *     the reference's "caller syncs" rule (tests/quant_parity.rs:102-107).
+ *   - A context belongs to one thread at a time (the reference's GPU context is
+ *     a thread-local singleton, src/metal/context.rs:2472-2510).
+ *   - There is no CPU fallback: without a usable sm_100 device pg_ctx_create fails.
+ *
+ * Matrix layouts are the reference's: activations [M,K] row-major f32;
+ * QuantizedTensor data_i8 [K,N] row-major, data_i8_t [N,K] row-major,
+ * scales [N]; outputs [M,N] row-major f32.
+ */
+#ifndef PEREGRINE_B200_H
+#define PEREGRINE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define PG_API
+#else
+#define PG_API __attribute__((visibility("default")))
+#endif
+
+typedef struct pg_ctx pg_ctx;
+typedef struct pg_qtensor pg_qtensor;
+typedef struct pg_gguf_weight pg_gguf_weight;
+
+typedef enum pg_status {
+    PG_OK = 0,
+    PG_ERR_INVALID = -1,        /* shape/argument check failed (reference: assert!/panic) */
+    PG_ERR_CUDA = -2,           /* a CUDA runtime/driver call failed */
+    PG_ERR_NOMEM = -3,          /* device or host allocation failed */
+    PG_ERR_UNSUPPORTED = -4,    /* no sm_100 device, or a shape the requested kernel cannot take */
+    PG_ERR_DEVICE_TIMEOUT = -5  /* a bounded wait inside a kernel ran out; the context stays usable */
+} pg_status;
+
+/* GGUF block formats (reference: GgmlType, src/gguf.rs:15-21, same numbering) */
+typedef enum pg_gguf_type { PG_GGUF_Q4_0 = 2, PG_GGUF_Q4_1 = 3, PG_GGUF_Q8_0 = 8 } pg_gguf_type;
+
+/* Kernel selection for pg_gemm_i8 / pg_matmul_quantized_algo. */
+typedef enum pg_gemm_algo {
+    PG_ALGO_AUTO = 0,      /* M <= 64: streaming kernel; otherwise tcgen05 */
+    PG_ALGO_NAIVE = 1,     /* one thread per output, dp4a; the on-device checker */
+    PG_ALGO_STREAM = 2,    /* bandwidth-bound decode kernel (128-bit loads + int8 MMA), M <= 64 */
+    PG_ALGO_TCGEN05 = 3    /* tcgen05.mma kind::i8, TMEM accumulators, TMA-fed */
+} pg_gemm_algo;
+
+PG_API const char *pg_last_error(void);
+PG_API int32_t pg_version(void);
+/* Number of kernels this library has launched in the calling process (for benchmarks). */
+PG_API uint64_t pg_launch_count(void);
+
+/* ---- context, replaces metal::init_gpu / GpuContext (src/metal/context.rs:45,2472-2510) ----
+ * `stream` is a cudaStream_t to enqueue on (not owned), or NULL to create one. */
+PG_API int32_t pg_ctx_create(int32_t device, void *stream, pg_ctx **out);
+PG_API int32_t pg_ctx_destroy(pg_ctx *ctx);
+/* GpuContext::sync (src/metal/context.rs:188-204) */
+PG_API int32_t pg_ctx_sync(pg_ctx *ctx);
+PG_API void *pg_ctx_stream(pg_ctx *ctx);
+/* Status word written by kernels whose waits are bounded; 0 if none gave up. Clears it. */
+PG_API int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out);
+
+/* ---- device memory, replaces GpuContext::alloc/upload and GpuBuffer::read
+ *      (src/metal/context.rs; used at src/quant.rs:176-187,207-210) ---- */
+PG_API int32_t pg_mem_alloc(pg_ctx *ctx, size_t bytes, void **d_out);
+PG_API int32_t pg_mem_free(pg_ctx *ctx, void *d_ptr);
+PG_API int32_t pg_mem_upload(pg_ctx *ctx, void *d_dst, const void *src, size_t bytes);   /* async */
+PG_API int32_t pg_mem_download(pg_ctx *ctx, void *dst, const void *d_src, size_t bytes); /* blocks */
+
+/* ---- quant::quantize_activations (src/quant.rs:79-112, scalar branch :97-109) ----
+ * x [M,K] f32 -> q [M,K] i8, scales [M] f32.  Bit-exact with the scalar branch. */
+PG_API int32_t pg_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols,
+                                       int8_t *d_q, float *d_scales);
+PG_API int32_t pg_quantize_activations_host(pg_ctx *ctx, const float *x, int64_t rows, int64_t cols,
+                                            int8_t *q, float *scales);
+
+/* ---- quant::quantize_weights (src/quant.rs:27-75) ----
+ * w [K,N] f32 -> data_i8 [K,N], data_i8_t [N,K] (either may be NULL), scales [N]. */
+PG_API int32_t pg_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols,
+                                   int8_t *d_data_i8, int8_t *d_data_i8_t, float *d_scales);
+PG_API int32_t pg_quantize_weights_host(pg_ctx *ctx, const float *w, int64_t rows, int64_t cols,
+                                        int8_t *data_i8, int8_t *data_i8_t, float *scales);
+
+/* ---- quant::dequantize (src/quant.rs:115-123) ---- */
+PG_API int32_t pg_dequantize(pg_ctx *ctx, const int8_t *d_data_i8, const float *d_scales,
+                             int64_t rows, int64_t cols, float *d_out);
+
+/* ---- QuantizedTensor::to_gpu / from_gpu (src/quant.rs:172-191) ----
+ * Uploads host data_i8_t [N,K] (required), data_i8 [K,N] (optional, may be NULL) and
+ * scales [N].  Columns [col_begin, col_end) only are kept on this GPU (pass 0, cols for
+ * the whole tensor): the column shard of one rank. */
+PG_API int32_t pg_qtensor_upload(pg_ctx *ctx, const int8_t *data_i8, const int8_t *data_i8_t,
+                                 const float *scales, int64_t rows, int64_t cols,
+                                 int64_t col_begin, int64_t col_end, pg_qtensor **out);
+/* Wraps device arrays the caller already holds (not owned, not copied). d_data_i8 may be NULL. */
+PG_API int32_t pg_qtensor_wrap(pg_ctx *ctx, const int8_t *d_data_i8, const int8_t *d_data_i8_t,
+                               const float *d_scales, int64_t rows, int64_t cols, pg_qtensor **out);
+/* Quantises f32 weights [K,N] already on the device and keeps the result on the device. */
+PG_API int32_t pg_qtensor_from_f32(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols,
+                                   int32_t keep_data_i8, pg_qtensor **out);
+PG_API int32_t pg_qtensor_download(pg_ctx *ctx, const pg_qtensor *t, int8_t *data_i8, int8_t *data_i8_t,
+                                   float *scales);
+PG_API int32_t pg_qtensor_free(pg_ctx *ctx, pg_qtensor *t);
+PG_API int64_t pg_qtensor_rows(const pg_qtensor *t);
+PG_API int64_t pg_qtensor_cols(const pg_qtensor *t);
+PG_API const int8_t *pg_qtensor_data_i8_t(const pg_qtensor *t);
+PG_API const float *pg_qtensor_scales(const pg_qtensor *t);
+
+/* ---- quant::matmul_quantized (src/quant.rs:129-169), Tensor::matmul_quantized
+ *      (src/tensor.rs:1382-1408), quant::matmul_quantized_gpu (src/quant.rs:195-218) ----
+ * y[M,N] = ((i32 sum_k q(x)[m,k] * w_t[n,k]) as f32 * a_scale[m]) * w_scale[n].
+ * d_acc (nullable) receives the i32 sums [M,N]; d_a_i8 / d_a_scales (nullable) receive the
+ * quantised activations.  Without them the context's own scratch holds the intermediates. */
+PG_API int32_t pg_matmul_quantized(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k,
+                                   const pg_qtensor *w, float *d_y);
+PG_API int32_t pg_matmul_quantized_ex(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k,
+                                      const pg_qtensor *w, float *d_y, int32_t *d_acc,
+                                      int8_t *d_a_i8, float *d_a_scales, int32_t algo);
+/* Host slices in, host result out: the exact shape of quant::matmul_quantized. Blocks. */
+PG_API int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t k,
+                                        const pg_qtensor *w, float *y);
+
+/* ---- the integer GEMM alone: simd_kernels::gemm_i8_sdot (src/simd_kernels.rs:1087-1214),
+ *      scalar form src/quant.rs:154-166 ---- */
+PG_API int32_t pg_gemm_i8(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k,
+                          const pg_qtensor *w, float *d_y, int32_t *d_acc, int32_t algo);
+
+/* ---- gguf::dequant_q8_0 / dequant_q4_0 / dequant_q4_1 / f16_to_f32
+ *      (src/gguf.rs:286-302, 307-326, 331-351, 354-382) ----
+ * raw block stream -> f32.  num_elements % 32 != 0 or a short buffer is PG_ERR_INVALID. */
+PG_API int32_t pg_dequant_blocks(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, size_t raw_len,
+                                 int64_t num_elements, float *d_out);
+PG_API int32_t pg_dequant_blocks_host(pg_ctx *ctx, int32_t type, const uint8_t *raw, size_t raw_len,
+                                      int64_t num_elements, float *out);
+PG_API int32_t pg_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float *d_out);
+
+/* ---- the Llama linear on a GGUF weight: GgufFile::load_tensor_f32 (src/gguf.rs:485-517) +
+ *      load_transposed_weight (src/models/llama/model.rs:243-257) + Tensor::matmul
+ *      (src/tensor.rs:1342-1354), done without materialising the f32 weight ----
+ * raw: [N rows][K/32 blocks] in GGUF [out,in] order; rows [row_begin,row_end) are kept
+ * (0, n for all).  y[M,N] = x[M,K] . dequant(W)[N,K]^T in f32. */
+PG_API int32_t pg_gguf_upload(pg_ctx *ctx, int32_t type, const uint8_t *raw, size_t raw_len,
+                              int64_t n, int64_t k, int64_t row_begin, int64_t row_end,
+                              pg_gguf_weight **out);
+PG_API int32_t pg_gguf_free(pg_ctx *ctx, pg_gguf_weight *w);
+PG_API int64_t pg_gguf_rows(const pg_gguf_weight *w);
+PG_API int64_t pg_gguf_cols(const pg_gguf_weight *w);
+PG_API int32_t pg_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
+PG_API int32_t pg_matmul_gguf_host(pg_ctx *ctx, const float *x, int64_t m, const pg_gguf_weight *w, float *y);
+/* gguf::load_tensor_q8_as_quantized (src/gguf.rs:386-401): Q8_0 blocks [rows,cols] ->
+ * dequantise -> quantize_weights(rows, cols), all on the device. */
+PG_API int32_t pg_qtensor_from_q8_0(pg_ctx *ctx, const uint8_t *raw, size_t raw_len, int64_t rows, int64_t cols,
+                                    pg_qtensor **out);
+
+/* ---- Tensor::matmul, naive branch (src/tensor.rs:1342-1354): [M,K] x [K,N] f32,
+ *      ascending-p accumulation with separately rounded multiply and add ---- */
+PG_API int32_t pg_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n,
+                             float *d_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PEREGRINE_B200_H */

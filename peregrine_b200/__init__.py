@@ -1,0 +1,15 @@
+"""peregrine_b200: the quantized-inference path of etam103/peregrine on NVIDIA B200 (sm_100a).
+
+    quant     mirror of peregrine::quant  (src/quant.rs)
+    gguf      mirror of the block codecs of peregrine::gguf  (src/gguf.rs:284-401)
+    runtime   GpuContext / GpuBuffer / init_gpu / with_gpu  (the reference's `metal` seam)
+    build     compiles libperegrine_b200.so with nvcc
+
+Everything computes in hand-written CUDA behind the C ABI of include/peregrine_b200.h.
+"""
+from . import _lib
+from ._lib import InvalidArgument, PeregrineError
+from .runtime import GpuBuffer, GpuContext, current_gpu, init_gpu, with_gpu
+from . import quant, gguf
+
+__all__ = ["quant", "gguf", "GpuContext", "GpuBuffer", "init_gpu", "with_gpu", "current_gpu", "PeregrineError", "InvalidArgument"]

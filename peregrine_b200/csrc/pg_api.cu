@@ -1,0 +1,693 @@
+// The extern "C" surface declared in include/peregrine_b200.h: argument checks (where the
+// reference asserts), object lifetimes, host<->device staging for the *_host forms and the
+// choice of kernel.  No arithmetic happens here.
+#include <stdarg.h>
+#include <string.h>
+
+#include <new>
+
+#include "pg_internal.cuh"
+
+std::atomic<uint64_t> g_pg_launches{0};
+static thread_local char g_err[512] = "";
+
+void pg_set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->scratch_bytes) return PG_OK;
+    // Work already enqueued may still use the old block: drain before replacing it.
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->scratch) PG_CUDA(cudaFree(ctx->scratch));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    want = (want + 255) & ~(size_t)255;
+    PG_CUDA(cudaMalloc(&ctx->scratch, want));
+    ctx->scratch_bytes = want;
+    return PG_OK;
+}
+
+int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->h_pinned_bytes) return PG_OK;
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->h_pinned) PG_CUDA(cudaFreeHost(ctx->h_pinned));
+    ctx->h_pinned = nullptr;
+    ctx->h_pinned_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    PG_CUDA(cudaMallocHost(&ctx->h_pinned, want));
+    ctx->h_pinned_bytes = want;
+    return PG_OK;
+}
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+    }
+    ~DeviceGuard()
+    {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+#define PG_ENTER(ctx)                                                   \
+    PG_REQUIRE((ctx) != nullptr, "null context");                       \
+    DeviceGuard _guard((ctx)->device);                                  \
+    if (!_guard.ok) PG_FAIL(PG_ERR_CUDA, "cudaSetDevice(%d) failed", (ctx)->device)
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+}  // namespace
+
+extern "C" {
+
+const char *pg_last_error(void) { return g_err; }
+int32_t pg_version(void) { return 100; }
+uint64_t pg_launch_count(void) { return g_pg_launches.load(); }
+
+int32_t pg_ctx_create(int32_t device, void *stream, pg_ctx **out)
+{
+    PG_REQUIRE(out != nullptr, "pg_ctx_create: out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        PG_FAIL(PG_ERR_UNSUPPORTED, "no CUDA device is visible (%s); this library has no CPU path",
+                e == cudaSuccess ? "device count 0" : cudaGetErrorString(e));
+    PG_REQUIRE(device >= 0 && device < count, "pg_ctx_create: device %d out of range (0..%d)", device, count - 1);
+    cudaDeviceProp prop;
+    PG_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        PG_FAIL(PG_ERR_UNSUPPORTED, "device %d is sm_%d%d; the kernels are built for sm_100a only", device, prop.major, prop.minor);
+    DeviceGuard guard(device);
+    if (!guard.ok) PG_FAIL(PG_ERR_CUDA, "cudaSetDevice(%d) failed", device);
+    pg_ctx *ctx = new (std::nothrow) pg_ctx();
+    if (!ctx) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = (cudaStream_t)stream;
+    } else {
+        cudaError_t se = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+        if (se != cudaSuccess) {
+            delete ctx;
+            PG_FAIL(PG_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(se));
+        }
+        ctx->owns_stream = true;
+    }
+    cudaError_t me = cudaMalloc(&ctx->d_status, sizeof(int32_t));
+    if (me == cudaSuccess) me = cudaMemset(ctx->d_status, 0, sizeof(int32_t));
+    if (me != cudaSuccess) {
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        PG_FAIL(PG_ERR_CUDA, "status word allocation failed: %s", cudaGetErrorString(me));
+    }
+    *out = ctx;
+    return PG_OK;
+}
+
+int32_t pg_ctx_destroy(pg_ctx *ctx)
+{
+    if (!ctx) return PG_OK;
+    DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return PG_OK;
+}
+
+int32_t pg_ctx_sync(pg_ctx *ctx)
+{
+    PG_ENTER(ctx);
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return PG_OK;
+}
+
+void *pg_ctx_stream(pg_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
+int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out)
+{
+    PG_ENTER(ctx);
+    int32_t v = 0;
+    PG_CUDA(cudaMemcpyAsync(&v, ctx->d_status, sizeof(v), cudaMemcpyDeviceToHost, ctx->stream));
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (v != 0) PG_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(v), ctx->stream));
+    if (status_out) *status_out = v;
+    return PG_OK;
+}
+
+int32_t pg_mem_alloc(pg_ctx *ctx, size_t bytes, void **d_out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_out != nullptr, "pg_mem_alloc: out is null");
+    *d_out = nullptr;
+    PG_CUDA(cudaMalloc(d_out, bytes ? bytes : 1));
+    return PG_OK;
+}
+
+int32_t pg_mem_free(pg_ctx *ctx, void *d_ptr)
+{
+    PG_ENTER(ctx);
+    if (d_ptr) {
+        PG_CUDA(cudaStreamSynchronize(ctx->stream));
+        PG_CUDA(cudaFree(d_ptr));
+    }
+    return PG_OK;
+}
+
+int32_t pg_mem_upload(pg_ctx *ctx, void *d_dst, const void *src, size_t bytes)
+{
+    PG_ENTER(ctx);
+    if (bytes == 0) return PG_OK;
+    PG_REQUIRE(d_dst && src, "pg_mem_upload: null pointer");
+    PG_CUDA(cudaMemcpyAsync(d_dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return PG_OK;
+}
+
+int32_t pg_mem_download(pg_ctx *ctx, void *dst, const void *d_src, size_t bytes)
+{
+    PG_ENTER(ctx);
+    if (bytes) {
+        PG_REQUIRE(dst && d_src, "pg_mem_download: null pointer");
+        PG_CUDA(cudaMemcpyAsync(dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return PG_OK;
+}
+
+// ------------------------------------------------------------ quantisers ----
+int32_t pg_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(rows >= 0 && cols >= 0, "quantize_activations: negative shape");
+    PG_REQUIRE(rows == 0 || (d_scales && (cols == 0 || (d_x && d_q))), "quantize_activations: null pointer");
+    return pgk_quantize_activations(ctx, d_x, rows, cols, d_q, d_scales);
+}
+
+int32_t pg_quantize_activations_host(pg_ctx *ctx, const float *x, int64_t rows, int64_t cols, int8_t *q, float *scales)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(rows >= 0 && cols >= 0, "quantize_activations: negative shape");
+    if (rows == 0) return PG_OK;
+    PG_REQUIRE(scales && (cols == 0 || (x && q)), "quantize_activations: null pointer");
+    const size_t nx = align256((size_t)rows * cols * 4), nq = align256((size_t)rows * cols), ns = align256((size_t)rows * 4);
+    int32_t rc = pg_scratch_reserve(ctx, nx + nq + ns);
+    if (rc) return rc;
+    char *base = (char *)ctx->scratch;
+    float *d_x = (float *)base;
+    int8_t *d_q = (int8_t *)(base + nx);
+    float *d_s = (float *)(base + nx + nq);
+    if (cols) PG_CUDA(cudaMemcpyAsync(d_x, x, (size_t)rows * cols * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = pgk_quantize_activations(ctx, d_x, rows, cols, d_q, d_s);
+    if (rc) return rc;
+    if (cols) PG_CUDA(cudaMemcpyAsync(q, d_q, (size_t)rows * cols, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_CUDA(cudaMemcpyAsync(scales, d_s, (size_t)rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return PG_OK;
+}
+
+int32_t pg_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int8_t *d_data_i8, int8_t *d_data_i8_t,
+                            float *d_scales)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(rows >= 0 && cols >= 0, "quantize_weights: negative shape");
+    PG_REQUIRE(cols == 0 || d_scales, "quantize_weights: scales is null");
+    PG_REQUIRE(rows * cols == 0 || d_w, "quantize_weights: weights pointer is null");
+    return pgk_quantize_weights(ctx, d_w, rows, cols, d_data_i8, d_data_i8_t, d_scales);
+}
+
+int32_t pg_quantize_weights_host(pg_ctx *ctx, const float *w, int64_t rows, int64_t cols, int8_t *data_i8, int8_t *data_i8_t,
+                                 float *scales)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(rows >= 0 && cols >= 0, "quantize_weights: negative shape");
+    if (cols == 0) return PG_OK;
+    PG_REQUIRE(scales && (rows == 0 || w), "quantize_weights: null pointer");
+    const size_t total = (size_t)rows * cols;
+    void *d_w = nullptr, *d_q = nullptr, *d_qt = nullptr, *d_s = nullptr;
+    int32_t rc = PG_OK;
+    auto cleanup = [&]() {
+        cudaFree(d_w);
+        cudaFree(d_q);
+        cudaFree(d_qt);
+        cudaFree(d_s);
+    };
+#define PG_TRY(expr)                                                                  \
+    do {                                                                              \
+        cudaError_t _e = (expr);                                                      \
+        if (_e != cudaSuccess) {                                                      \
+            pg_set_error("%s failed: %s", #expr, cudaGetErrorString(_e));             \
+            cleanup();                                                                \
+            return _e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA;      \
+        }                                                                             \
+    } while (0)
+    PG_TRY(cudaMalloc(&d_w, total * 4 + 16));
+    PG_TRY(cudaMalloc(&d_q, total + 16));
+    PG_TRY(cudaMalloc(&d_qt, total + 16));
+    PG_TRY(cudaMalloc(&d_s, (size_t)cols * 4));
+    if (total) PG_TRY(cudaMemcpyAsync(d_w, w, total * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = pgk_quantize_weights(ctx, (const float *)d_w, rows, cols, (int8_t *)d_q, (int8_t *)d_qt, (float *)d_s);
+    if (rc) {
+        cleanup();
+        return rc;
+    }
+    if (total && data_i8) PG_TRY(cudaMemcpyAsync(data_i8, d_q, total, cudaMemcpyDeviceToHost, ctx->stream));
+    if (total && data_i8_t) PG_TRY(cudaMemcpyAsync(data_i8_t, d_qt, total, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_TRY(cudaMemcpyAsync(scales, d_s, (size_t)cols * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_TRY(cudaStreamSynchronize(ctx->stream));
+    cleanup();
+    return PG_OK;
+}
+
+int32_t pg_dequantize(pg_ctx *ctx, const int8_t *d_data_i8, const float *d_scales, int64_t rows, int64_t cols, float *d_out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(rows >= 0 && cols >= 0, "dequantize: negative shape");
+    PG_REQUIRE(rows * cols == 0 || (d_data_i8 && d_scales && d_out), "dequantize: null pointer");
+    return pgk_dequantize(ctx, d_data_i8, d_scales, rows, cols, d_out);
+}
+
+// ---------------------------------------------------------------- qtensor ----
+int32_t pg_qtensor_upload(pg_ctx *ctx, const int8_t *data_i8, const int8_t *data_i8_t, const float *scales, int64_t rows,
+                          int64_t cols, int64_t col_begin, int64_t col_end, pg_qtensor **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "qtensor_upload: out is null");
+    *out = nullptr;
+    PG_REQUIRE(rows >= 0 && cols >= 0, "qtensor_upload: negative shape");
+    PG_REQUIRE(0 <= col_begin && col_begin <= col_end && col_end <= cols, "qtensor_upload: column range [%lld,%lld) outside [0,%lld)",
+               (long long)col_begin, (long long)col_end, (long long)cols);
+    PG_REQUIRE(data_i8_t && scales, "qtensor_upload: data_i8_t and scales are required");
+    const int64_t nc = col_end - col_begin;
+    pg_qtensor *t = new (std::nothrow) pg_qtensor();
+    if (!t) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    t->rows = rows;
+    t->cols = nc;
+    t->owned = true;
+    void *d_t = nullptr, *d_s = nullptr, *d_q = nullptr;
+    auto fail = [&](cudaError_t e, const char *what) {
+        pg_set_error("qtensor_upload: %s failed: %s", what, cudaGetErrorString(e));
+        cudaFree(d_t);
+        cudaFree(d_s);
+        cudaFree(d_q);
+        delete t;
+        return e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA;
+    };
+    cudaError_t e;
+    const size_t tb = (size_t)nc * rows;
+    // 1 KiB of slack after the weights lets tiled loads of the last rows stay inside the allocation
+    if ((e = cudaMalloc(&d_t, tb + 1024)) != cudaSuccess) return fail(e, "cudaMalloc");
+    if ((e = cudaMalloc(&d_s, (size_t)(nc ? nc : 1) * 4)) != cudaSuccess) return fail(e, "cudaMalloc");
+    if (tb && (e = cudaMemcpyAsync(d_t, data_i8_t + col_begin * rows, tb, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess)
+        return fail(e, "upload of data_i8_t");
+    if (nc && (e = cudaMemcpyAsync(d_s, scales + col_begin, (size_t)nc * 4, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess)
+        return fail(e, "upload of scales");
+    if (data_i8) {
+        if ((e = cudaMalloc(&d_q, tb + 16)) != cudaSuccess) return fail(e, "cudaMalloc");
+        if (tb && (e = cudaMemcpy2DAsync(d_q, (size_t)nc, data_i8 + col_begin, (size_t)cols, (size_t)nc, (size_t)rows,
+                                         cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess)
+            return fail(e, "upload of data_i8");
+    }
+    if ((e = cudaStreamSynchronize(ctx->stream)) != cudaSuccess) return fail(e, "sync");
+    t->d_data_i8_t = (const int8_t *)d_t;
+    t->d_scales = (const float *)d_s;
+    t->d_data_i8 = (const int8_t *)d_q;
+    *out = t;
+    return PG_OK;
+}
+
+int32_t pg_qtensor_wrap(pg_ctx *ctx, const int8_t *d_data_i8, const int8_t *d_data_i8_t, const float *d_scales, int64_t rows,
+                        int64_t cols, pg_qtensor **out)
+{
+    PG_REQUIRE(ctx && out, "qtensor_wrap: null argument");
+    *out = nullptr;
+    PG_REQUIRE(rows >= 0 && cols >= 0, "qtensor_wrap: negative shape");
+    PG_REQUIRE(rows * cols == 0 || (d_data_i8_t && d_scales), "qtensor_wrap: data_i8_t and scales are required");
+    pg_qtensor *t = new (std::nothrow) pg_qtensor();
+    if (!t) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    t->d_data_i8 = d_data_i8;
+    t->d_data_i8_t = d_data_i8_t;
+    t->d_scales = d_scales;
+    t->rows = rows;
+    t->cols = cols;
+    t->owned = false;
+    *out = t;
+    return PG_OK;
+}
+
+int32_t pg_qtensor_from_f32(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int32_t keep_data_i8, pg_qtensor **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "qtensor_from_f32: out is null");
+    *out = nullptr;
+    PG_REQUIRE(rows >= 0 && cols >= 0, "qtensor_from_f32: negative shape");
+    PG_REQUIRE(rows * cols == 0 || d_w, "qtensor_from_f32: weights pointer is null");
+    pg_qtensor *t = new (std::nothrow) pg_qtensor();
+    if (!t) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    void *d_t = nullptr, *d_s = nullptr, *d_q = nullptr;
+    const size_t tb = (size_t)rows * cols;
+    cudaError_t e = cudaMalloc(&d_t, tb + 1024);
+    if (e == cudaSuccess) e = cudaMalloc(&d_s, (size_t)(cols ? cols : 1) * 4);
+    if (e == cudaSuccess && keep_data_i8) e = cudaMalloc(&d_q, tb + 16);
+    int32_t rc = PG_OK;
+    if (e != cudaSuccess) {
+        pg_set_error("qtensor_from_f32: cudaMalloc failed: %s", cudaGetErrorString(e));
+        rc = PG_ERR_NOMEM;
+    } else {
+        rc = pgk_quantize_weights(ctx, d_w, rows, cols, (int8_t *)d_q, (int8_t *)d_t, (float *)d_s);
+    }
+    if (rc != PG_OK) {
+        cudaFree(d_t);
+        cudaFree(d_s);
+        cudaFree(d_q);
+        delete t;
+        return rc;
+    }
+    t->d_data_i8 = (const int8_t *)d_q;
+    t->d_data_i8_t = (const int8_t *)d_t;
+    t->d_scales = (const float *)d_s;
+    t->rows = rows;
+    t->cols = cols;
+    t->owned = true;
+    *out = t;
+    return PG_OK;
+}
+
+int32_t pg_qtensor_download(pg_ctx *ctx, const pg_qtensor *t, int8_t *data_i8, int8_t *data_i8_t, float *scales)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(t != nullptr, "qtensor_download: tensor is null");
+    const size_t tb = (size_t)t->rows * t->cols;
+    if (data_i8) {
+        PG_REQUIRE(t->d_data_i8 != nullptr, "qtensor_download: data_i8 is not on the GPU");
+        if (tb) PG_CUDA(cudaMemcpyAsync(data_i8, t->d_data_i8, tb, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    if (data_i8_t && tb) PG_CUDA(cudaMemcpyAsync(data_i8_t, t->d_data_i8_t, tb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (scales && t->cols) PG_CUDA(cudaMemcpyAsync(scales, t->d_scales, (size_t)t->cols * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return PG_OK;
+}
+
+int32_t pg_qtensor_free(pg_ctx *ctx, pg_qtensor *t)
+{
+    if (!t) return PG_OK;
+    PG_ENTER(ctx);
+    if (t->owned) {
+        PG_CUDA(cudaStreamSynchronize(ctx->stream));
+        cudaFree((void *)t->d_data_i8);
+        cudaFree((void *)t->d_data_i8_t);
+        cudaFree((void *)t->d_scales);
+    }
+    delete t;
+    return PG_OK;
+}
+
+int64_t pg_qtensor_rows(const pg_qtensor *t) { return t ? t->rows : 0; }
+int64_t pg_qtensor_cols(const pg_qtensor *t) { return t ? t->cols : 0; }
+const int8_t *pg_qtensor_data_i8_t(const pg_qtensor *t) { return t ? t->d_data_i8_t : nullptr; }
+const float *pg_qtensor_scales(const pg_qtensor *t) { return t ? t->d_scales : nullptr; }
+
+// ---------------------------------------------------------- integer GEMM ----
+static int32_t gemm_dispatch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const pg_qtensor *w,
+                             float *d_y, int32_t *d_acc, int32_t algo)
+{
+    const int64_t n = w->cols;
+    if (m == 0 || n == 0) return PG_OK;
+    if (k == 0) {
+        // empty sums: acc = 0, y = 0 * a_scale * w_scale = +0.0 (or NaN for a non-finite scale);
+        // the naive kernel evaluates exactly that
+        return pgk_gemm_i8_naive(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
+    }
+    const bool aligned = (((uintptr_t)d_a | (uintptr_t)w->d_data_i8_t) & 15) == 0;
+    switch (algo) {
+        case PG_ALGO_NAIVE:
+            return pgk_gemm_i8_naive(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
+        case PG_ALGO_STREAM:
+            return pgk_gemm_i8_stream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
+        case PG_ALGO_TCGEN05:
+            return pgk_gemm_i8_tcgen05(ctx, d_a, d_as, m, k, const_cast<pg_qtensor *>(w), d_y, d_acc);
+        case PG_ALGO_AUTO:
+            if (aligned && pgk_gemm_i8_stream_supports(m, k, n))
+                return pgk_gemm_i8_stream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
+            if (aligned && pgk_gemm_i8_tcgen05_supports(m, k, n))
+                return pgk_gemm_i8_tcgen05(ctx, d_a, d_as, m, k, const_cast<pg_qtensor *>(w), d_y, d_acc);
+            // shapes neither fast kernel takes (K not a multiple of 16, odd alignment)
+            return pgk_gemm_i8_naive(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
+    }
+    PG_FAIL(PG_ERR_INVALID, "unknown algo %d", algo);
+}
+
+int32_t pg_gemm_i8(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k, const pg_qtensor *w,
+                   float *d_y, int32_t *d_acc, int32_t algo)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(w != nullptr, "gemm_i8: weights are null");
+    PG_REQUIRE(m >= 0 && k >= 0, "gemm_i8: negative shape");
+    PG_REQUIRE(w->rows == k, "gemm_i8: w.rows (%lld) != k (%lld)", (long long)w->rows, (long long)k);
+    PG_REQUIRE(m * w->cols == 0 || ((d_y == nullptr || d_a_scales) && (d_y || d_acc)), "gemm_i8: null output or scales");
+    PG_REQUIRE(m * k == 0 || d_a_i8, "gemm_i8: activations are null");
+    return gemm_dispatch(ctx, d_a_i8, d_a_scales, m, k, w, d_y, d_acc, algo);
+}
+
+int32_t pg_matmul_quantized_ex(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k, const pg_qtensor *w, float *d_y,
+                               int32_t *d_acc, int8_t *d_a_i8, float *d_a_scales, int32_t algo)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(w != nullptr, "matmul_quantized: weights not on GPU");
+    PG_REQUIRE(m >= 0 && k >= 0, "matmul_quantized: negative shape");
+    PG_REQUIRE(w->rows == k, "matmul_quantized: w.rows (%lld) != k (%lld)", (long long)w->rows, (long long)k);
+    PG_REQUIRE(m * k == 0 || d_x, "matmul_quantized: activations are null");
+    PG_REQUIRE(m * w->cols == 0 || d_y || d_acc, "matmul_quantized: no output");
+    if (m == 0) return PG_OK;
+    int8_t *a_i8 = d_a_i8;
+    float *a_s = d_a_scales;
+    if (!a_i8 || !a_s) {
+        const size_t nq = align256((size_t)m * k + 16), ns = align256((size_t)m * 4);
+        int32_t rc = pg_scratch_reserve(ctx, nq + ns);
+        if (rc) return rc;
+        if (!a_i8) a_i8 = (int8_t *)ctx->scratch;
+        if (!a_s) a_s = (float *)((char *)ctx->scratch + nq);
+    }
+    int32_t rc = pgk_quantize_activations(ctx, d_x, m, k, a_i8, a_s);
+    if (rc) return rc;
+    return gemm_dispatch(ctx, a_i8, a_s, m, k, w, d_y, d_acc, algo);
+}
+
+int32_t pg_matmul_quantized(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k, const pg_qtensor *w, float *d_y)
+{
+    return pg_matmul_quantized_ex(ctx, d_x, m, k, w, d_y, nullptr, nullptr, nullptr, PG_ALGO_AUTO);
+}
+
+int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t k, const pg_qtensor *w, float *y)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(w != nullptr, "matmul_quantized: weights not on GPU");
+    PG_REQUIRE(m >= 0 && k >= 0, "matmul_quantized: negative shape");
+    PG_REQUIRE(w->rows == k, "matmul_quantized: w.rows (%lld) != k (%lld)", (long long)w->rows, (long long)k);
+    const int64_t n = w->cols;
+    if (m * n == 0) return PG_OK;
+    PG_REQUIRE((m * k == 0 || x) && y, "matmul_quantized: null pointer");
+    const size_t nx = align256((size_t)m * k * 4 + 16), ny = align256((size_t)m * n * 4), nq = align256((size_t)m * k + 16),
+                 ns = align256((size_t)m * 4);
+    int32_t rc = pg_scratch_reserve(ctx, nx + ny + nq + ns);
+    if (rc) return rc;
+    char *base = (char *)ctx->scratch;
+    float *d_x = (float *)base;
+    float *d_y = (float *)(base + nx);
+    int8_t *d_q = (int8_t *)(base + nx + ny);
+    float *d_s = (float *)(base + nx + ny + nq);
+    if (m * k) PG_CUDA(cudaMemcpyAsync(d_x, x, (size_t)m * k * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = pgk_quantize_activations(ctx, d_x, m, k, d_q, d_s);
+    if (rc) return rc;
+    rc = gemm_dispatch(ctx, d_q, d_s, m, k, w, d_y, nullptr, PG_ALGO_AUTO);
+    if (rc) return rc;
+    PG_CUDA(cudaMemcpyAsync(y, d_y, (size_t)m * n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return PG_OK;
+}
+
+// ------------------------------------------------------------------- GGUF ----
+static int block_size_of(int32_t type) { return type == PG_GGUF_Q8_0 ? 34 : type == PG_GGUF_Q4_0 ? 18 : type == PG_GGUF_Q4_1 ? 20 : 0; }
+
+int32_t pg_dequant_blocks(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, size_t raw_len, int64_t num_elements, float *d_out)
+{
+    PG_ENTER(ctx);
+    const int bs = block_size_of(type);
+    PG_REQUIRE(bs != 0, "dequant: unknown block type %d", type);
+    PG_REQUIRE(num_elements >= 0 && num_elements % 32 == 0, "dequant: num_elements %% 32 != 0");
+    const int64_t nb = num_elements / 32;
+    PG_REQUIRE(raw_len >= (size_t)nb * bs, "dequant: data holds %zu bytes, %lld blocks need %lld", raw_len, (long long)nb,
+               (long long)nb * bs);
+    PG_REQUIRE(nb == 0 || (d_raw && d_out), "dequant: null pointer");
+    return pgk_dequant_blocks(ctx, type, d_raw, nb, d_out);
+}
+
+int32_t pg_dequant_blocks_host(pg_ctx *ctx, int32_t type, const uint8_t *raw, size_t raw_len, int64_t num_elements, float *out)
+{
+    PG_ENTER(ctx);
+    const int bs = block_size_of(type);
+    PG_REQUIRE(bs != 0, "dequant: unknown block type %d", type);
+    PG_REQUIRE(num_elements >= 0 && num_elements % 32 == 0, "dequant: num_elements %% 32 != 0");
+    const int64_t nb = num_elements / 32;
+    PG_REQUIRE(raw_len >= (size_t)nb * bs, "dequant: data holds %zu bytes, %lld blocks need %lld", raw_len, (long long)nb,
+               (long long)nb * bs);
+    if (nb == 0) return PG_OK;
+    PG_REQUIRE(raw && out, "dequant: null pointer");
+    void *d_raw = nullptr, *d_out = nullptr;
+    cudaError_t e = cudaMalloc(&d_raw, (size_t)nb * bs);
+    if (e == cudaSuccess) e = cudaMalloc(&d_out, (size_t)num_elements * 4);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_raw, raw, (size_t)nb * bs, cudaMemcpyHostToDevice, ctx->stream);
+    int32_t rc = PG_OK;
+    if (e == cudaSuccess) rc = pgk_dequant_blocks(ctx, type, (const uint8_t *)d_raw, nb, (float *)d_out);
+    if (e == cudaSuccess && rc == PG_OK) e = cudaMemcpyAsync(out, d_out, (size_t)num_elements * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d_raw);
+    cudaFree(d_out);
+    if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "dequant: %s", cudaGetErrorString(e));
+    return rc;
+}
+
+int32_t pg_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float *d_out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(count >= 0 && (count == 0 || (d_bits && d_out)), "f16_to_f32: bad arguments");
+    return pgk_f16_to_f32(ctx, d_bits, count, d_out);
+}
+
+int32_t pg_gguf_upload(pg_ctx *ctx, int32_t type, const uint8_t *raw, size_t raw_len, int64_t n, int64_t k, int64_t row_begin,
+                       int64_t row_end, pg_gguf_weight **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "gguf_upload: out is null");
+    *out = nullptr;
+    const int bs = block_size_of(type);
+    PG_REQUIRE(bs != 0, "gguf_upload: unknown block type %d", type);
+    PG_REQUIRE(n >= 0 && k >= 0 && k % 32 == 0, "gguf_upload: k (%lld) must be a multiple of 32", (long long)k);
+    PG_REQUIRE(0 <= row_begin && row_begin <= row_end && row_end <= n, "gguf_upload: row range outside the tensor");
+    const int64_t nblk = k / 32;
+    PG_REQUIRE(raw_len >= (size_t)n * nblk * bs, "gguf_upload: data holds %zu bytes, need %lld", raw_len, (long long)(n * nblk * bs));
+    const int64_t nr = row_end - row_begin;
+    PG_REQUIRE(nr * nblk == 0 || raw, "gguf_upload: raw is null");
+    pg_gguf_weight *w = new (std::nothrow) pg_gguf_weight();
+    if (!w) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    w->type = type;
+    w->n = nr;
+    w->k = k;
+    const size_t blocks = (size_t)nr * nblk;
+    const size_t qbytes = blocks * (type == PG_GGUF_Q8_0 ? 32 : 16);
+    void *d_raw = nullptr;
+    cudaError_t e = cudaMalloc((void **)&w->d_qs, qbytes + 64);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&w->d_d, blocks * 2 + 64);
+    if (e == cudaSuccess && type == PG_GGUF_Q4_1) e = cudaMalloc((void **)&w->d_m, blocks * 2 + 64);
+    if (e == cudaSuccess && blocks) e = cudaMalloc(&d_raw, blocks * bs);
+    if (e == cudaSuccess && blocks)
+        e = cudaMemcpyAsync(d_raw, raw + (size_t)row_begin * nblk * bs, blocks * bs, cudaMemcpyHostToDevice, ctx->stream);
+    int32_t rc = PG_OK;
+    if (e == cudaSuccess) rc = pgk_gguf_repack(ctx, type, (const uint8_t *)d_raw, nr, k, w);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d_raw);
+    if (e != cudaSuccess || rc != PG_OK) {
+        if (e != cudaSuccess) pg_set_error("gguf_upload: %s", cudaGetErrorString(e));
+        cudaFree(w->d_qs);
+        cudaFree(w->d_d);
+        cudaFree(w->d_m);
+        delete w;
+        return e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : (e != cudaSuccess ? PG_ERR_CUDA : rc);
+    }
+    *out = w;
+    return PG_OK;
+}
+
+int32_t pg_gguf_free(pg_ctx *ctx, pg_gguf_weight *w)
+{
+    if (!w) return PG_OK;
+    PG_ENTER(ctx);
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    cudaFree(w->d_qs);
+    cudaFree(w->d_d);
+    cudaFree(w->d_m);
+    delete w;
+    return PG_OK;
+}
+
+int64_t pg_gguf_rows(const pg_gguf_weight *w) { return w ? w->n : 0; }
+int64_t pg_gguf_cols(const pg_gguf_weight *w) { return w ? w->k : 0; }
+
+int32_t pg_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(w != nullptr, "matmul_gguf: weight is null");
+    PG_REQUIRE(m >= 0, "matmul_gguf: negative m");
+    PG_REQUIRE(m * w->n == 0 || (d_y && (w->k == 0 || d_x)), "matmul_gguf: null pointer");
+    return pgk_matmul_gguf(ctx, d_x, m, w, d_y);
+}
+
+int32_t pg_matmul_gguf_host(pg_ctx *ctx, const float *x, int64_t m, const pg_gguf_weight *w, float *y)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(w != nullptr, "matmul_gguf: weight is null");
+    PG_REQUIRE(m >= 0, "matmul_gguf: negative m");
+    if (m * w->n == 0) return PG_OK;
+    PG_REQUIRE(y && (w->k == 0 || x), "matmul_gguf: null pointer");
+    const size_t nx = align256((size_t)m * w->k * 4 + 16), ny = align256((size_t)m * w->n * 4);
+    int32_t rc = pg_scratch_reserve(ctx, nx + ny);
+    if (rc) return rc;
+    float *d_x = (float *)ctx->scratch;
+    float *d_y = (float *)((char *)ctx->scratch + nx);
+    if (m * w->k) PG_CUDA(cudaMemcpyAsync(d_x, x, (size_t)m * w->k * 4, cudaMemcpyHostToDevice, ctx->stream));
+    rc = pgk_matmul_gguf(ctx, d_x, m, w, d_y);
+    if (rc) return rc;
+    PG_CUDA(cudaMemcpyAsync(y, d_y, (size_t)m * w->n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return PG_OK;
+}
+
+int32_t pg_qtensor_from_q8_0(pg_ctx *ctx, const uint8_t *raw, size_t raw_len, int64_t rows, int64_t cols, pg_qtensor **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "qtensor_from_q8_0: out is null");
+    *out = nullptr;
+    PG_REQUIRE(rows >= 0 && cols >= 0 && cols % 32 == 0, "qtensor_from_q8_0: cols %% 32 != 0");
+    const int64_t nb = rows * cols / 32;
+    PG_REQUIRE(raw_len >= (size_t)nb * 34, "qtensor_from_q8_0: data too short");
+    PG_REQUIRE(nb == 0 || raw, "qtensor_from_q8_0: raw is null");
+    void *d_raw = nullptr, *d_f = nullptr;
+    cudaError_t e = cudaMalloc(&d_raw, (size_t)nb * 34 + 16);
+    if (e == cudaSuccess) e = cudaMalloc(&d_f, (size_t)nb * 32 * 4 + 16);
+    if (e == cudaSuccess && nb) e = cudaMemcpyAsync(d_raw, raw, (size_t)nb * 34, cudaMemcpyHostToDevice, ctx->stream);
+    int32_t rc = PG_OK;
+    if (e == cudaSuccess) rc = pgk_dequant_blocks(ctx, PG_GGUF_Q8_0, (const uint8_t *)d_raw, nb, (float *)d_f);
+    if (e == cudaSuccess && rc == PG_OK) rc = pg_qtensor_from_f32(ctx, (const float *)d_f, rows, cols, 1, out);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d_raw);
+    cudaFree(d_f);
+    if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "qtensor_from_q8_0: %s", cudaGetErrorString(e));
+    return rc;
+}
+
+int32_t pg_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n, float *d_out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(m >= 0 && k >= 0 && n >= 0, "matmul_f32: negative shape");
+    PG_REQUIRE(m * n == 0 || (d_out && (k == 0 || (d_a && d_b))), "matmul_f32: null pointer");
+    return pgk_matmul_f32(ctx, d_a, d_b, m, k, n, d_out);
+}
+
+}  // extern "C"

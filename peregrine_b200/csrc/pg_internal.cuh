@@ -1,0 +1,115 @@
+// Internal declarations shared by the translation units of libperegrine_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <atomic>
+
+#include "peregrine_b200.h"
+
+// ---------------------------------------------------------------- errors ----
+void pg_set_error(const char *fmt, ...);
+extern std::atomic<uint64_t> g_pg_launches;
+
+#define PG_FAIL(code, ...)          \
+    do {                            \
+        pg_set_error(__VA_ARGS__);  \
+        return (code);              \
+    } while (0)
+
+#define PG_REQUIRE(cond, ...)                          \
+    do {                                               \
+        if (!(cond)) PG_FAIL(PG_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+#define PG_CUDA(expr)                                                                         \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess) {                                                              \
+            pg_set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+            return _e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA;              \
+        }                                                                                     \
+    } while (0)
+
+// Call after every kernel launch: counts it and turns a launch error into a status.
+#define PG_LAUNCHED()                       \
+    do {                                    \
+        g_pg_launches.fetch_add(1);         \
+        PG_CUDA(cudaGetLastError());        \
+    } while (0)
+
+// --------------------------------------------------------------- objects ----
+struct pg_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    // scratch for intermediates (quantised activations, split-K partial sums); grows on demand
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    int32_t *d_status = nullptr;  // device status word for bounded waits
+    void *h_pinned = nullptr;     // pinned staging for *_host calls
+    size_t h_pinned_bytes = 0;
+};
+
+struct pg_qtensor {
+    const int8_t *d_data_i8 = nullptr;    // [K,N] (optional)
+    const int8_t *d_data_i8_t = nullptr;  // [N,K]
+    const float *d_scales = nullptr;      // [N]
+    int64_t rows = 0;                     // K
+    int64_t cols = 0;                     // N held on this GPU
+    bool owned = false;
+    // TMA descriptor of data_i8_t for the tcgen05 path, built on first use (128 B, opaque)
+    alignas(64) unsigned char tmap_b[128];
+    int tmap_b_box_rows = 0;
+};
+
+struct pg_gguf_weight {
+    int32_t type = 0;
+    int64_t n = 0, k = 0;       // rows held on this GPU, columns
+    // Repacked at upload: quants and scales in separate, 16-byte aligned planes.
+    //   Q8_0: qs [N][K] i8                         d [N][K/32] f16
+    //   Q4_0: qs [N][K/2] u8 (block-local order)   d [N][K/32] f16
+    //   Q4_1: as Q4_0                              d, m [N][K/32] f16
+    uint8_t *d_qs = nullptr;
+    uint16_t *d_d = nullptr;
+    uint16_t *d_m = nullptr;
+};
+
+int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes);
+int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes);
+
+// ------------------------------------------------------- kernel launchers ----
+// pg_quantize.cu
+int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales);
+int32_t pgk_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int8_t *d_q, int8_t *d_qt, float *d_scales);
+int32_t pgk_dequantize(pg_ctx *ctx, const int8_t *d_q, const float *d_scales, int64_t rows, int64_t cols, float *d_out);
+int32_t pgk_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n, float *d_out);
+// pg_gemm_naive.cu
+int32_t pgk_gemm_i8_naive(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                          const float *d_ws, int64_t n, float *d_y, int32_t *d_acc);
+// pg_gemv_w8a8.cu
+bool pgk_gemm_i8_stream_supports(int64_t m, int64_t k, int64_t n);
+int32_t pgk_gemm_i8_stream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                           const float *d_ws, int64_t n, float *d_y, int32_t *d_acc);
+// pg_gemm_tcgen05.cu
+bool pgk_gemm_i8_tcgen05_supports(int64_t m, int64_t k, int64_t n);
+int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, pg_qtensor *w,
+                            float *d_y, int32_t *d_acc);
+// pg_gguf.cu
+int32_t pgk_dequant_blocks(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t num_blocks, float *d_out);
+int32_t pgk_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float *d_out);
+int32_t pgk_gguf_repack(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t n, int64_t k, pg_gguf_weight *w);
+int32_t pgk_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
+
+// ------------------------------------------------------- device helpers ----
+// Rust `(v.round().clamp(-127.0, 127.0)) as i8`: roundf is half away from zero; the
+// float->int conversion maps NaN to 0 and saturates, so the clamp can be done on the
+// integer and NaN never meets a float min/max (which would drop it).
+__device__ __forceinline__ int pg_round_clamp_i8(float v)
+{
+    int i = __float2int_rz(roundf(v));
+    return max(-127, min(127, i));
+}

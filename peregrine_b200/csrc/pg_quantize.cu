@@ -1,0 +1,229 @@
+// Quantisers of the int8 path.
+//
+//   quantize_rows_kernel     quant::quantize_activations, scalar branch (src/quant.rs:97-109)
+//   col_absmax_kernel +
+//   quantize_cols_kernel     quant::quantize_weights (src/quant.rs:27-75)
+//   dequantize_kernel        quant::dequantize (src/quant.rs:115-123)
+//   matmul_f32_kernel        Tensor::matmul naive branch (src/tensor.rs:1342-1354)
+//
+// All float steps use the explicitly rounded intrinsics (__fdiv_rn, __fmul_rn, __fadd_rn)
+// so that no FMA contraction or approximate division can change a bit; denormals are kept
+// (the library is built without -use_fast_math / -ftz).
+#include "pg_internal.cuh"
+
+namespace {
+
+constexpr int QR_THREADS = 256;
+
+__device__ __forceinline__ float block_max(float v, float *smem)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float r = (lane < (blockDim.x >> 5)) ? smem[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
+    return r;  // every thread holds the block maximum
+}
+
+// One CTA per row.  The row is read once with 128-bit loads and kept in registers
+// (up to VPT float4 per thread); the absmax is a warp-shuffle + shared-memory reduction
+// (max is order-independent, fmaxf drops NaN like f32::max); the i8 results leave as
+// packed 32-bit stores.  Columns past THREADS*VPT*4 are re-read in the second pass.
+template <int VPT>
+__global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *__restrict__ x, int64_t cols,
+                                                                    int8_t *__restrict__ q, float *__restrict__ scales)
+{
+    __shared__ float red[32];
+    const int64_t row = blockIdx.x;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols);
+    const int64_t nvec = cols >> 2;
+    float4 v[VPT];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
+        v[i] = (c < nvec) ? __ldg(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+    }
+    for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) {
+        const float4 t = __ldg(xr + c);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
+    }
+    amax = block_max(amax, red);
+    const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (threadIdx.x == 0) scales[row] = scale;
+    uint32_t *qr = reinterpret_cast<uint32_t *>(q + row * cols);
+    auto pack = [&](const float4 &t) -> uint32_t {
+        const int a = pg_round_clamp_i8(__fmul_rn(t.x, inv));
+        const int b = pg_round_clamp_i8(__fmul_rn(t.y, inv));
+        const int c = pg_round_clamp_i8(__fmul_rn(t.z, inv));
+        const int d = pg_round_clamp_i8(__fmul_rn(t.w, inv));
+        return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+    };
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+        const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
+        if (c < nvec) qr[c] = pack(v[i]);
+    }
+    for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) qr[c] = pack(__ldg(xr + c));
+}
+
+// Any cols / any alignment: scalar loads, two passes.
+__global__ void __launch_bounds__(QR_THREADS) quantize_rows_scalar_kernel(const float *__restrict__ x, int64_t cols,
+                                                                           int8_t *__restrict__ q, float *__restrict__ scales)
+{
+    __shared__ float red[32];
+    const int64_t row = blockIdx.x;
+    const float *xr = x + row * cols;
+    float amax = 0.0f;
+    for (int64_t c = threadIdx.x; c < cols; c += QR_THREADS) amax = fmaxf(amax, fabsf(xr[c]));
+    amax = block_max(amax, red);
+    const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (threadIdx.x == 0) scales[row] = scale;
+    for (int64_t c = threadIdx.x; c < cols; c += QR_THREADS) q[row * cols + c] = (int8_t)pg_round_clamp_i8(__fmul_rn(xr[c], inv));
+}
+
+// ---- weights: per-column absmax over [K,N] ---------------------------------
+// Thread = one column (a warp reads 128 contiguous bytes of a row); grid.y splits the rows.
+// Partial maxima meet in an integer atomicMax on the bit pattern, which orders non-negative
+// floats correctly.  `v > m` is false for NaN, so NaN never becomes a maximum (quant.rs:35).
+constexpr int CA_THREADS = 256;
+constexpr int CA_ROWS = 128;
+__global__ void __launch_bounds__(CA_THREADS) col_absmax_kernel(const float *__restrict__ w, int64_t rows, int64_t cols,
+                                                                 int *__restrict__ amax_bits)
+{
+    const int64_t n = (int64_t)blockIdx.x * CA_THREADS + threadIdx.x;
+    if (n >= cols) return;
+    const int64_t r0 = (int64_t)blockIdx.y * CA_ROWS;
+    const int64_t r1 = min(rows, r0 + CA_ROWS);
+    float m = 0.0f;
+    for (int64_t r = r0; r < r1; r++) {
+        const float v = fabsf(__ldg(w + r * cols + n));
+        if (v > m) m = v;
+    }
+    atomicMax(amax_bits + n, __float_as_int(m));
+}
+
+// ---- weights: quantise a 32x32 tile and write both layouts coalesced --------
+__global__ void __launch_bounds__(256) quantize_cols_kernel(const float *__restrict__ w, int64_t rows, int64_t cols,
+                                                             const int *__restrict__ amax_bits, int8_t *__restrict__ q,
+                                                             int8_t *__restrict__ qt, float *__restrict__ scales)
+{
+    __shared__ int8_t tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const int64_t n = (int64_t)blockIdx.x * 32 + tx;
+    const int64_t k0 = (int64_t)blockIdx.y * 32;
+    float scale = 1.0f;
+    if (n < cols) {
+        const float amax = __int_as_float(amax_bits[n]);
+        scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
+        if (blockIdx.y == 0 && ty == 0) scales[n] = scale;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int kk = ty + j * 8;
+        const int64_t k = k0 + kk;
+        int8_t v = 0;
+        if (n < cols && k < rows) {
+            v = (int8_t)pg_round_clamp_i8(__fdiv_rn(__ldg(w + k * cols + n), scale));
+            if (q) q[k * cols + n] = v;
+        }
+        tile[kk][tx] = v;
+    }
+    __syncthreads();
+    if (qt) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int nn = ty + j * 8;
+            const int64_t no = (int64_t)blockIdx.x * 32 + nn;
+            const int64_t k = k0 + tx;
+            if (no < cols && k < rows) qt[no * rows + k] = tile[tx][nn];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) dequantize_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
+                                                          int64_t total, int64_t cols, float *__restrict__ out)
+{
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < total) out[i] = __fmul_rn((float)q[i], __ldg(scales + (i % cols)));
+}
+
+// One thread per output; the sum runs in ascending p with the multiply and the add rounded
+// separately, so the result is bit-identical to the reference's naive loop.
+__global__ void __launch_bounds__(256) matmul_f32_kernel(const float *__restrict__ a, const float *__restrict__ b, int64_t m,
+                                                          int64_t k, int64_t n, float *__restrict__ out)
+{
+    const int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t i = blockIdx.y;
+    if (j >= n || i >= m) return;
+    float sum = 0.0f;
+    for (int64_t p = 0; p < k; p++) sum = __fadd_rn(sum, __fmul_rn(__ldg(a + i * k + p), __ldg(b + p * n + j)));
+    out[i * n + j] = sum;
+}
+
+}  // namespace
+
+int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales)
+{
+    if (rows == 0) return PG_OK;
+    PG_REQUIRE(rows <= 0x7fffffff, "quantize_activations: rows=%lld exceeds the grid limit", (long long)rows);
+    const bool vec = (cols % 4 == 0) && (((uintptr_t)d_x & 15) == 0) && (((uintptr_t)d_q & 3) == 0);
+    if (cols == 0) {
+        // scale of an empty row is 1.0 (amax == 0)
+        quantize_rows_scalar_kernel<<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, 0, d_q, d_scales);
+    } else if (!vec) {
+        quantize_rows_scalar_kernel<<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
+    } else if (cols <= 4 * QR_THREADS * 4) {
+        quantize_rows_kernel<4><<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
+    } else {
+        quantize_rows_kernel<16><<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
+    }
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
+int32_t pgk_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int8_t *d_q, int8_t *d_qt,
+                             float *d_scales)
+{
+    if (cols == 0) return PG_OK;
+    const int32_t rc = pg_scratch_reserve(ctx, (size_t)cols * sizeof(int));
+    if (rc != PG_OK) return rc;
+    int *amax = reinterpret_cast<int *>(ctx->scratch);
+    PG_CUDA(cudaMemsetAsync(amax, 0, (size_t)cols * sizeof(int), ctx->stream));
+    if (rows > 0) {
+        dim3 g1((unsigned)((cols + CA_THREADS - 1) / CA_THREADS), (unsigned)((rows + CA_ROWS - 1) / CA_ROWS));
+        PG_REQUIRE(g1.y <= 65535, "quantize_weights: rows=%lld too large", (long long)rows);
+        col_absmax_kernel<<<g1, CA_THREADS, 0, ctx->stream>>>(d_w, rows, cols, amax);
+        PG_LAUNCHED();
+    }
+    dim3 g2((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32 > 0 ? (rows + 31) / 32 : 1));
+    PG_REQUIRE(g2.y <= 65535, "quantize_weights: rows=%lld too large", (long long)rows);
+    quantize_cols_kernel<<<g2, 256, 0, ctx->stream>>>(d_w, rows, cols, amax, d_q, d_qt, d_scales);
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
+int32_t pgk_dequantize(pg_ctx *ctx, const int8_t *d_q, const float *d_scales, int64_t rows, int64_t cols, float *d_out)
+{
+    const int64_t total = rows * cols;
+    if (total == 0) return PG_OK;
+    dequantize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(d_q, d_scales, total, cols, d_out);
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
+int32_t pgk_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n, float *d_out)
+{
+    if (m == 0 || n == 0) return PG_OK;
+    PG_REQUIRE(m <= 65535, "matmul_f32: m=%lld exceeds the grid limit of this checker kernel", (long long)m);
+    dim3 g((unsigned)((n + 255) / 256), (unsigned)m);
+    matmul_f32_kernel<<<g, 256, 0, ctx->stream>>>(d_a, d_b, m, k, n, d_out);
+    PG_LAUNCHED();
+    return PG_OK;
+}

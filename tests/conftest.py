@@ -24,3 +24,11 @@ def oracle_mt():
     from oracle.pgoracle import Oracle
 
     return Oracle(mt=True)
+
+
+@pytest.fixture(scope="session")
+def gpu():
+    """The thread's GPU context.  Fails (never skips) if the CUDA library cannot be used."""
+    import peregrine_b200 as pg
+
+    return pg.init_gpu(0)

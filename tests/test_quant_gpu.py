@@ -1,0 +1,340 @@
+"""Parity of the CUDA int8 path with the CPU oracle, through the C ABI (ctypes).
+
+Bars: quantised i8 activations/weights, f32 scales and i32 accumulators are compared
+bit for bit; the f32 output of the W8A8 product is also compared bit for bit (the epilogue is two
+rounded multiplies in a fixed order), which is stricter than the 1e-5 relative the path requires.
+The reference's own tolerance tests (src/quant.rs:225-291, tests/quant_parity.rs:6-77) are
+re-run against the CUDA path with their inputs and tolerances."""
+import numpy as np
+import pytest
+
+from _inputs import bits_equal, linear_inputs, normal, rng
+
+pytestmark = pytest.mark.gpu
+
+ALGOS = {"naive": 1, "stream": 2, "tcgen05": 3}
+
+
+@pytest.fixture(scope="module")
+def pg():
+    import peregrine_b200
+
+    return peregrine_b200
+
+
+# ------------------------------------------------------------ activations ----
+@pytest.mark.parametrize("m,k,seed,outliers", [
+    (32, 4096, 0, False),      # single-linear config
+    (1, 4096, 1000, True), (4, 4096, 1001, True), (16, 4096, 1002, True),
+    (16, 14336, 1008, True),   # widest decode row
+    (512, 4096, 2000, False),
+    (3, 20000, 5, False),      # longer than the register-resident part of a row
+    (7, 1027, 6, False), (5, 1, 7, False), (2, 3, 8, False), (1, 18, 9, False),  # unaligned: scalar kernel
+])
+def test_quantize_activations_bit_exact(pg, gpu, oracle_mt, m, k, seed, outliers):
+    x, _ = linear_inputs(m, k, 1, seed, outliers)
+    q, s = pg.quant.quantize_activations(x, m, k, gpu)
+    qo, so = oracle_mt.quantize_activations(x, m, k)
+    assert bits_equal(s, so)
+    assert np.array_equal(q, qo)
+
+
+def test_quantize_activations_special_rows(pg, gpu, oracle):
+    k = 256
+    g = rng(11)
+    x = normal(g, (10, k))
+    x[0] = 0.0                                   # all-zero row: scale 1.0
+    x[1, 5] = np.nan                             # NaN ignored by absmax, quantises to 0
+    x[2, 7] = np.inf                             # scale inf, everything -> 0
+    x[3, 9] = -np.inf
+    x[4] = np.float32(1e-45) * np.sign(x[4])     # amax/127 underflows to 0: inv = inf
+    x[5] = x[5] * np.float32(1e-38)              # subnormal scale
+    x[6, :] = np.nan                             # all NaN: amax 0 -> scale 1, q = 0
+    x[7] = x[7] * np.float32(1e30)               # large finite
+    x[8, :4] = [3.4e38, -3.4e38, 1.0, 0.0]
+    x[9, 0] = -0.0
+    q, s = pg.quant.quantize_activations(x, 10, k, gpu)
+    qo, so = oracle.quantize_activations(x, 10, k)
+    assert bits_equal(s, so)
+    assert np.array_equal(q, qo)
+    assert s[0] == 1.0 and not q[0].any() and not q[2].any() and not q[6].any()
+
+
+def test_quantize_activations_ties_round_half_away(pg, gpu, oracle):
+    """absmax 127 makes scale = inv = 1, so x.5 inputs are exact ties: the scalar reference rounds
+    them away from zero (src/quant.rs:106)."""
+    k = 512
+    x = np.zeros((2, k), np.float32)
+    x[0, 0] = 127.0
+    x[0, 1:255] = np.arange(-127, 127, dtype=np.float32) + 0.5
+    x[1, 0] = -127.0
+    x[1, 1:255] = -(np.arange(-127, 127, dtype=np.float32) + 0.5)
+    q, s = pg.quant.quantize_activations(x, 2, k, gpu)
+    qo, so = oracle.quantize_activations(x, 2, k)
+    assert s[0] == 1.0 and np.array_equal(q, qo) and bits_equal(s, so)
+    assert q[0, 1 + 127] == 1 and q[0, 1 + 126] == -1  # 0.5 -> 1, -0.5 -> -1
+
+
+def test_quantize_activations_empty(pg, gpu):
+    q, s = pg.quant.quantize_activations(np.zeros(0, np.float32), 0, 64, gpu)
+    assert q.shape == (0, 64) and s.shape == (0,)
+    q, s = pg.quant.quantize_activations(np.zeros(0, np.float32), 3, 0, gpu)
+    assert q.shape == (3, 0) and np.array_equal(s, np.ones(3, np.float32))
+    with pytest.raises(AssertionError):  # the reference's assert_eq!(data.len(), rows * cols)
+        pg.quant.quantize_activations(np.zeros(5, np.float32), 2, 3, gpu)
+
+
+# ---------------------------------------------------------------- weights ----
+@pytest.mark.parametrize("k,n,seed", [(4096, 4096, 0), (4096, 1024, 1), (33, 65, 2), (1, 7, 3), (129, 31, 4), (64, 1, 5)])
+def test_quantize_weights_bit_exact(pg, gpu, oracle_mt, k, n, seed):
+    w = normal(rng(seed), (k, n), 0.02)
+    qt = pg.quant.quantize_weights(w, k, n, gpu)
+    ref = oracle_mt.quantize_weights(w, k, n)
+    assert bits_equal(qt.scales, ref.scales)
+    assert np.array_equal(qt.data_i8, ref.data_i8)
+    assert np.array_equal(qt.data_i8_t, ref.data_i8_t)
+    assert (qt.rows, qt.cols) == (k, n)
+
+
+def test_quantize_weights_special_columns(pg, gpu, oracle):
+    g = rng(21)
+    w = normal(g, (40, 12), 0.02)
+    w[:, 0] = 0.0              # zero column: scale 1
+    w[3, 1] = np.nan           # NaN never wins the absmax, quantises to 0
+    w[5, 2] = np.inf           # scale inf: inf/inf = NaN -> 0, finite/inf -> 0
+    w[:, 3] = np.float32(1e-44)
+    w[:, 4] *= np.float32(1e-38)
+    w[:, 5] = np.nan
+    w[0, 6], w[1, 6] = 127.0, 63.5   # tie after a true division
+    qt = pg.quant.quantize_weights(w, 40, 12, gpu)
+    ref = oracle.quantize_weights(w, 40, 12)
+    assert bits_equal(qt.scales, ref.scales)
+    assert np.array_equal(qt.data_i8, ref.data_i8) and np.array_equal(qt.data_i8_t, ref.data_i8_t)
+
+
+def test_dequantize_bit_exact(pg, gpu, oracle):
+    w = normal(rng(31), (96, 50), 0.02)
+    qt = pg.quant.quantize_weights(w, 96, 50, gpu)
+    ref = oracle.quantize_weights(w, 96, 50)
+    assert bits_equal(pg.quant.dequantize(qt, gpu), oracle.dequantize(ref))
+
+
+# ----- the reference's own tests, against the CUDA path (same inputs and tolerances) -----
+def test_reference_roundtrip_tests(pg, gpu):
+    for rows, cols, gen, eps in (
+        (32, 64, lambda i: (i.astype(np.float32) - np.float32(32 * 64 // 2)) * np.float32(0.01), 1e-6),   # src/quant.rs:225-249
+        (64, 128, lambda i: ((i * 17 + 5) % 400).astype(np.float32) / np.float32(100.0) - np.float32(2.0), 1e-7),  # tests/quant_parity.rs:6-32
+    ):
+        data = gen(np.arange(rows * cols, dtype=np.int64)).astype(np.float32)
+        qt = pg.quant.quantize_weights(data, rows, cols, gpu)
+        rec = pg.quant.dequantize(qt, gpu)
+        d = data.reshape(rows, cols)
+        amax = np.abs(d).max(axis=0)
+        scale = np.where(amax == 0, np.float32(1), amax / np.float32(127))
+        assert np.all(np.abs(d - rec) <= scale[None, :] + eps)
+
+
+@pytest.mark.parametrize("m,k,n,mod,rt,at", [(16, 64, 32, 100, 0.05, 0.01), (32, 128, 64, 200, 0.15, 0.05)])
+def test_reference_i8_vs_f32_matmul(pg, gpu, oracle, m, k, n, mod, rt, at):
+    """src/quant.rs:252-291 and tests/quant_parity.rs:35-77."""
+    a = (((np.arange(m * k, dtype=np.int64) * 7 + 3) % mod).astype(np.float32) / np.float32(mod) - np.float32(0.5)).astype(np.float32)
+    w = (((np.arange(k * n, dtype=np.int64) * 13 + 7) % mod).astype(np.float32) / np.float32(mod) - np.float32(0.5)).astype(np.float32)
+    expected = oracle.matmul_f32(a, w, m, k, n)
+    qt = pg.quant.quantize_weights(w, k, n, gpu)
+    result = pg.quant.matmul_quantized(a, m, k, qt, gpu)
+    diff = np.abs(result - expected)
+    rtol = diff / np.maximum(np.abs(expected), 1e-6)
+    assert np.all((rtol < rt) | (diff < at))
+    # and bit-exact against the oracle's W8A8 result
+    assert bits_equal(result, oracle.matmul_quantized(a, m, k, oracle.quantize_weights(w, k, n)))
+
+
+def _lcg(n, seed):
+    out = np.empty(n, np.float32)
+    state = seed
+    for i in range(n):
+        state = (state * 1103515245 + 12345) & 0xFFFFFFFF
+        out[i] = np.float32(np.float32(state) / np.float32(0xFFFFFFFF)) * np.float32(2.0) - np.float32(1.0)
+    return out
+
+
+@pytest.mark.parametrize("m,k,n", [(8, 32, 16), (1, 64, 1), (32, 128, 64), (16, 256, 32)])
+def test_reference_lcg_shapes(pg, gpu, oracle, m, k, n):
+    """Inputs and shapes of tests/huffman_parity.rs:23-41."""
+    a, w = _lcg(m * k, 42), _lcg(k * n, 123)
+    ref = oracle.quantize_weights(w, k, n)
+    out_o, acc_o, q_o, s_o = oracle.matmul_quantized(a, m, k, ref, return_parts=True)
+    qt = pg.quant.quantize_weights(w, k, n, gpu)
+    y, acc, q, s = pg.quant.matmul_quantized_parts(gpu, a, m, k, qt)
+    assert np.array_equal(q, q_o) and bits_equal(s, s_o) and np.array_equal(acc, acc_o) and bits_equal(y, out_o)
+
+
+# ------------------------------------------------ the product, every kernel ----
+def _check_product(pg, gpu, orc, x, w, m, k, n, algos):
+    ref = orc.quantize_weights(w, k, n)
+    out_o, acc_o, q_o, s_o = orc.matmul_quantized(x, m, k, ref, return_parts=True)
+    qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, k, n)
+    qt.to_gpu(gpu)
+    for name in algos:
+        y, acc, q, s = pg.quant.matmul_quantized_parts(gpu, x, m, k, qt, ALGOS[name])
+        assert np.array_equal(q, q_o) and bits_equal(s, s_o), name
+        assert np.array_equal(acc, acc_o), f"{name}: i32 accumulators differ"
+        assert bits_equal(y, out_o), f"{name}: f32 outputs differ"
+    y = pg.quant.matmul_quantized(x, m, k, qt, gpu)      # host API, automatic kernel choice
+    assert bits_equal(y, out_o)
+    qt.free_gpu()
+
+
+def test_single_linear_config(pg, gpu, oracle_mt):
+    """M=32, K=4096, N=4096, seed 0."""
+    x, w = linear_inputs(32, 4096, 4096, 0)
+    _check_product(pg, gpu, oracle_mt, x, w, 32, 4096, 4096, ["naive", "stream", "tcgen05"])
+
+
+@pytest.mark.parametrize("idx,m,k,n", [(i, m, k, n) for i, (m, (k, n)) in enumerate(
+    [(m, kn) for kn in [(4096, 4096), (4096, 14336), (14336, 4096)] for m in (1, 4, 16)])])
+def test_decode_gemv_sweep(pg, gpu, oracle_mt, idx, m, k, n):
+    """Llama-3-8B projection shapes, activations with 1 % outlier channels (x20)."""
+    x, w = linear_inputs(m, k, n, 1000 + idx, outliers=True)
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["stream", "tcgen05"])
+
+
+@pytest.mark.parametrize("m,k,n", [
+    (1, 16, 1), (2, 32, 9), (8, 48, 8), (9, 64, 17), (16, 80, 24), (17, 128, 40), (33, 144, 7), (64, 4096 + 16, 100),
+    (5, 1040, 1000), (12, 2048, 130),
+])
+def test_stream_kernel_ragged_shapes(pg, gpu, oracle_mt, m, k, n):
+    x, w = linear_inputs(m, k, n, 77 + m + n)
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive", "stream"])
+
+
+@pytest.mark.parametrize("m,k,n", [
+    (1, 16, 1), (128, 128, 256), (127, 112, 255), (129, 144, 257), (200, 1040, 300), (300, 4096, 520), (65, 272, 64),
+    (256, 2048, 1000),
+])
+def test_tcgen05_kernel_ragged_shapes(pg, gpu, oracle_mt, m, k, n):
+    """Tile edges in M, N and K (K not a multiple of the 128-byte stage, N not of the tile)."""
+    x, w = linear_inputs(m, k, n, 99 + m + n)
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive", "tcgen05"])
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_tcgen05_every_tile_width(pg, gpu, oracle_mt, bn):
+    x, w = linear_inputs(384, 1024, 1280, 500 + bn)
+    gpu.lib.pg_tune_tcgen05_bn(bn)
+    try:
+        _check_product(pg, gpu, oracle_mt, x, w, 384, 1024, 1280, ["tcgen05"])
+    finally:
+        gpu.lib.pg_tune_tcgen05_bn(0)
+
+
+@pytest.mark.parametrize("ng", [1, 2, 4])
+def test_stream_every_column_group(pg, gpu, oracle_mt, ng):
+    gpu.lib.pg_tune_stream_ng(ng)
+    try:
+        for m in (3, 16):
+            x, w = linear_inputs(m, 1024, 333, 600 + ng + m)
+            _check_product(pg, gpu, oracle_mt, x, w, m, 1024, 333, ["stream"])
+    finally:
+        gpu.lib.pg_tune_stream_ng(0)
+
+
+def test_unaligned_k_uses_the_checker_kernel(pg, gpu, oracle):
+    """K not a multiple of 16: neither fast kernel takes it; the result is still exact."""
+    for m, k, n in ((3, 17, 5), (20, 1001, 33), (70, 250, 19)):
+        x, w = linear_inputs(m, k, n, 42 + k)
+        ref = oracle.quantize_weights(w, k, n)
+        out_o = oracle.matmul_quantized(x, m, k, ref)
+        qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, k, n)
+        assert bits_equal(pg.quant.matmul_quantized(x, m, k, qt, gpu), out_o)
+
+
+def test_prefill_m512(pg, gpu, oracle_mt):
+    """Prefill config M=512, K=4096, N=4096: full i32 and f32 comparison with the CPU oracle."""
+    x, w = linear_inputs(512, 4096, 4096, 2000)
+    _check_product(pg, gpu, oracle_mt, x, w, 512, 4096, 4096, ["tcgen05"])
+
+
+@pytest.mark.parametrize("idx,m,n", [(2, 2048, 4096), (3, 2048, 14336), (4, 8192, 4096), (5, 8192, 14336)])
+def test_prefill_large_vs_checker_and_sampled_oracle(pg, gpu, oracle_mt, idx, m, n):
+    """Too large to sweep on the CPU: the tcgen05 result is compared over the whole output with the
+    independent one-thread-per-output kernel, and on 200k random outputs with the CPU oracle."""
+    import ctypes as C
+
+    k = 4096
+    g = rng(2000 + idx)
+    x = normal(g, (m, k))
+    # weights: quantise on the GPU (bit-exact with the oracle, checked above) to keep the test short
+    w = normal(g, (k, n), 0.02)
+    qt = pg.quant.quantize_weights(w, k, n, gpu)
+    qt.to_gpu(gpu)
+    lib = gpu.lib
+    d_x = gpu.upload(x.reshape(-1))
+    d_q = gpu.alloc(m * k + 16, np.int8)
+    d_s = gpu.alloc(m, np.float32)
+    d_y1, d_y2 = gpu.alloc(m * n, np.float32), gpu.alloc(m * n, np.float32)
+    d_a1, d_a2 = gpu.alloc(m * n, np.int32), gpu.alloc(m * n, np.int32)
+    from peregrine_b200 import _lib
+
+    _lib.check(lib.pg_matmul_quantized_ex(gpu.handle, d_x.ptr, m, k, qt._gpu, d_y1.ptr, d_a1.ptr, d_q.ptr, d_s.ptr, 3))
+    _lib.check(lib.pg_gemm_i8(gpu.handle, d_q.ptr, d_s.ptr, m, k, qt._gpu, d_y2.ptr, d_a2.ptr, 1))
+    gpu.sync()
+    assert gpu.device_status() == 0
+    a1, a2 = d_a1.read(), d_a2.read()
+    assert np.array_equal(a1, a2)
+    y1 = d_y1.read()
+    assert bits_equal(y1, d_y2.read())
+    q = d_q.read()[: m * k].reshape(m, k)
+    qo, so = oracle_mt.quantize_activations(x, m, k)
+    assert np.array_equal(q, qo) and bits_equal(d_s.read(), so)
+    idx_s = rng(9).integers(0, m * n, 200_000)
+    acc_s = oracle_mt.gemm_i8_sampled(qo, qt.data_i8_t, n, k, idx_s)
+    assert np.array_equal(a1[idx_s], acc_s)
+    ep = (acc_s.astype(np.float32) * so[idx_s // n]) * qt.scales[idx_s % n]
+    assert bits_equal(y1[idx_s], ep.astype(np.float32))
+    # linearity in the integer domain: A and -A give negated sums
+    for b in (d_x, d_q, d_s, d_y1, d_y2, d_a1, d_a2):
+        b.free()
+    qt.free_gpu()
+
+
+def test_shape_errors_match_reference_asserts(pg, gpu):
+    w = normal(rng(1), (64, 8), 0.02)
+    qt = pg.quant.quantize_weights(w, 64, 8, gpu)
+    with pytest.raises(AssertionError):   # assert_eq!(w.rows, k)
+        pg.quant.matmul_quantized(np.zeros(2 * 32, np.float32), 2, 32, qt, gpu)
+    with pytest.raises(AssertionError):   # assert_eq!(a_data.len(), m * k)
+        pg.quant.matmul_quantized(np.zeros(10, np.float32), 2, 64, qt, gpu)
+    with pytest.raises(AssertionError):   # expect("weights not on GPU")
+        pg.quant.matmul_quantized_gpu(gpu, np.zeros(128, np.float32), 2, 64, pg.quant.quantize_weights(w, 64, 8, gpu))
+    assert pg.quant.matmul_quantized(np.zeros(0, np.float32), 0, 64, qt, gpu).shape == (0, 8)
+
+
+def test_matmul_quantized_gpu_is_async_and_resident(pg, gpu, oracle):
+    """to_gpu is idempotent, the result buffer is returned unsynchronised and read() blocks
+    (tests/quant_parity.rs:98-107)."""
+    x, w = linear_inputs(4, 256, 48, 5)
+    ref = oracle.quantize_weights(w, 256, 48)
+    qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, 256, 48)
+    qt.to_gpu(gpu)
+    h = qt._gpu
+    qt.to_gpu(gpu)
+    assert qt._gpu is h
+    buf = pg.quant.matmul_quantized_gpu(gpu, x, 4, 256, qt)
+    gpu.sync()
+    assert bits_equal(buf.read().reshape(4, 48), oracle.matmul_quantized(x, 4, 256, ref))
+    qt.data_i8_t[:] = 0
+    qt.scales[:] = 0
+    qt.from_gpu(gpu)
+    assert np.array_equal(qt.data_i8_t, ref.data_i8_t) and bits_equal(qt.scales, ref.scales)
+
+
+def test_column_shard_equals_slice_of_full_result(pg, gpu, oracle):
+    """A GPU holding columns [b,e) produces exactly y[:, b:e] of the unsharded product."""
+    x, w = linear_inputs(16, 512, 96, 8)
+    ref = oracle.quantize_weights(w, 512, 96)
+    full = oracle.matmul_quantized(x, 16, 512, ref)
+    for b, e in ((0, 48), (48, 96), (24, 25), (96, 96)):
+        qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, 512, 96)
+        qt.to_gpu(gpu, b, e)
+        assert bits_equal(pg.quant.matmul_quantized(x, 16, 512, qt, gpu), full[:, b:e])
