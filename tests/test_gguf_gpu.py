@@ -62,7 +62,11 @@ def test_dequant_bit_exact_random_bytes(pg, gpu, oracle, kind):
     raw = g.integers(0, 256, nb * BS[kind], dtype=np.uint8)
     got = _dq(pg, kind)(raw, nb * 32, gpu)
     want = oracle.dequant(kind, raw, nb * 32)
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # a NaN scale gives NaN on both sides; which NaN payload an arithmetic op returns is a property
+    # of the processor, not of the algorithm, so NaNs are compared by position only
+    nan = np.isnan(want)
+    assert nan.any() and np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan])
 
 
 @pytest.mark.parametrize("kind", KINDS)
