@@ -1,0 +1,519 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 decode path (quant::matmul_quantized at M <= 16) on B200.
+
+Workload: the decode GEMV sweep -- M in {1,4,16} x (K,N) in {(4096,4096),(4096,14336),(14336,4096)}
+(Llama-3-8B projection shapes), activations ~N(0,1) with 1 % of channels scaled x20, weights
+~N(0,0.02) quantised per column to i8.  One "step" is one pass over the nine cases:
+per case, per-row activation quantisation followed by the int8 product and the scale epilogue.
+
+Metric: achieved HBM bandwidth in GB/s = algorithmic bytes of the sweep / time, with
+  bytes(M,K,N) = 4*M*K (x f32) + K*N (weights i8) + 4*N (scales) + 4*M*N (y f32).
+
+    python bench.py --gpus N --steps K --warmup W            this library
+    python bench.py --impl reference ...                     the reference's CPU algorithm (C port)
+
+With N > 1 the weights are sharded by output column over the ranks (one process per GPU,
+torchrun) and the output slices are all-gathered over NCCL; `value` is the whole job's bytes over
+the slowest rank's time.
+
+Cache discipline: every case of a step reads its own copy of the weights (three copies per shape,
+402 MB in total), so a weight matrix is re-read only after ~400 MB of other traffic (L2 is 126 MB).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (4096, 14336), (14336, 4096)]
+MS = [1, 4, 16]
+# order of a step: all shapes at M=1, then M=4, then M=16; case index = position in BASELINE's sweep
+CASES = [(mi, si) for mi in range(3) for si in range(3)]
+L2_BYTES = 126 * 1024 * 1024
+
+
+def bytes_w8a8(m, k, n):
+    return 4 * m * k + k * n + 4 * n + 4 * m * n
+
+
+def bytes_gemv_kernel(m, k, n):
+    """The product kernel alone: quantised activations in (i8 + scales) instead of f32."""
+    return m * k + 4 * m + k * n + 4 * n + 4 * m * n
+
+
+def sweep_bytes():
+    return sum(bytes_w8a8(MS[mi], *SHAPES[si]) for mi, si in CASES)
+
+
+def make_inputs(case_idx, m, k):
+    g = np.random.Generator(np.random.PCG64(1000 + case_idx))
+    x = g.standard_normal((m, k), dtype=np.float32)
+    ch = g.choice(k, size=int(np.ceil(0.01 * k)), replace=False)
+    x[:, ch] *= np.float32(20.0)
+    return x
+
+
+def make_weight(shape_idx, k, n):
+    g = np.random.Generator(np.random.PCG64(7000 + shape_idx))
+    return (g.standard_normal((k, n), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+
+
+# --------------------------------------------------------------------- clocks ----
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.rows = []
+        self.proc = None
+        self.t_mark = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(device_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def mark(self):
+        self.t_mark = time.time()
+
+    def stop(self, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "nvidia-smi unavailable"}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        inside = [r for t, r in self.rows if self.t_mark is not None and self.t_mark <= t <= t_end + 0.06]
+        window = "timed region"
+        if not inside:
+            inside = [r for _, r in self.rows[-4:]]
+            window = "timed region shorter than the sampling period: last samples under load (warm-up + timed)"
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in inside:
+            p = [c.strip() for c in r.split(",")]
+            if len(p) < 8:
+                continue
+            try:
+                sm.append(float(p[0]))
+                smax.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
+
+
+# ------------------------------------------------------------ reference (CPU) ----
+def run_reference(args):
+    """The reference's algorithm for this path (scalar branch of src/quant.rs, C port) on the host
+    cores.  The reference itself runs this path on one thread; here every output element is an
+    independent OpenMP task, so all cores are used and the result is unchanged."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle.pgoracle import Oracle
+
+    orc = Oracle(mt=True)
+    qts = []
+    for si, (k, n) in enumerate(SHAPES):
+        qts.append(orc.quantize_weights(make_weight(si, k, n), k, n))
+    xs = [make_inputs(ci, MS[mi], SHAPES[si][0]) for ci, (mi, si) in enumerate(CASES)]
+
+    from oracle.pgoracle import QuantizedTensor
+
+    def make_step(frac):
+        part = []
+        for qt in qts:
+            nf = max(1, int(qt.cols * frac))
+            part.append(QuantizedTensor(qt.data_i8, np.ascontiguousarray(qt.data_i8_t[:nf]), np.ascontiguousarray(qt.scales[:nf]), qt.rows, nf))
+
+        def step():
+            for ci, (mi, si) in enumerate(CASES):
+                orc.matmul_quantized(xs[ci], MS[mi], SHAPES[si][0], part[si])
+
+        return step, sum(bytes_w8a8(MS[mi], SHAPES[si][0], part[si].cols) for mi, si in CASES)
+
+    # A step is one pass over the sweep; when K passes would not finish in about 90 s, each step
+    # covers the same leading fraction of every case's output columns (columns are independent).
+    step, nbytes = make_step(1.0)
+    t0 = time.perf_counter()
+    step()
+    t_full = time.perf_counter() - t0
+    frac = 1.0
+    budget = 90.0 / max(args.steps + args.warmup, 1)
+    if t_full > budget:
+        frac = max(budget / t_full, 1.0 / 64)
+        step, nbytes = make_step(frac)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = nbytes * args.steps / dt / 1e9
+    sample = (f"{args.steps} passes of the nine-case sweep" if frac == 1.0 else
+              f"{args.steps} passes over the first {frac:.4f} of each case's output columns (full pass takes {t_full * 1e3:.0f} ms)")
+    line = {
+        "impl": "reference", "metric": "w8a8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": orc.threads, "kind": "port",
+                         "sample": sample + "; OpenMP over independent outputs (the reference itself runs this path on one thread)"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# -------------------------------------------------------------------- our arm ----
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import peregrine_b200 as pg
+    from peregrine_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one process per GPU)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.Stream(device=dev)
+    gpu = pg.GpuContext(local, stream.cuda_stream)
+    lib = gpu.lib
+    warmup = max(args.warmup, 3)
+
+    # ---- weights: quantise on the GPU, keep this rank's column shard, three copies per shape ----
+    COPIES = 3
+    pool = []      # pool[si][c] = (pg_qtensor handle, torch tensors kept alive)
+    shard = []
+    for si, (k, n) in enumerate(SHAPES):
+        w = make_weight(si, k, n)
+        qt = pg.quant.quantize_weights(w, k, n, gpu)
+        b, e = (n * rank) // world, (n * (rank + 1)) // world
+        shard.append((b, e))
+        t_w = torch.from_numpy(np.ascontiguousarray(qt.data_i8_t[b:e])).to(dev)
+        t_s = torch.from_numpy(np.ascontiguousarray(qt.scales[b:e])).to(dev)
+        copies = []
+        for c in range(COPIES):
+            # 1 KiB of slack after the weights keeps tiled loads of the last rows inside the allocation
+            buf = torch.empty(t_w.numel() + 1024, dtype=torch.int8, device=dev)
+            buf[: t_w.numel()].copy_(t_w.view(-1))
+            sc = t_s.clone()
+            h = _lib.C.c_void_p()
+            _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, buf.data_ptr(), sc.data_ptr(), k, e - b, _lib.C.byref(h)))
+            copies.append((h, buf, sc))
+        pool.append(copies)
+        del w, qt
+    torch.cuda.synchronize()
+
+    xs_host = [torch.from_numpy(make_inputs(ci, MS[mi], SHAPES[si][0])).pin_memory() for ci, (mi, si) in enumerate(CASES)]
+    xs = [x.to(dev) for x in xs_host]
+    ys = [torch.empty(MS[mi], shard[si][1] - shard[si][0], dtype=torch.float32, device=dev) for mi, si in CASES]
+    ys_full = [torch.empty(world, MS[mi], shard[si][1] - shard[si][0], dtype=torch.float32, device=dev) if world > 1 else None
+               for mi, si in CASES]
+    ys_host = [torch.empty(MS[mi], SHAPES[si][1], dtype=torch.float32).pin_memory() for mi, si in CASES]
+    even = all(SHAPES[si][1] % world == 0 for si in range(3))
+    if world > 1 and not even:
+        raise SystemExit("column shards must be equal for the all-gather")
+
+    def enqueue_products():
+        for ci, (mi, si) in enumerate(CASES):
+            k, _ = SHAPES[si]
+            h = pool[si][mi][0]
+            _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
+
+    def step_eager():
+        for ci, (mi, si) in enumerate(CASES):
+            k, _ = SHAPES[si]
+            h = pool[si][mi][0]
+            _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
+            if world > 1:
+                dist.all_gather_into_tensor(ys_full[ci], ys[ci])
+
+    n0 = lib.pg_launch_count()
+    with torch.cuda.stream(stream):
+        step_eager()
+    stream.synchronize()
+    launches_per_step = int(lib.pg_launch_count() - n0)
+
+    graph = None
+    if world == 1:
+        with gpu.record() as graph:
+            enqueue_products()
+
+    def step():
+        if graph is not None:
+            graph.launch()
+        else:
+            step_eager()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- timed region: exactly K steps, device time, max over ranks ----
+    sampler = ClockSampler(local) if rank == 0 else None
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            step()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.mark()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        barrier()
+    t_end = time.time()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop(t_end) if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    total_bytes = sweep_bytes()
+    value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+    assert gpu.device_status() == 0
+
+    # ---- end to end: host buffers in, host result out, every step ----
+    e2e_steps = min(args.steps, 2000)
+    h2d = sum(4 * MS[mi] * SHAPES[si][0] for mi, si in CASES)
+    d2h = sum(4 * MS[mi] * SHAPES[si][1] for mi, si in CASES)
+
+    def e2e_step():
+        for ci, (mi, si) in enumerate(CASES):
+            k, n = SHAPES[si]
+            h = pool[si][mi][0]
+            if world == 1:
+                # the C-ABI call with the exact shape of quant::matmul_quantized: copies x up, runs, copies y back, blocks
+                _lib.check(lib.pg_matmul_quantized_host(gpu.handle, xs_host[ci].data_ptr(), MS[mi], k, h, ys_host[ci].data_ptr()))
+            else:
+                xs[ci].copy_(xs_host[ci], non_blocking=True)
+                _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
+                dist.all_gather_into_tensor(ys_full[ci], ys[ci])
+                ys_host[ci].view(MS[mi], world, -1).copy_(ys_full[ci].permute(1, 0, 2), non_blocking=True)
+                stream.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = total_bytes * e2e_steps / e2e_s / 1e9
+
+    line = None
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except (OSError, ValueError):
+            pass
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
+
+        # ---- roofline of the dominant kernel (the int8 product): kernel-only replay of the nine launches
+        d_q, d_s = [], []
+        with torch.cuda.stream(stream):
+            for ci, (mi, si) in enumerate(CASES):
+                k = SHAPES[si][0]
+                q = torch.empty(MS[mi] * k + 16, dtype=torch.int8, device=dev)
+                s = torch.empty(MS[mi], dtype=torch.float32, device=dev)
+                _lib.check(lib.pg_quantize_activations(gpu.handle, xs[ci].data_ptr(), MS[mi], k, q.data_ptr(), s.data_ptr()))
+                d_q.append(q)
+                d_s.append(s)
+
+            def products_only():
+                for ci, (mi, si) in enumerate(CASES):
+                    k = SHAPES[si][0]
+                    _lib.check(lib.pg_gemm_i8(gpu.handle, d_q[ci].data_ptr(), d_s[ci].data_ptr(), MS[mi], k, pool[si][mi][0],
+                                              ys[ci].data_ptr(), None, _lib.ALGO_AUTO))
+
+            products_only()
+            with gpu.record() as g2:
+                products_only()
+            for _ in range(5):
+                g2.launch()
+            reps = max(20, min(args.steps, 2000))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                g2.launch()
+            e1.record(stream)
+            stream.synchronize()
+        k_ms = e0.elapsed_time(e1) / reps
+        kern_bytes = sum(bytes_gemv_kernel(MS[mi], SHAPES[si][0], shard[si][1] - shard[si][0]) for mi, si in CASES)
+        achieved = kern_bytes / (k_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gemv_w8a8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_src,
+                    "bytes_per_launch_avg": kern_bytes / 9, "us_per_launch_avg": k_ms * 1e3 / 9,
+                    "how": f"{reps} replays of a graph holding only the nine product launches, CUDA events on the launch stream"}
+
+        # ---- CPU baseline: the oracle's single-thread port (what the reference runs), bounded sample
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle.pgoracle import Oracle
+
+            orc = Oracle(mt=False)
+            qts = [orc.quantize_weights(make_weight(si, k, n), k, n) for si, (k, n) in enumerate(SHAPES)]
+            xn = [x.numpy() for x in xs_host]
+            passes = 0
+            t0 = time.perf_counter()
+            while passes < 2 or (time.perf_counter() - t0 < 10.0 and passes < 8):
+                for ci, (mi, si) in enumerate(CASES):
+                    orc.matmul_quantized(xn[ci], MS[mi], SHAPES[si][0], qts[si])
+                passes += 1
+            dt = time.perf_counter() - t0
+            cpu = {"value": total_bytes * passes / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                   "sample": f"{passes} full passes of the nine-case sweep, single thread (the reference's quant path is single-threaded)",
+                   "ms_per_step": dt / passes * 1e3, "host_cpus": os.cpu_count()}
+
+        line = {
+            "metric": "w8a8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9,
+                       "parallelism": f"column-sharded x{world}" + (", NCCL all-gather of output slices" if world > 1 else ""),
+                       "l2": "inputs larger than L2: each case reads its own copy of the weights (3 copies per shape, 402 MB per step)",
+                       "submission": "one CUDA graph per step" if graph is not None else "eager launches + NCCL",
+                       "bytes_per_step": total_bytes},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "api": "pg_matmul_quantized_host (pinned host x in, host y out, blocking)" if world == 1 else
+                           "pinned H2D + pg_matmul_quantized + all-gather + D2H"},
+            "gpu_launches": launches_per_step * args.steps,
+            "kernels_per_step": launches_per_step,
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+        }
+        if args.extra:
+            line["also"] = extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
+    """Secondary figures of the same path: prefill GEMM TOPS and GGUF dequant-product GB/s."""
+    import peregrine_b200 as pg
+    from peregrine_b200 import _lib
+
+    lib = gpu.lib
+    out = {}
+    g = np.random.Generator(np.random.PCG64(2002))
+    bf16 = float(peaks.get("bf16_tflops", 1590.0))
+    with torch.cuda.stream(stream):
+        for (m, k, n) in ((2048, 4096, 4096), (8192, 4096, 4096), (8192, 4096, 14336)):
+            x = torch.from_numpy(g.standard_normal((m, k), dtype=np.float32)).to(dev)
+            wq = torch.randint(-127, 128, (n * k + 1024,), dtype=torch.int8, device=dev)
+            sc = torch.rand(n, dtype=torch.float32, device=dev) * 1e-3
+            h = _lib.C.c_void_p()
+            _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, wq.data_ptr(), sc.data_ptr(), k, n, _lib.C.byref(h)))
+            y = torch.empty(m, n, dtype=torch.float32, device=dev)
+            q = torch.empty(m * k + 16, dtype=torch.int8, device=dev)
+            s = torch.empty(m, dtype=torch.float32, device=dev)
+            _lib.check(lib.pg_quantize_activations(gpu.handle, x.data_ptr(), m, k, q.data_ptr(), s.data_ptr()))
+            for _ in range(3):
+                _lib.check(lib.pg_gemm_i8(gpu.handle, q.data_ptr(), s.data_ptr(), m, k, h, y.data_ptr(), None, _lib.ALGO_TCGEN05))
+            reps = 20
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                _lib.check(lib.pg_gemm_i8(gpu.handle, q.data_ptr(), s.data_ptr(), m, k, h, y.data_ptr(), None, _lib.ALGO_TCGEN05))
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) / reps * 1e3
+            tops = 2.0 * m * n * k / (us * 1e-6) / 1e12
+            out[f"w8a8_gemm_M{m}_K{k}_N{n}"] = {"us": us, "tops": tops, "frac_of_2x_measured_bf16": tops / (2 * bf16),
+                                                  "frac_of_4500_nominal": tops / 4500.0}
+            lib.pg_qtensor_free(gpu.handle, h)
+            del x, wq, y, q
+    from oracle.pgoracle import Oracle
+
+    orc = Oracle(mt=True)
+    n, k = 14336, 4096
+    w = (g.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    for kind, bs in (("q4_0", 18), ("q8_0", 34)):
+        raw = orc.encode(kind, w)
+        copies = [pg.gguf.GgufWeight(kind, raw, n, k, gpu) for _ in range(6 if kind == "q4_0" else 3)]
+        for m in (1, 8):
+            with torch.cuda.stream(stream):
+                x = torch.from_numpy(g.standard_normal((m, k), dtype=np.float32)).to(dev)
+                y = torch.empty(m, n, dtype=torch.float32, device=dev)
+                for c in copies:
+                    c.matmul_device(x, m, y)
+                reps = 10
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    for c in copies:
+                        c.matmul_device(x, m, y)
+                e1.record(stream)
+                stream.synchronize()
+            us = e0.elapsed_time(e1) / (reps * len(copies)) * 1e3
+            nbytes = n * (k // 32) * bs + 4 * m * k + 4 * m * n
+            gbs = nbytes / (us * 1e-6) / 1e9
+            out[f"gguf_{kind}_M{m}"] = {"us": us, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak}
+        for c in copies:
+            c.free()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5000)
+    ap.add_argument("--warmup", type=int, default=100)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--extra", action="store_true", help="also time the prefill GEMM and the GGUF products")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

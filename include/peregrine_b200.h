@@ -47,6 +47,7 @@ extern "C" {
 typedef struct pg_ctx pg_ctx;
 typedef struct pg_qtensor pg_qtensor;
 typedef struct pg_gguf_weight pg_gguf_weight;
+typedef struct pg_graph pg_graph;
 
 typedef enum pg_status {
     PG_OK = 0,
@@ -82,6 +83,17 @@ PG_API int32_t pg_ctx_sync(pg_ctx *ctx);
 PG_API void *pg_ctx_stream(pg_ctx *ctx);
 /* Status word written by kernels whose waits are bounded; 0 if none gave up. Clears it. */
 PG_API int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out);
+
+/* ---- batched submission, replaces the pending command buffer of GpuContext
+ *      (src/metal/context.rs:188-204: commands accumulate and are submitted together) ----
+ * Everything enqueued on the context between begin and end is recorded into a CUDA graph
+ * instead of running; pg_graph_launch then submits the whole batch with one call.  Run the same
+ * calls once before recording: a call that has to grow the context's scratch memory cannot
+ * be recorded.  *_host calls (they block) cannot be recorded. */
+PG_API int32_t pg_graph_begin(pg_ctx *ctx);
+PG_API int32_t pg_graph_end(pg_ctx *ctx, pg_graph **out);
+PG_API int32_t pg_graph_launch(pg_ctx *ctx, pg_graph *graph);
+PG_API int32_t pg_graph_free(pg_ctx *ctx, pg_graph *graph);
 
 /* ---- device memory, replaces GpuContext::alloc/upload and GpuBuffer::read
  *      (src/metal/context.rs; used at src/quant.rs:176-187,207-210) ---- */

@@ -47,6 +47,10 @@ SIGNATURES = {
     "pg_ctx_sync": (_i32, [_vp]),
     "pg_ctx_stream": (_vp, [_vp]),
     "pg_ctx_device_status": (_i32, [_vp, C.POINTER(_i32)]),
+    "pg_graph_begin": (_i32, [_vp]),
+    "pg_graph_end": (_i32, [_vp, C.POINTER(_vp)]),
+    "pg_graph_launch": (_i32, [_vp, _vp]),
+    "pg_graph_free": (_i32, [_vp, _vp]),
     "pg_mem_alloc": (_i32, [_vp, _sz, C.POINTER(_vp)]),
     "pg_mem_free": (_i32, [_vp, _vp]),
     "pg_mem_upload": (_i32, [_vp, _vp, _vp, _sz]),

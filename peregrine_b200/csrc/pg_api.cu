@@ -22,6 +22,7 @@ void pg_set_error(const char *fmt, ...)
 int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes)
 {
     if (bytes <= ctx->scratch_bytes) return PG_OK;
+    if (ctx->capturing) PG_FAIL(PG_ERR_INVALID, "scratch memory would have to grow while a graph is being recorded; run the call once before recording");
     // Work already enqueued may still use the old block: drain before replacing it.
     PG_CUDA(cudaStreamSynchronize(ctx->stream));
     if (ctx->scratch) PG_CUDA(cudaFree(ctx->scratch));
@@ -150,6 +151,56 @@ int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out)
     PG_CUDA(cudaStreamSynchronize(ctx->stream));
     if (v != 0) PG_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(v), ctx->stream));
     if (status_out) *status_out = v;
+    return PG_OK;
+}
+
+int32_t pg_graph_begin(pg_ctx *ctx)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(!ctx->capturing, "pg_graph_begin: already recording");
+    PG_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    ctx->capturing = true;
+    return PG_OK;
+}
+
+int32_t pg_graph_end(pg_ctx *ctx, pg_graph **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "pg_graph_end: out is null");
+    *out = nullptr;
+    PG_REQUIRE(ctx->capturing, "pg_graph_end: not recording");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    PG_CUDA(cudaStreamEndCapture(ctx->stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) PG_FAIL(PG_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    pg_graph *pgg = new (std::nothrow) pg_graph();
+    if (!pgg) {
+        cudaGraphExecDestroy(exec);
+        PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    }
+    pgg->exec = exec;
+    *out = pgg;
+    return PG_OK;
+}
+
+int32_t pg_graph_launch(pg_ctx *ctx, pg_graph *graph)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(graph && graph->exec, "pg_graph_launch: graph is null");
+    PG_CUDA(cudaGraphLaunch(graph->exec, ctx->stream));
+    return PG_OK;
+}
+
+int32_t pg_graph_free(pg_ctx *ctx, pg_graph *graph)
+{
+    if (!graph) return PG_OK;
+    PG_ENTER(ctx);
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    delete graph;
     return PG_OK;
 }
 

@@ -52,6 +52,11 @@ struct pg_ctx {
     int32_t *d_status = nullptr;  // device status word for bounded waits
     void *h_pinned = nullptr;     // pinned staging for *_host calls
     size_t h_pinned_bytes = 0;
+    bool capturing = false;       // between pg_graph_begin and pg_graph_end
+};
+
+struct pg_graph {
+    cudaGraphExec_t exec = nullptr;
 };
 
 struct pg_qtensor {

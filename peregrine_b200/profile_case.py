@@ -1,0 +1,98 @@
+"""Runs one case of one kernel a few times, for profiling under `ncu` or quick timing.
+
+    python -m peregrine_b200.profile_case --op w8a8 --algo stream --m 16 --k 4096 --n 32768 --reps 3
+    python -m peregrine_b200.profile_case --op w8a8 --algo tcgen05 --m 2048 --k 4096 --n 4096
+    python -m peregrine_b200.profile_case --op gguf --kind q4_0 --m 1 --k 4096 --n 32768
+    python -m peregrine_b200.profile_case --op quant --m 8192 --k 4096
+
+Inputs are seeded random values generated on the host; weights for `w8a8` are random int8 (no
+quantisation pass), so start-up stays short.  Prints the mean time per call in microseconds
+(host clock around a synchronised loop, adequate for kernels of tens of microseconds and up).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import time
+
+import numpy as np
+
+from . import _lib
+from .gguf import BLOCK_BYTES, TYPE_BY_NAME, GgufWeight
+from .runtime import GpuContext
+
+ALGOS = {"auto": _lib.ALGO_AUTO, "naive": _lib.ALGO_NAIVE, "stream": _lib.ALGO_STREAM, "tcgen05": _lib.ALGO_TCGEN05}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", choices=["w8a8", "gguf", "quant"], default="w8a8")
+    ap.add_argument("--algo", choices=list(ALGOS), default="auto")
+    ap.add_argument("--kind", choices=list(TYPE_BY_NAME), default="q4_0")
+    ap.add_argument("--m", type=int, default=16)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--copies", type=int, default=1, help="rotate over this many copies of the weights")
+    ap.add_argument("--ng", type=int, default=0)
+    ap.add_argument("--bn", type=int, default=0)
+    a = ap.parse_args()
+
+    gpu = GpuContext(0)
+    lib = gpu.lib
+    lib.pg_tune_stream_ng(a.ng)
+    lib.pg_tune_tcgen05_bn(a.bn)
+    g = np.random.Generator(np.random.PCG64(1))
+    m, k, n = a.m, a.k, a.n
+    x = g.standard_normal((m, k), dtype=np.float32)
+    d_x = gpu.upload(x.reshape(-1))
+
+    if a.op == "quant":
+        d_q, d_s = gpu.alloc(m * k + 16, np.int8), gpu.alloc(m, np.float32)
+        call = lambda i: _lib.check(lib.pg_quantize_activations(gpu.handle, d_x.ptr, m, k, d_q.ptr, d_s.ptr))
+        nbytes = 5 * m * k + 4 * m
+    elif a.op == "gguf":
+        bs = BLOCK_BYTES[TYPE_BY_NAME[a.kind]]
+        raw = g.integers(0, 256, n * (k // 32) * bs, dtype=np.uint8)
+        blocks = raw.reshape(-1, bs)
+        blocks[:, 0:2] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)   # a sane f16 scale
+        if a.kind == "q4_1":
+            blocks[:, 2:4] = np.frombuffer(np.float16(-0.08).tobytes(), np.uint8)
+        ws = [GgufWeight(a.kind, raw, n, k, gpu) for _ in range(a.copies)]
+        d_y = gpu.alloc(m * n, np.float32)
+        call = lambda i: ws[i % a.copies].matmul_device(d_x.ptr, m, d_y.ptr)
+        nbytes = n * (k // 32) * bs + 4 * m * k + 4 * m * n
+    else:
+        hs, keep = [], []
+        for _ in range(a.copies):
+            wt = g.integers(-127, 128, n * k, dtype=np.int8)
+            d_w = gpu.alloc(n * k + 1024, np.int8)
+            _lib.check(lib.pg_mem_upload(gpu.handle, d_w.ptr, wt.ctypes.data, n * k))
+            gpu.sync()
+            d_ws = gpu.upload(np.full(n, 1e-3, np.float32))
+            h = C.c_void_p()
+            _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, d_w.ptr, d_ws.ptr, k, n, C.byref(h)))
+            hs.append(h)
+            keep += [d_w, d_ws]
+        d_q, d_s, d_y = gpu.alloc(m * k + 16, np.int8), gpu.alloc(m, np.float32), gpu.alloc(m * n, np.float32)
+        _lib.check(lib.pg_quantize_activations(gpu.handle, d_x.ptr, m, k, d_q.ptr, d_s.ptr))
+        call = lambda i: _lib.check(lib.pg_gemm_i8(gpu.handle, d_q.ptr, d_s.ptr, m, k, hs[i % a.copies], d_y.ptr, None, ALGOS[a.algo]))
+        nbytes = m * k + 4 * m + k * n + 4 * n + 4 * m * n
+
+    call(0)
+    gpu.sync()
+    t0 = time.perf_counter()
+    for i in range(a.reps):
+        call(i + 1)
+    gpu.sync()
+    us = (time.perf_counter() - t0) / a.reps * 1e6
+    status = gpu.device_status()
+    ops = 2.0 * m * n * k
+    print(f"op={a.op} algo={a.algo} m={m} k={k} n={n}: {us:.1f} us/call, {nbytes / us / 1e3:.1f} GB/s algorithmic, "
+          f"{ops / us / 1e6:.1f} TOPS, device_status={status}")
+    if status != 0:
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    main()

@@ -102,6 +102,10 @@ class GpuContext:
         _lib.check(self.lib.pg_ctx_device_status(self.handle, C.byref(v)))
         return v.value
 
+    # batched submission (CUDA graph): `with gpu.record() as g: ...` then `g.launch()`
+    def record(self) -> "Graph":
+        return Graph(self)
+
     def close(self) -> None:
         if self.handle:
             self.lib.pg_ctx_destroy(self.handle)
@@ -112,6 +116,38 @@ class GpuContext:
             self.close()
         except Exception:
             pass
+
+
+class Graph:
+    """Records the calls made on a context inside the `with` block and replays them with one
+    submission (`launch`).  Run the calls once before recording so that scratch memory is sized."""
+
+    def __init__(self, ctx: GpuContext):
+        self.ctx = ctx
+        self.handle = None
+        self.kernels = 0
+
+    def __enter__(self):
+        self._n0 = self.ctx.lib.pg_launch_count()
+        _lib.check(self.ctx.lib.pg_graph_begin(self.ctx.handle))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        h = C.c_void_p()
+        rc = self.ctx.lib.pg_graph_end(self.ctx.handle, C.byref(h))
+        if exc_type is None:
+            _lib.check(rc)
+            self.handle = h
+            self.kernels = int(self.ctx.lib.pg_launch_count() - self._n0)
+        return False
+
+    def launch(self) -> None:
+        _lib.check(self.ctx.lib.pg_graph_launch(self.ctx.handle, self.handle))
+
+    def free(self) -> None:
+        if self.handle is not None and self.ctx.handle:
+            self.ctx.lib.pg_graph_free(self.ctx.handle, self.handle)
+        self.handle = None
 
 
 _tls = threading.local()
