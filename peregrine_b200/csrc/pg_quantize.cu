@@ -37,6 +37,10 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
                                                                     int8_t *__restrict__ q, float *__restrict__ scales)
 {
     __shared__ float red[32];
+    // x comes from the preceding kernel; once this grid runs, the one after it may start its own
+    // independent prologue (the product kernel prefetches weights)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t row = blockIdx.x;
     const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols);
     const int64_t nvec = cols >> 2;
@@ -179,10 +183,20 @@ int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, in
         quantize_rows_scalar_kernel<<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, 0, d_q, d_scales);
     } else if (!vec) {
         quantize_rows_scalar_kernel<<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
-    } else if (cols <= 4 * QR_THREADS * 4) {
-        quantize_rows_kernel<4><<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
     } else {
-        quantize_rows_kernel<16><<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)rows);
+        cfg.blockDim = dim3(QR_THREADS);
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cols <= 4 * QR_THREADS * 4)
+            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<4>, d_x, cols, d_q, d_scales));
+        else
+            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<16>, d_x, cols, d_q, d_scales));
     }
     PG_LAUNCHED();
     return PG_OK;

@@ -239,6 +239,22 @@ def test_stream_every_column_group(pg, gpu, oracle_mt, ng):
         gpu.lib.pg_tune_stream_ng(0)
 
 
+@pytest.mark.parametrize("split", [1, 2, 4])
+@pytest.mark.parametrize("depth", [4, 8])
+def test_stream_cluster_split_and_fifo_depth(pg, gpu, oracle_mt, split, depth):
+    """K split over a thread-block cluster (partial sums through distributed shared memory) and
+    both FIFO depths, on shapes whose K does not divide evenly."""
+    gpu.lib.pg_tune_stream_split(split)
+    gpu.lib.pg_tune_stream_depth(depth)
+    try:
+        for m, k, n in ((1, 4096, 520), (16, 14336, 72), (7, 1040, 33), (33, 2064, 40), (64, 192, 9)):
+            x, w = linear_inputs(m, k, n, 700 + split + depth + m)
+            _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["stream"])
+    finally:
+        gpu.lib.pg_tune_stream_split(0)
+        gpu.lib.pg_tune_stream_depth(0)
+
+
 def test_unaligned_k_uses_the_checker_kernel(pg, gpu, oracle):
     """K not a multiple of 16: neither fast kernel takes it; the result is still exact."""
     for m, k, n in ((3, 17, 5), (20, 1001, 33), (70, 250, 19)):
