@@ -25,6 +25,7 @@ SOURCES = [
     "pg_gemv_w8a8.cu",
     "pg_gemm_tcgen05.cu",
     "pg_gguf.cu",
+    "pg_gguf_mma.cu",
 ]
 
 NVCC_FLAGS = [

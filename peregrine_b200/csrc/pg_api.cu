@@ -35,6 +35,21 @@ int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes)
     return PG_OK;
 }
 
+int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->staging_bytes) return PG_OK;
+    if (ctx->capturing) PG_FAIL(PG_ERR_INVALID, "staging memory would have to grow while a graph is being recorded");
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->staging) PG_CUDA(cudaFree(ctx->staging));
+    ctx->staging = nullptr;
+    ctx->staging_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    want = (want + 255) & ~(size_t)255;
+    PG_CUDA(cudaMalloc(&ctx->staging, want));
+    ctx->staging_bytes = want;
+    return PG_OK;
+}
+
 int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes)
 {
     if (bytes <= ctx->h_pinned_bytes) return PG_OK;
@@ -127,6 +142,7 @@ int32_t pg_ctx_destroy(pg_ctx *ctx)
     DeviceGuard guard(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->staging) cudaFree(ctx->staging);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -259,9 +275,9 @@ int32_t pg_quantize_activations_host(pg_ctx *ctx, const float *x, int64_t rows, 
     if (rows == 0) return PG_OK;
     PG_REQUIRE(scales && (cols == 0 || (x && q)), "quantize_activations: null pointer");
     const size_t nx = align256((size_t)rows * cols * 4), nq = align256((size_t)rows * cols), ns = align256((size_t)rows * 4);
-    int32_t rc = pg_scratch_reserve(ctx, nx + nq + ns);
+    int32_t rc = pg_staging_reserve(ctx, nx + nq + ns);
     if (rc) return rc;
-    char *base = (char *)ctx->scratch;
+    char *base = (char *)ctx->staging;
     float *d_x = (float *)base;
     int8_t *d_q = (int8_t *)(base + nx);
     float *d_s = (float *)(base + nx + nq);
@@ -557,9 +573,9 @@ int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t
     PG_REQUIRE((m * k == 0 || x) && y, "matmul_quantized: null pointer");
     const size_t nx = align256((size_t)m * k * 4 + 16), ny = align256((size_t)m * n * 4), nq = align256((size_t)m * k + 16),
                  ns = align256((size_t)m * 4);
-    int32_t rc = pg_scratch_reserve(ctx, nx + ny + nq + ns);
+    int32_t rc = pg_staging_reserve(ctx, nx + ny + nq + ns);
     if (rc) return rc;
-    char *base = (char *)ctx->scratch;
+    char *base = (char *)ctx->staging;
     float *d_x = (float *)base;
     float *d_y = (float *)(base + nx);
     int8_t *d_q = (int8_t *)(base + nx + ny);
@@ -698,10 +714,10 @@ int32_t pg_matmul_gguf_host(pg_ctx *ctx, const float *x, int64_t m, const pg_ggu
     if (m * w->n == 0) return PG_OK;
     PG_REQUIRE(y && (w->k == 0 || x), "matmul_gguf: null pointer");
     const size_t nx = align256((size_t)m * w->k * 4 + 16), ny = align256((size_t)m * w->n * 4);
-    int32_t rc = pg_scratch_reserve(ctx, nx + ny);
+    int32_t rc = pg_staging_reserve(ctx, nx + ny);
     if (rc) return rc;
-    float *d_x = (float *)ctx->scratch;
-    float *d_y = (float *)((char *)ctx->scratch + nx);
+    float *d_x = (float *)ctx->staging;
+    float *d_y = (float *)((char *)ctx->staging + nx);
     if (m * w->k) PG_CUDA(cudaMemcpyAsync(d_x, x, (size_t)m * w->k * 4, cudaMemcpyHostToDevice, ctx->stream));
     rc = pgk_matmul_gguf(ctx, d_x, m, w, d_y);
     if (rc) return rc;

@@ -1,0 +1,376 @@
+// Dequantising product y = x . dequant(W)^T for GGUF Q4_0 / Q8_0 weights, decode sizes, on the
+// tensor cores.  It replaces, without ever writing the f32 weight, what the reference does in three
+// passes: gguf::dequant_q4_0 / dequant_q8_0 (src/gguf.rs:286-326), the transposition of
+// load_transposed_weight (src/models/llama/model.rs:243-257) and Tensor::matmul
+// (src/tensor.rs:1342-1354).
+//
+// Why tensor cores for a bandwidth-bound op: with f32 activations a CUDA-core kernel needs one
+// FMA per weight and activation row plus the nibble->float conversions, which caps it far below
+// the HBM rate already at M = 8.  Here
+//   * the quants go to the MMA as exact fp16 integers, built with two logic ops per pair from the
+//     packed nibbles/bytes (exponent-bias trick: 0x6400 | u is the half 1024 + u);
+//   * each f32 activation is split into two fp16 parts, x * 2^s = hi + lo * 2^-11 (s a per-row
+//     power of two that brings the row into [-16,16)), which keeps 22 significant bits; every
+//     product quant x part is exact and the sums accumulate in f32 inside the MMA;
+//   * per 32-element block the two partial sums are combined and multiplied by the block's f16
+//     scale: y += d * (sum_hi + sum_lo * 2^-11), in f32.
+// The result differs from the reference's strictly sequential f32 loop only in summation order
+// (documented tolerance: 1e-5 of max|y|; measured about 1e-7).
+//
+// Data flow, per CTA of 16 warps (one CTA per SM, persistent over tiles of 16*R weight rows):
+//   * warp w owns a fixed slice of eight 32-element blocks of K and keeps the activation
+//     fragments of that slice in registers for the whole kernel, so activations cost no memory
+//     traffic in the main loop whatever M is;
+//   * the quants and block scales of tile after tile stream through a per-lane cp.async FIFO in
+//     shared memory (128-bit copies, L2 only), several entries deep, so HBM requests stay in flight
+//     across tile boundaries;
+//   * per tile the 16 warps' partial sums meet in shared memory (fixed order: deterministic).
+// K longer than 128 blocks is handled by one launch per 4096-element chunk, accumulating into y.
+#include <cuda_fp16.h>
+
+#include "pg_internal.cuh"
+
+namespace {
+
+constexpr int G_WARPS = 16;
+constexpr int G_THREADS = G_WARPS * 32;
+constexpr int G_SLICE = 8;                      // blocks of K per warp
+constexpr int G_CHUNK = G_WARPS * G_SLICE;      // 128 blocks = 4096 elements per launch
+// One FIFO entry of a warp: quants of rows g and g+8 for the eight lane groups, 64 B each padded to
+// 80 B so that the groups fall into distinct banks, then 16 B of block scales per lane.
+constexpr int G_QAREA = 2 * 8 * 80;
+constexpr int G_WSLOT = G_QAREA + 32 * 16;      // 1792 B per warp and entry
+constexpr int G_SLOT_BYTES = G_WARPS * G_WSLOT;  // one entry for the whole CTA
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t n)
+{
+    asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src, uint32_t n)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t n)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t mask, uint32_t magic)
+{
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(magic));  // (a & mask) | magic
+    return d;
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- activation fragments -------------------------------------------------------------------
+// One CTA per activation row of the 8-row tile (rows past M are written as zeros).  Output, per
+// 32-element block b and part p (0 = hi, 1 = lo): 32 lanes x 16 bytes, lane = (row % 8) * 4 + t
+// holding the eight elements 8t..8t+7 of the block in the order the weight unpacking produces them:
+//   Q8_0: e0 e1 e2 e3 e4 e5 e6 e7
+//   Q4_0: e0 e4 e1' e5' e2 e6 e3' e7'   (' = divided by 16: the high nibbles are unpacked as 16*q)
+// row_scale[m] = 2^-s undoes the per-row power-of-two scaling.
+template <int TYPE>
+__global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restrict__ x, int M, int K, int m0, uint4 *__restrict__ xs,
+                                                           float *__restrict__ row_scale)
+{
+    __shared__ float red[32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int g = blockIdx.x;  // row inside the tile
+    const int m = m0 + g;
+    const int nblk = K >> 5;
+    const bool live = m < M;
+    const float *xr = x + (int64_t)(live ? m : 0) * K;
+    float amax = 0.0f;
+    if (live)
+        for (int i = threadIdx.x; i < K; i += 256) amax = fmaxf(amax, fabsf(xr[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < 8; wv++) amax = fmaxf(amax, red[wv]);  // every thread needs the row maximum
+    int e = 0;
+    if (amax > 0.0f && amax < INFINITY) e = max(-100, min(100, ilogbf(amax)));
+    const float s = scalbnf(1.0f, 3 - e);  // |x| * s < 16
+    if (threadIdx.x == 0 && live) row_scale[g] = scalbnf(1.0f, e - 3);
+    for (int i = threadIdx.x; i < nblk * 4; i += 256) {
+        const int b = i >> 2, t = i & 3;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = live ? xr[b * 32 + t * 8 + j] * s : 0.0f;
+        float o[8];
+        if (TYPE == PG_GGUF_Q4_0) {
+            const float h = 0.0625f;
+            o[0] = v[0]; o[1] = v[4]; o[2] = v[1] * h; o[3] = v[5] * h;
+            o[4] = v[2]; o[5] = v[6]; o[6] = v[3] * h; o[7] = v[7] * h;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) o[j] = v[j];
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half h0 = __float2half_rn(o[2 * j]), h1 = __float2half_rn(o[2 * j + 1]);
+            const __half l0 = __float2half_rn((o[2 * j] - __half2float(h0)) * 2048.0f);
+            const __half l1 = __float2half_rn((o[2 * j + 1] - __half2float(h1)) * 2048.0f);
+            hi[j] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+            lo[j] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+        }
+        const int lane = g * 4 + t;
+        xs[((int64_t)b * 2 + 0) * 32 + lane] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        xs[((int64_t)b * 2 + 1) * 32 + lane] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+// ---- the product -----------------------------------------------------------------------------
+// BPS = blocks per 64-byte step of a row's quants: 4 for Q4_0 (16 B per block), 2 for Q8_0 (32 B).
+template <int TYPE, int R, int D>
+__global__ void __launch_bounds__(G_THREADS, 1)
+    gguf_mma_kernel(const uint4 *__restrict__ xs, const float *__restrict__ row_scale, const uint8_t *__restrict__ qs,
+                    const uint16_t *__restrict__ dd, int64_t N, int nblk_row, int blk0, int nblk_chunk, int M, int m0,
+                    float *__restrict__ y, int accumulate)
+{
+    constexpr int BPS = (TYPE == PG_GGUF_Q4_0) ? 4 : 2;
+    constexpr int STEPS = G_SLICE / BPS;          // steps per warp per row group
+    constexpr int QB = (TYPE == PG_GGUF_Q4_0) ? 16 : 32;  // bytes of quants per block
+    constexpr int TROWS = 16 * R;
+    extern __shared__ uint4 smem_g[];
+    // [D] entries of G_SLOT_BYTES, then float red[2][WARPS][R][8][16]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t wbase = (uint32_t)__cvta_generic_to_shared(smem_g) + warp * G_WSLOT;
+    float *red = reinterpret_cast<float *>(reinterpret_cast<char *>(smem_g) + (size_t)D * G_SLOT_BYTES);
+    const int wblk = warp * G_SLICE;              // first block of this warp's slice inside the chunk
+    const int64_t tiles = (N + TROWS - 1) / TROWS;
+    const int my_tiles = (tiles > blockIdx.x) ? (int)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+
+    // Issue side of the FIFO: walks (tile, step, row group) in the order the consumer does and copies
+    // the quants and block scales of rows g and g+8 of the group.
+    int i_tile = 0, i_step = 0, i_rg = 0, i_slot = 0;
+    auto issue = [&]() {
+        const int64_t tile = blockIdx.x + (int64_t)i_tile * gridDim.x;
+        const int b = wblk + i_step * BPS;        // first block of the step inside the chunk
+        const bool kok = (i_tile < my_tiles) && (b < nblk_chunk);
+        const uint32_t slot = wbase + (uint32_t)i_slot * G_SLOT_BYTES;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            int64_t row = tile * TROWS + i_rg * 16 + g + h * 8;
+            const bool ok = kok && (row < N);
+            row = ok ? row : 0;
+            const int64_t blk = row * nblk_row + blk0 + (ok ? b : 0);
+            // lane t copies 16 of the step's 64 quant bytes; the four lanes of a group share them
+            cp_async16(slot + (h * 8 + g) * 80 + t * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
+            if (TYPE == PG_GGUF_Q4_0)
+                cp_async8(slot + G_QAREA + lane * 16 + h * 8, dd + blk, ok ? 8u : 0u);
+            else
+                cp_async4(slot + G_QAREA + lane * 16 + h * 8, dd + blk, ok ? 4u : 0u);
+        }
+        cp_commit();
+        if (++i_slot == D) i_slot = 0;
+        if (++i_rg == R) {
+            i_rg = 0;
+            if (++i_step == STEPS) {
+                i_step = 0;
+                ++i_tile;
+            }
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < D - 1; i++) issue();
+
+    // the activation fragments come from the preceding kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    uint4 xh[G_SLICE], xl[G_SLICE];
+#pragma unroll
+    for (int j = 0; j < G_SLICE; j++) {
+        const int b = wblk + j;
+        if (b < nblk_chunk) {
+            xh[j] = __ldg(xs + ((int64_t)(blk0 + b) * 2 + 0) * 32 + lane);
+            xl[j] = __ldg(xs + ((int64_t)(blk0 + b) * 2 + 1) * 32 + lane);
+        } else {
+            xh[j] = xl[j] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    int c_slot = 0;
+    for (int ti = 0; ti < my_tiles; ti++) {
+        float acc[R][4];
+#pragma unroll
+        for (int rg = 0; rg < R; rg++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[rg][i] = 0.0f;
+#pragma unroll
+        for (int step = 0; step < STEPS; step++) {
+#pragma unroll
+            for (int rg = 0; rg < R; rg++) {
+                issue();
+                cp_wait<D - 1>();
+                __syncwarp();  // the group's lanes read each other's copies
+                const uint32_t slot = wbase + (uint32_t)c_slot * G_SLOT_BYTES;
+                if (++c_slot == D) c_slot = 0;
+                // block scales of rows g and g+8 (each lane copied the same ones; read our own)
+                const uint2 sc0 = lds64(slot + G_QAREA + lane * 16), sc1 = lds64(slot + G_QAREA + lane * 16 + 8);
+                const uint32_t q0 = slot + g * 80, q1 = slot + (8 + g) * 80;  // quants of rows g and g+8
+#pragma unroll
+                for (int bi = 0; bi < BPS; bi++) {
+                    const int j = step * BPS + bi;  // block inside the warp's slice
+                    uint32_t a[2][4];               // [row half][pair]
+                    if (TYPE == PG_GGUF_Q4_0) {
+                        // block bi was copied by lane (g, bi): its word t holds our eight nibbles
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const uint32_t w = lds32((h ? q1 : q0) + bi * 16 + t * 4);
+                            const uint32_t w8 = w >> 8;
+                            a[h][0] = sub_f16x2(lop_and_or(w, 0x000F000Fu, 0x64006400u), 0x64086408u);   // q
+                            a[h][1] = sub_f16x2(lop_and_or(w, 0x00F000F0u, 0x64006400u), 0x64806480u);   // 16 q
+                            a[h][2] = sub_f16x2(lop_and_or(w8, 0x000F000Fu, 0x64006400u), 0x64086408u);
+                            a[h][3] = sub_f16x2(lop_and_or(w8, 0x00F000F0u, 0x64006400u), 0x64806480u);
+                        }
+                    } else {
+                        // block bi spans the copies of lanes (g, 2bi) and (g, 2bi+1); our 8 bytes are in lane (g, 2bi + t/2)
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const uint2 w = lds64((h ? q1 : q0) + bi * 32 + t * 8);
+                            const uint32_t u0 = w.x ^ 0x80808080u, u1 = w.y ^ 0x80808080u;  // q + 128 as unsigned bytes
+                            a[h][0] = sub_f16x2(__byte_perm(u0, 0x64646464u, 0x4140), 0x64806480u);
+                            a[h][1] = sub_f16x2(__byte_perm(u0, 0x64646464u, 0x4342), 0x64806480u);
+                            a[h][2] = sub_f16x2(__byte_perm(u1, 0x64646464u, 0x4140), 0x64806480u);
+                            a[h][3] = sub_f16x2(__byte_perm(u1, 0x64646464u, 0x4342), 0x64806480u);
+                        }
+                    }
+                    float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_f16(ch, a[0][0], a[1][0], a[0][1], a[1][1], xh[j].x, xh[j].y);
+                    mma_f16(ch, a[0][2], a[1][2], a[0][3], a[1][3], xh[j].z, xh[j].w);
+                    mma_f16(cl, a[0][0], a[1][0], a[0][1], a[1][1], xl[j].x, xl[j].y);
+                    mma_f16(cl, a[0][2], a[1][2], a[0][3], a[1][3], xl[j].z, xl[j].w);
+                    // scale of block bi for the two rows
+                    const uint32_t p0 = (bi < 2) ? sc0.x : sc0.y, p1 = (bi < 2) ? sc1.x : sc1.y;
+                    const float d0 = __half2float(__ushort_as_half((unsigned short)((bi & 1) ? (p0 >> 16) : (p0 & 0xffff))));
+                    const float d1 = __half2float(__ushort_as_half((unsigned short)((bi & 1) ? (p1 >> 16) : (p1 & 0xffff))));
+                    const float k = 1.0f / 2048.0f;
+                    acc[rg][0] = fmaf(d0, fmaf(cl[0], k, ch[0]), acc[rg][0]);
+                    acc[rg][1] = fmaf(d0, fmaf(cl[1], k, ch[1]), acc[rg][1]);
+                    acc[rg][2] = fmaf(d1, fmaf(cl[2], k, ch[2]), acc[rg][2]);
+                    acc[rg][3] = fmaf(d1, fmaf(cl[3], k, ch[3]), acc[rg][3]);
+                }
+                __syncwarp();  // all reads of this entry are done before any lane's next copy reuses it
+            }
+        }
+        // partial sums of this warp's K slice -> shared memory, [buf][warp][rg][m 0..7][row 0..15]
+        float *mine = red + ((size_t)(ti & 1) * G_WARPS + warp) * (R * 128);
+#pragma unroll
+        for (int rg = 0; rg < R; rg++) {
+            mine[rg * 128 + (2 * t) * 16 + g] = acc[rg][0];
+            mine[rg * 128 + (2 * t + 1) * 16 + g] = acc[rg][1];
+            mine[rg * 128 + (2 * t) * 16 + g + 8] = acc[rg][2];
+            mine[rg * 128 + (2 * t + 1) * 16 + g + 8] = acc[rg][3];
+        }
+        __syncthreads();
+        const int64_t tile = blockIdx.x + (int64_t)ti * gridDim.x;
+        for (int idx = threadIdx.x; idx < 8 * TROWS; idx += G_THREADS) {
+            const int mm = idx / TROWS, nn = idx - mm * TROWS;     // consecutive threads -> consecutive n
+            const int rg = nn >> 4, row = nn & 15;
+            const int64_t n = tile * TROWS + nn;
+            if (m0 + mm >= M || n >= N) continue;
+            const float *src = red + (size_t)(ti & 1) * G_WARPS * (R * 128) + rg * 128 + mm * 16 + row;
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < G_WARPS; w++) sum += src[(size_t)w * (R * 128)];
+            sum *= row_scale[mm];
+            float *dst = y + (int64_t)(m0 + mm) * N + n;
+            *dst = accumulate ? (*dst + sum) : sum;
+        }
+    }
+    cp_wait<0>();
+}
+
+template <int TYPE>
+int32_t run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
+{
+    constexpr int R = 2, D = 6;
+    const int K = (int)w->k, nblk = K / 32, M = (int)m;
+    // scratch: activation fragments of one 8-row tile (nblk * 2 parts * 512 B) + 8 row scales
+    const size_t xs_bytes = (size_t)nblk * 2 * 32 * sizeof(uint4);
+    int32_t rc = pg_scratch_reserve(ctx, xs_bytes + 256);
+    if (rc) return rc;
+    uint4 *xs = reinterpret_cast<uint4 *>(ctx->scratch);
+    float *row_scale = reinterpret_cast<float *>(reinterpret_cast<char *>(ctx->scratch) + xs_bytes);
+    const size_t smem = (size_t)D * G_SLOT_BYTES + 2 * G_WARPS * R * 128 * sizeof(float);
+    auto kern = gguf_mma_kernel<TYPE, R, D>;
+    PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int64_t tiles = (w->n + 16 * R - 1) / (16 * R);
+    const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        cudaLaunchConfig_t pc = {};
+        pc.gridDim = dim3(8);
+        pc.blockDim = dim3(256);
+        pc.stream = ctx->stream;
+        pc.attrs = attr;
+        pc.numAttrs = 1;
+        PG_CUDA(cudaLaunchKernelEx(&pc, gguf_prep_x_kernel<TYPE>, d_x, M, K, m0, xs, row_scale));
+        PG_LAUNCHED();
+        for (int blk0 = 0; blk0 < nblk; blk0 += G_CHUNK) {
+            const int chunk = (nblk - blk0 < G_CHUNK) ? (nblk - blk0) : G_CHUNK;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(grid);
+            cfg.blockDim = dim3(G_THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = ctx->stream;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            PG_CUDA(cudaLaunchKernelEx(&cfg, kern, (const uint4 *)xs, (const float *)row_scale, (const uint8_t *)w->d_qs,
+                                       (const uint16_t *)w->d_d, w->n, nblk, blk0, chunk, M, m0, d_y, blk0 > 0 ? 1 : 0));
+            PG_LAUNCHED();
+        }
+    }
+    return PG_OK;
+}
+
+}  // namespace
+
+bool pgk_matmul_gguf_mma_supports(const pg_gguf_weight *w, int64_t m)
+{
+    return (w->type == PG_GGUF_Q4_0 || w->type == PG_GGUF_Q8_0) && w->k >= 128 && (w->k % 128 == 0) && m >= 1 && m <= 64 && w->n >= 1;
+}
+
+int32_t pgk_matmul_gguf_mma(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
+{
+    if (w->type == PG_GGUF_Q4_0) return run<PG_GGUF_Q4_0>(ctx, d_x, m, w, d_y);
+    return run<PG_GGUF_Q8_0>(ctx, d_x, m, w, d_y);
+}

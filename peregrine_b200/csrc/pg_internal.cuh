@@ -49,6 +49,10 @@ struct pg_ctx {
     // scratch for intermediates (quantised activations, split-K partial sums); grows on demand
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    // device copies of host arguments for the *_host entry points; separate from `scratch`, which
+    // kernels launched inside those calls may resize or overwrite
+    void *staging = nullptr;
+    size_t staging_bytes = 0;
     int32_t *d_status = nullptr;  // device status word for bounded waits
     void *h_pinned = nullptr;     // pinned staging for *_host calls
     size_t h_pinned_bytes = 0;
@@ -85,6 +89,7 @@ struct pg_gguf_weight {
 
 int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes);
+int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes);
 
 // ------------------------------------------------------- kernel launchers ----
 // pg_quantize.cu
@@ -108,6 +113,9 @@ int32_t pgk_dequant_blocks(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int6
 int32_t pgk_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float *d_out);
 int32_t pgk_gguf_repack(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t n, int64_t k, pg_gguf_weight *w);
 int32_t pgk_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
+// pg_gguf_mma.cu
+bool pgk_matmul_gguf_mma_supports(const pg_gguf_weight *w, int64_t m);
+int32_t pgk_matmul_gguf_mma(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
 
 // ------------------------------------------------------- device helpers ----
 // Rust `(v.round().clamp(-127.0, 127.0)) as i8`: roundf is half away from zero; the

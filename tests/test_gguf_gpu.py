@@ -120,6 +120,32 @@ def test_matmul_gguf_config(pg, gpu, oracle_mt, kind, m):
     _check_matmul(pg, gpu, oracle_mt, kind, 14336, 4096, m, 3000)
 
 
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+def test_matmul_gguf_cuda_core_path(pg, gpu, oracle_mt, kind):
+    """The CUDA-core kernel (used for Q4_1 and for K not a multiple of 128) on shapes the tensor-core
+    kernel would otherwise take."""
+    gpu.lib.pg_tune_gguf_simple(1)
+    try:
+        _check_matmul(pg, gpu, oracle_mt, kind, 200, 1024, 5, 3100)
+    finally:
+        gpu.lib.pg_tune_gguf_simple(0)
+
+
+@pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("m,n,k", [(1, 33, 128), (9, 40, 384), (17, 100, 4096 + 128), (2, 4096, 14336)])
+def test_matmul_gguf_tensor_core_path_edges(pg, gpu, oracle_mt, kind, m, n, k):
+    """More than eight activation rows (two passes), K longer than one 4096-element chunk
+    (accumulating launches), ragged N, outlier activations."""
+    g = rng(3200 + m + n)
+    w = normal(g, (n, k), 0.02)
+    x = normal(g, (m, k))
+    x[:, g.choice(k, size=max(1, k // 100), replace=False)] *= np.float32(20.0)
+    raw = oracle_mt.encode(kind, w)
+    ref = oracle_mt.gguf_matmul(x, m, k, raw, kind, n)
+    y = pg.gguf.GgufWeight(kind, raw, n, k, gpu).matmul(x, m)
+    assert np.abs(y - ref).max() <= REL_TOL * np.abs(ref).max()
+
+
 def test_matmul_gguf_row_shard_and_errors(pg, gpu, oracle_mt):
     g = rng(7)
     n, k, m = 96, 256, 4
