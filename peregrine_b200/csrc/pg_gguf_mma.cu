@@ -37,9 +37,10 @@ constexpr int G_THREADS = G_WARPS * 32;
 constexpr int G_SLICE = 8;                      // blocks of K per warp
 constexpr int G_CHUNK = G_WARPS * G_SLICE;      // 128 blocks = 4096 elements per launch
 // One FIFO entry of a warp: quants of rows g and g+8 for the eight lane groups, 64 B each padded to
-// 80 B so that the groups fall into distinct banks, then 16 B of block scales per lane.
+// 80 B so that the groups fall into distinct banks; then, filled only by the first step of a row
+// group, the 16 B of block scales (eight f16) of each of the 16 rows.
 constexpr int G_QAREA = 2 * 8 * 80;
-constexpr int G_WSLOT = G_QAREA + 32 * 16;      // 1792 B per warp and entry
+constexpr int G_WSLOT = G_QAREA + 16 * 16;      // 1536 B per warp and entry
 constexpr int G_SLOT_BYTES = G_WARPS * G_WSLOT;  // one entry for the whole CTA
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t n)
@@ -70,6 +71,12 @@ __device__ __forceinline__ uint2 lds64(uint32_t a)
 {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
 __device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b)
@@ -176,8 +183,9 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     const int64_t tiles = (N + TROWS - 1) / TROWS;
     const int my_tiles = (tiles > blockIdx.x) ? (int)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
 
-    // Issue side of the FIFO: walks (tile, step, row group) in the order the consumer does and copies
-    // the quants and block scales of rows g and g+8 of the group.
+    // Issue side of the FIFO: walks (tile, row group, step) in the order the consumer does and copies
+    // the quants of rows g and g+8 of the group; the first step of a row group also brings the block
+    // scales of the warp's whole K slice for those rows (lanes t = 0, 1 copy them for g and g+8).
     int i_tile = 0, i_step = 0, i_rg = 0, i_slot = 0;
     auto issue = [&]() {
         const int64_t tile = blockIdx.x + (int64_t)i_tile * gridDim.x;
@@ -192,17 +200,14 @@ __global__ void __launch_bounds__(G_THREADS, 1)
             const int64_t blk = row * nblk_row + blk0 + (ok ? b : 0);
             // lane t copies 16 of the step's 64 quant bytes; the four lanes of a group share them
             cp_async16(slot + (h * 8 + g) * 80 + t * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
-            if (TYPE == PG_GGUF_Q4_0)
-                cp_async8(slot + G_QAREA + lane * 16 + h * 8, dd + blk, ok ? 8u : 0u);
-            else
-                cp_async4(slot + G_QAREA + lane * 16 + h * 8, dd + blk, ok ? 4u : 0u);
+            if (i_step == 0 && t == h) cp_async16(slot + G_QAREA + (h * 8 + g) * 16, dd + blk, ok ? 16u : 0u);
         }
         cp_commit();
         if (++i_slot == D) i_slot = 0;
-        if (++i_rg == R) {
-            i_rg = 0;
-            if (++i_step == STEPS) {
-                i_step = 0;
+        if (++i_step == STEPS) {
+            i_step = 0;
+            if (++i_rg == R) {
+                i_rg = 0;
                 ++i_tile;
             }
         }
@@ -227,22 +232,22 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     }
     int c_slot = 0;
     for (int ti = 0; ti < my_tiles; ti++) {
-        float acc[R][4];
+        float *mine = red + ((size_t)(ti & 1) * G_WARPS + warp) * (R * 128);
 #pragma unroll
-        for (int rg = 0; rg < R; rg++)
+        for (int rg = 0; rg < R; rg++) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            uint4 sc0, sc1;  // eight f16 block scales of rows g and g+8 (this warp's K slice)
 #pragma unroll
-            for (int i = 0; i < 4; i++) acc[rg][i] = 0.0f;
-#pragma unroll
-        for (int step = 0; step < STEPS; step++) {
-#pragma unroll
-            for (int rg = 0; rg < R; rg++) {
+            for (int step = 0; step < STEPS; step++) {
                 issue();
                 cp_wait<D - 1>();
                 __syncwarp();  // the group's lanes read each other's copies
                 const uint32_t slot = wbase + (uint32_t)c_slot * G_SLOT_BYTES;
                 if (++c_slot == D) c_slot = 0;
-                // block scales of rows g and g+8 (each lane copied the same ones; read our own)
-                const uint2 sc0 = lds64(slot + G_QAREA + lane * 16), sc1 = lds64(slot + G_QAREA + lane * 16 + 8);
+                if (step == 0) {
+                    sc0 = lds128(slot + G_QAREA + g * 16);
+                    sc1 = lds128(slot + G_QAREA + (8 + g) * 16);
+                }
                 const uint32_t q0 = slot + g * 80, q1 = slot + (8 + g) * 80;  // quants of rows g and g+8
 #pragma unroll
                 for (int bi = 0; bi < BPS; bi++) {
@@ -260,7 +265,7 @@ __global__ void __launch_bounds__(G_THREADS, 1)
                             a[h][3] = sub_f16x2(lop_and_or(w8, 0x00F000F0u, 0x64006400u), 0x64806480u);
                         }
                     } else {
-                        // block bi spans the copies of lanes (g, 2bi) and (g, 2bi+1); our 8 bytes are in lane (g, 2bi + t/2)
+                        // the step's two blocks are contiguous in the group's 64 bytes; ours are bytes 8t..8t+7 of block bi
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
                             const uint2 w = lds64((h ? q1 : q0) + bi * 32 + t * 8);
@@ -276,27 +281,24 @@ __global__ void __launch_bounds__(G_THREADS, 1)
                     mma_f16(ch, a[0][2], a[1][2], a[0][3], a[1][3], xh[j].z, xh[j].w);
                     mma_f16(cl, a[0][0], a[1][0], a[0][1], a[1][1], xl[j].x, xl[j].y);
                     mma_f16(cl, a[0][2], a[1][2], a[0][3], a[1][3], xl[j].z, xl[j].w);
-                    // scale of block bi for the two rows
-                    const uint32_t p0 = (bi < 2) ? sc0.x : sc0.y, p1 = (bi < 2) ? sc1.x : sc1.y;
-                    const float d0 = __half2float(__ushort_as_half((unsigned short)((bi & 1) ? (p0 >> 16) : (p0 & 0xffff))));
-                    const float d1 = __half2float(__ushort_as_half((unsigned short)((bi & 1) ? (p1 >> 16) : (p1 & 0xffff))));
+                    // f16 scale of block j of the slice, rows g and g+8
+                    const uint32_t p0 = (j < 2) ? sc0.x : (j < 4) ? sc0.y : (j < 6) ? sc0.z : sc0.w;
+                    const uint32_t p1 = (j < 2) ? sc1.x : (j < 4) ? sc1.y : (j < 6) ? sc1.z : sc1.w;
+                    const float d0 = __half2float(__ushort_as_half((unsigned short)((j & 1) ? (p0 >> 16) : (p0 & 0xffff))));
+                    const float d1 = __half2float(__ushort_as_half((unsigned short)((j & 1) ? (p1 >> 16) : (p1 & 0xffff))));
                     const float k = 1.0f / 2048.0f;
-                    acc[rg][0] = fmaf(d0, fmaf(cl[0], k, ch[0]), acc[rg][0]);
-                    acc[rg][1] = fmaf(d0, fmaf(cl[1], k, ch[1]), acc[rg][1]);
-                    acc[rg][2] = fmaf(d1, fmaf(cl[2], k, ch[2]), acc[rg][2]);
-                    acc[rg][3] = fmaf(d1, fmaf(cl[3], k, ch[3]), acc[rg][3]);
+                    acc[0] = fmaf(d0, fmaf(cl[0], k, ch[0]), acc[0]);
+                    acc[1] = fmaf(d0, fmaf(cl[1], k, ch[1]), acc[1]);
+                    acc[2] = fmaf(d1, fmaf(cl[2], k, ch[2]), acc[2]);
+                    acc[3] = fmaf(d1, fmaf(cl[3], k, ch[3]), acc[3]);
                 }
                 __syncwarp();  // all reads of this entry are done before any lane's next copy reuses it
             }
-        }
-        // partial sums of this warp's K slice -> shared memory, [buf][warp][rg][m 0..7][row 0..15]
-        float *mine = red + ((size_t)(ti & 1) * G_WARPS + warp) * (R * 128);
-#pragma unroll
-        for (int rg = 0; rg < R; rg++) {
-            mine[rg * 128 + (2 * t) * 16 + g] = acc[rg][0];
-            mine[rg * 128 + (2 * t + 1) * 16 + g] = acc[rg][1];
-            mine[rg * 128 + (2 * t) * 16 + g + 8] = acc[rg][2];
-            mine[rg * 128 + (2 * t + 1) * 16 + g + 8] = acc[rg][3];
+            // partial sums of this warp's K slice -> shared memory, [buf][warp][rg][m 0..7][row 0..15]
+            mine[rg * 128 + (2 * t) * 16 + g] = acc[0];
+            mine[rg * 128 + (2 * t + 1) * 16 + g] = acc[1];
+            mine[rg * 128 + (2 * t) * 16 + g + 8] = acc[2];
+            mine[rg * 128 + (2 * t + 1) * 16 + g + 8] = acc[3];
         }
         __syncthreads();
         const int64_t tile = blockIdx.x + (int64_t)ti * gridDim.x;
@@ -317,10 +319,9 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     cp_wait<0>();
 }
 
-template <int TYPE>
+template <int TYPE, int R, int D>
 int32_t run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
 {
-    constexpr int R = 2, D = 6;
     const int K = (int)w->k, nblk = K / 32, M = (int)m;
     // scratch: activation fragments of one 8-row tile (nblk * 2 parts * 512 B) + 8 row scales
     const size_t xs_bytes = (size_t)nblk * 2 * 32 * sizeof(uint4);
@@ -364,13 +365,19 @@ int32_t run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, f
 
 }  // namespace
 
+static int g_gguf_rows = 0;  // tuning: row groups per tile, 0 = heuristic
+extern "C" PG_API void pg_tune_gguf_rows(int r) { g_gguf_rows = r; }
+
 bool pgk_matmul_gguf_mma_supports(const pg_gguf_weight *w, int64_t m)
 {
-    return (w->type == PG_GGUF_Q4_0 || w->type == PG_GGUF_Q8_0) && w->k >= 128 && (w->k % 128 == 0) && m >= 1 && m <= 64 && w->n >= 1;
+    return (w->type == PG_GGUF_Q4_0 || w->type == PG_GGUF_Q8_0) && w->k >= 256 && (w->k % 256 == 0) && m >= 1 && m <= 64 && w->n >= 1;
 }
 
 int32_t pgk_matmul_gguf_mma(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
 {
-    if (w->type == PG_GGUF_Q4_0) return run<PG_GGUF_Q4_0>(ctx, d_x, m, w, d_y);
-    return run<PG_GGUF_Q8_0>(ctx, d_x, m, w, d_y);
+    // One 16-row group per tile when that is what it takes to give every SM several tiles.
+    const bool fine = g_gguf_rows ? (g_gguf_rows == 1) : (w->n < 64ll * 32 * ctx->sm_count);
+    if (w->type == PG_GGUF_Q4_0)
+        return fine ? run<PG_GGUF_Q4_0, 1, 8>(ctx, d_x, m, w, d_y) : run<PG_GGUF_Q4_0, 2, 6>(ctx, d_x, m, w, d_y);
+    return fine ? run<PG_GGUF_Q8_0, 1, 8>(ctx, d_x, m, w, d_y) : run<PG_GGUF_Q8_0, 2, 6>(ctx, d_x, m, w, d_y);
 }

@@ -132,7 +132,7 @@ def test_matmul_gguf_cuda_core_path(pg, gpu, oracle_mt, kind):
 
 
 @pytest.mark.parametrize("kind", ["q4_0", "q8_0"])
-@pytest.mark.parametrize("m,n,k", [(1, 33, 128), (9, 40, 384), (17, 100, 4096 + 128), (2, 4096, 14336)])
+@pytest.mark.parametrize("m,n,k", [(1, 33, 256), (9, 40, 768), (17, 100, 4096 + 256), (2, 4096, 14336)])
 def test_matmul_gguf_tensor_core_path_edges(pg, gpu, oracle_mt, kind, m, n, k):
     """More than eight activation rows (two passes), K longer than one 4096-element chunk
     (accumulating launches), ragged N, outlier activations."""
