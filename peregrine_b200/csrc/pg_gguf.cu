@@ -77,7 +77,20 @@ __global__ void __launch_bounds__(256) f16_to_f32_kernel(const uint16_t *__restr
 }
 
 // raw [N][K/32][block] -> qs plane + scale planes.
-__global__ void __launch_bounds__(256) repack_kernel(int type, const uint8_t *__restrict__ raw, int64_t num_blocks,
+// With `interleave`, each 64-byte group of quants (4 Q4_0 blocks / 2 Q8_0 blocks) is stored so that
+// its 16-byte chunk t holds what lane t of a tensor-core fragment needs: word t of each of the four
+// Q4_0 blocks, or bytes 8t..8t+7 of each of the two Q8_0 blocks.
+__device__ __forceinline__ int64_t qs_index(int type, int interleave, int64_t b, int byte)
+{
+    if (type == PG_GGUF_Q8_0) {
+        if (!interleave) return b * 32 + byte;
+        return (b >> 1) * 64 + (byte >> 3) * 16 + (b & 1) * 8 + (byte & 7);
+    }
+    if (!interleave) return b * 16 + byte;
+    return (b >> 2) * 64 + (byte >> 2) * 16 + (b & 3) * 4 + (byte & 3);
+}
+
+__global__ void __launch_bounds__(256) repack_kernel(int type, int interleave, const uint8_t *__restrict__ raw, int64_t num_blocks,
                                                       uint8_t *__restrict__ qs, uint16_t *__restrict__ dd, uint16_t *__restrict__ mm)
 {
     const int lane = threadIdx.x & 31;
@@ -88,9 +101,9 @@ __global__ void __launch_bounds__(256) repack_kernel(int type, const uint8_t *__
         const uint8_t *p = raw + b * bs;
         if (lane == 0) dd[b] = (uint16_t)(p[0] | (p[1] << 8));
         if (type == PG_GGUF_Q8_0) {
-            qs[b * 32 + lane] = p[2 + lane];
+            qs[qs_index(type, interleave, b, lane)] = p[2 + lane];
         } else if (type == PG_GGUF_Q4_0) {
-            if (lane < 16) qs[b * 16 + lane] = p[2 + lane];
+            if (lane < 16) qs[qs_index(type, interleave, b, lane)] = p[2 + lane];
         } else {
             if (lane == 1) mm[b] = (uint16_t)(p[2] | (p[3] << 8));
             if (lane < 16) qs[b * 16 + lane] = p[4 + lane];
@@ -104,7 +117,7 @@ __global__ void __launch_bounds__(256) repack_kernel(int type, const uint8_t *__
 // each activation row forms the block's partial sum in f32 before applying the block scale:
 // y += d * sum_i x_i q_i  (+ m * sum_i x_i for Q4_1).  Lanes are then summed by shuffles.
 template <int TYPE, int R, int MC>
-__global__ void __launch_bounds__(256) matmul_gguf_kernel(const float *__restrict__ x, int m0, int M, int K,
+__global__ void __launch_bounds__(256) matmul_gguf_kernel(const float *__restrict__ x, int m0, int M, int K, int interleave,
                                                            const uint8_t *__restrict__ qs, const uint16_t *__restrict__ dd,
                                                            const uint16_t *__restrict__ mm, int64_t N, float *__restrict__ y)
 {
@@ -129,16 +142,33 @@ __global__ void __launch_bounds__(256) matmul_gguf_kernel(const float *__restric
             d[j] = __half2float(__ushort_as_half(dd[blk]));
             mn[j] = 0.0f;
             if (TYPE == PG_GGUF_Q8_0) {
-                const uint4 *p = reinterpret_cast<const uint4 *>(qs + blk * 32);
-                const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
-                const uint32_t wds[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                uint32_t wds[8];
+                if (!interleave) {
+                    const uint4 *p = reinterpret_cast<const uint4 *>(qs + blk * 32);
+                    const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
+                    wds[0] = v0.x; wds[1] = v0.y; wds[2] = v0.z; wds[3] = v0.w;
+                    wds[4] = v1.x; wds[5] = v1.y; wds[6] = v1.z; wds[7] = v1.w;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(qs + (blk >> 1) * 64 + c * 16 + (blk & 1) * 8));
+                        wds[2 * c] = v.x;
+                        wds[2 * c + 1] = v.y;
+                    }
+                }
 #pragma unroll
                 for (int wd = 0; wd < 8; wd++)
 #pragma unroll
                     for (int e = 0; e < 4; e++) q[j][wd * 4 + e] = (float)(int8_t)((wds[wd] >> (8 * e)) & 0xff);
             } else {
-                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(qs + blk * 16));
-                const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+                uint32_t wds[4];
+                if (!interleave) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(qs + blk * 16));
+                    wds[0] = v.x; wds[1] = v.y; wds[2] = v.z; wds[3] = v.w;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) wds[c] = __ldg(reinterpret_cast<const uint32_t *>(qs + (blk >> 2) * 64 + c * 16 + (blk & 3) * 4));
+                }
 #pragma unroll
                 for (int wd = 0; wd < 4; wd++)
 #pragma unroll
@@ -197,7 +227,7 @@ int32_t launch_matmul(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_we
     const int64_t warps = (w->n + R - 1) / R;
     const int64_t blocks = (warps + 7) / 8;
     for (int64_t m0 = 0; m0 < m; m0 += MC) {
-        matmul_gguf_kernel<TYPE, R, MC><<<(unsigned)blocks, 256, 0, ctx->stream>>>(d_x, (int)m0, (int)m, (int)w->k, w->d_qs, w->d_d,
+        matmul_gguf_kernel<TYPE, R, MC><<<(unsigned)blocks, 256, 0, ctx->stream>>>(d_x, (int)m0, (int)m, (int)w->k, w->interleaved, w->d_qs, w->d_d,
                                                                                   w->d_m, w->n, d_y);
         PG_LAUNCHED();
     }
@@ -230,7 +260,9 @@ int32_t pgk_gguf_repack(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t
     if (num_blocks == 0) return PG_OK;
     int64_t blocks = (num_blocks + 7) / 8;
     if (blocks > (int64_t)ctx->sm_count * 64) blocks = (int64_t)ctx->sm_count * 64;
-    repack_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(type, d_raw, num_blocks, w->d_qs, w->d_d, w->d_m);
+    // the tensor-core kernel's layout whenever that kernel can take the weight (its shape test)
+    w->interleaved = (type == PG_GGUF_Q4_0 || type == PG_GGUF_Q8_0) && k >= 256 && (k % 256 == 0);
+    repack_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(type, w->interleaved, d_raw, num_blocks, w->d_qs, w->d_d, w->d_m);
     PG_LAUNCHED();
     return PG_OK;
 }

@@ -9,21 +9,23 @@
 // the HBM rate already at M = 8.  Here
 //   * the quants go to the MMA as exact fp16 integers, built with two logic ops per pair from the
 //     packed nibbles/bytes (exponent-bias trick: 0x6400 | u is the half 1024 + u);
-//   * each f32 activation is split into two fp16 parts, x * 2^s = hi + lo * 2^-11 (s a per-row
-//     power of two that brings the row into [-16,16)), which keeps 22 significant bits; every
-//     product quant x part is exact and the sums accumulate in f32 inside the MMA;
-//   * per 32-element block the two partial sums are combined and multiplied by the block's f16
-//     scale: y += d * (sum_hi + sum_lo * 2^-11), in f32.
+//   * each f32 activation is split into two fp16 parts, x * 2^s = hi + lo (s a per-row power of
+//     two that brings the row's largest element into [8,16), so that lo keeps an absolute
+//     precision of 2^-25 on that scale); every product quant x part is exact and the sums
+//     accumulate in f32 inside the MMA;
+//   * per 32-element block the partial sum is multiplied by the block's f16 scale: y += d * sum.
 // The result differs from the reference's strictly sequential f32 loop only in summation order
-// (documented tolerance: 1e-5 of max|y|; measured about 1e-7).
+// and in the 2^-28 relative truncation of the activations (documented tolerance: 1e-5 of max|y|;
+// measured a few 1e-6, which is also the sequential f32 loop's own distance from an f64 sum).
 //
 // Data flow, per CTA of 16 warps (one CTA per SM, persistent over tiles of 16*R weight rows):
 //   * warp w owns a fixed slice of eight 32-element blocks of K and keeps the activation
 //     fragments of that slice in registers for the whole kernel, so activations cost no memory
 //     traffic in the main loop whatever M is;
-//   * the quants and block scales of tile after tile stream through a per-lane cp.async FIFO in
-//     shared memory (128-bit copies, L2 only), several entries deep, so HBM requests stay in flight
-//     across tile boundaries;
+//   * the quants stream through a lane-private cp.async FIFO in shared memory (128-bit copies,
+//     L2 only), several entries deep, so HBM requests stay in flight across tile boundaries.  The
+//     upload interleaves each 64-byte group of quants so that the 16 bytes a lane needs for the
+//     group's blocks are contiguous: a lane copies exactly what it will read back;
 //   * per tile the 16 warps' partial sums meet in shared memory (fixed order: deterministic).
 // K longer than 128 blocks is handled by one launch per 4096-element chunk, accumulating into y.
 #include <cuda_fp16.h>
@@ -36,42 +38,21 @@ constexpr int G_WARPS = 16;
 constexpr int G_THREADS = G_WARPS * 32;
 constexpr int G_SLICE = 8;                      // blocks of K per warp
 constexpr int G_CHUNK = G_WARPS * G_SLICE;      // 128 blocks = 4096 elements per launch
-// One FIFO entry of a warp: quants of rows g and g+8 for the eight lane groups, 64 B each padded to
-// 80 B so that the groups fall into distinct banks; then, filled only by the first step of a row
-// group, the 16 B of block scales (eight f16) of each of the 16 rows.
-constexpr int G_QAREA = 2 * 8 * 80;
-constexpr int G_WSLOT = G_QAREA + 16 * 16;      // 1536 B per warp and entry
+// One FIFO entry of a warp: 16 B of quants per lane for rows g and g+8 (lane-private), then, filled
+// only by the first step of a row group, the 16 B of block scales (eight f16) of each of the 16 rows.
+constexpr int G_QAREA = 2 * 32 * 16;
+constexpr int G_WSLOT = G_QAREA + 16 * 16;      // 1280 B per warp and entry
 constexpr int G_SLOT_BYTES = G_WARPS * G_WSLOT;  // one entry for the whole CTA
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t n)
 {
     asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src, uint32_t n)
-{
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t n)
-{
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_wait()
 {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t a)
-{
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ uint2 lds64(uint32_t a)
-{
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
-    return v;
 }
 __device__ __forceinline__ uint4 lds128(uint32_t a)
 {
@@ -97,6 +78,26 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// the eight quants of one block that lane t owns, as four fp16 pairs
+template <int TYPE>
+__device__ __forceinline__ void unpack(uint32_t w0, uint32_t w1, uint32_t (&a)[4])
+{
+    if (TYPE == PG_GGUF_Q4_0) {
+        // w0 = word t of the block: nibbles e0..e7 from bit 0 up.  Pairs (e0,e4) (e1,e5)*16 (e2,e6) (e3,e7)*16.
+        const uint32_t w8 = w0 >> 8;
+        a[0] = sub_f16x2(lop_and_or(w0, 0x000F000Fu, 0x64006400u), 0x64086408u);
+        a[1] = sub_f16x2(lop_and_or(w0, 0x00F000F0u, 0x64006400u), 0x64806480u);
+        a[2] = sub_f16x2(lop_and_or(w8, 0x000F000Fu, 0x64006400u), 0x64086408u);
+        a[3] = sub_f16x2(lop_and_or(w8, 0x00F000F0u, 0x64006400u), 0x64806480u);
+    } else {
+        // w0, w1 = bytes 8t..8t+7 of the block; q + 128 as unsigned bytes, then 0x6400 | u = 1024 + u
+        const uint32_t u0 = w0 ^ 0x80808080u, u1 = w1 ^ 0x80808080u;
+        a[0] = sub_f16x2(__byte_perm(u0, 0x64646464u, 0x4140), 0x64806480u);
+        a[1] = sub_f16x2(__byte_perm(u0, 0x64646464u, 0x4342), 0x64806480u);
+        a[2] = sub_f16x2(__byte_perm(u1, 0x64646464u, 0x4140), 0x64806480u);
+        a[3] = sub_f16x2(__byte_perm(u1, 0x64646464u, 0x4342), 0x64806480u);
+    }
 }
 
 // ---- activation fragments -------------------------------------------------------------------
@@ -150,8 +151,8 @@ __global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restric
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const __half h0 = __float2half_rn(o[2 * j]), h1 = __float2half_rn(o[2 * j + 1]);
-            const __half l0 = __float2half_rn((o[2 * j] - __half2float(h0)) * 2048.0f);
-            const __half l1 = __float2half_rn((o[2 * j + 1] - __half2float(h1)) * 2048.0f);
+            const __half l0 = __float2half_rn(o[2 * j] - __half2float(h0));
+            const __half l1 = __float2half_rn(o[2 * j + 1] - __half2float(h1));
             hi[j] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
             lo[j] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
         }
@@ -163,6 +164,9 @@ __global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restric
 
 // ---- the product -----------------------------------------------------------------------------
 // BPS = blocks per 64-byte step of a row's quants: 4 for Q4_0 (16 B per block), 2 for Q8_0 (32 B).
+// Interleaved quant layout (made at upload): inside each 64-byte group, the 16-byte chunk t holds
+//   Q4_0: word t (nibbles 8t..8t+7) of the group's blocks 0,1,2,3
+//   Q8_0: bytes 8t..8t+7 of block 0, then of block 1.
 template <int TYPE, int R, int D>
 __global__ void __launch_bounds__(G_THREADS, 1)
     gguf_mma_kernel(const uint4 *__restrict__ xs, const float *__restrict__ row_scale, const uint8_t *__restrict__ qs,
@@ -183,8 +187,8 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     const int64_t tiles = (N + TROWS - 1) / TROWS;
     const int my_tiles = (tiles > blockIdx.x) ? (int)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
 
-    // Issue side of the FIFO: walks (tile, row group, step) in the order the consumer does and copies
-    // the quants of rows g and g+8 of the group; the first step of a row group also brings the block
+    // Issue side of the FIFO: walks (tile, row group, step) in the order the consumer does.  Each lane
+    // copies its own 16 bytes of rows g and g+8; the first step of a row group also brings the block
     // scales of the warp's whole K slice for those rows (lanes t = 0, 1 copy them for g and g+8).
     int i_tile = 0, i_step = 0, i_rg = 0, i_slot = 0;
     auto issue = [&]() {
@@ -198,8 +202,7 @@ __global__ void __launch_bounds__(G_THREADS, 1)
             const bool ok = kok && (row < N);
             row = ok ? row : 0;
             const int64_t blk = row * nblk_row + blk0 + (ok ? b : 0);
-            // lane t copies 16 of the step's 64 quant bytes; the four lanes of a group share them
-            cp_async16(slot + (h * 8 + g) * 80 + t * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
+            cp_async16(slot + (h * 32 + lane) * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
             if (i_step == 0 && t == h) cp_async16(slot + G_QAREA + (h * 8 + g) * 16, dd + blk, ok ? 16u : 0u);
         }
         cp_commit();
@@ -241,58 +244,42 @@ __global__ void __launch_bounds__(G_THREADS, 1)
             for (int step = 0; step < STEPS; step++) {
                 issue();
                 cp_wait<D - 1>();
-                __syncwarp();  // the group's lanes read each other's copies
                 const uint32_t slot = wbase + (uint32_t)c_slot * G_SLOT_BYTES;
                 if (++c_slot == D) c_slot = 0;
                 if (step == 0) {
+                    __syncwarp();  // the scales were copied by other lanes of the group
                     sc0 = lds128(slot + G_QAREA + g * 16);
                     sc1 = lds128(slot + G_QAREA + (8 + g) * 16);
                 }
-                const uint32_t q0 = slot + g * 80, q1 = slot + (8 + g) * 80;  // quants of rows g and g+8
+                const uint4 qa = lds128(slot + lane * 16), qb = lds128(slot + (32 + lane) * 16);  // rows g, g+8
+                const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
                 for (int bi = 0; bi < BPS; bi++) {
                     const int j = step * BPS + bi;  // block inside the warp's slice
-                    uint32_t a[2][4];               // [row half][pair]
+                    uint32_t a0[4], a1[4];          // rows g and g+8
                     if (TYPE == PG_GGUF_Q4_0) {
-                        // block bi was copied by lane (g, bi): its word t holds our eight nibbles
-#pragma unroll
-                        for (int h = 0; h < 2; h++) {
-                            const uint32_t w = lds32((h ? q1 : q0) + bi * 16 + t * 4);
-                            const uint32_t w8 = w >> 8;
-                            a[h][0] = sub_f16x2(lop_and_or(w, 0x000F000Fu, 0x64006400u), 0x64086408u);   // q
-                            a[h][1] = sub_f16x2(lop_and_or(w, 0x00F000F0u, 0x64006400u), 0x64806480u);   // 16 q
-                            a[h][2] = sub_f16x2(lop_and_or(w8, 0x000F000Fu, 0x64006400u), 0x64086408u);
-                            a[h][3] = sub_f16x2(lop_and_or(w8, 0x00F000F0u, 0x64006400u), 0x64806480u);
-                        }
+                        unpack<TYPE>(wa[bi], 0u, a0);
+                        unpack<TYPE>(wb[bi], 0u, a1);
                     } else {
-                        // the step's two blocks are contiguous in the group's 64 bytes; ours are bytes 8t..8t+7 of block bi
-#pragma unroll
-                        for (int h = 0; h < 2; h++) {
-                            const uint2 w = lds64((h ? q1 : q0) + bi * 32 + t * 8);
-                            const uint32_t u0 = w.x ^ 0x80808080u, u1 = w.y ^ 0x80808080u;  // q + 128 as unsigned bytes
-                            a[h][0] = sub_f16x2(__byte_perm(u0, 0x64646464u, 0x4140), 0x64806480u);
-                            a[h][1] = sub_f16x2(__byte_perm(u0, 0x64646464u, 0x4342), 0x64806480u);
-                            a[h][2] = sub_f16x2(__byte_perm(u1, 0x64646464u, 0x4140), 0x64806480u);
-                            a[h][3] = sub_f16x2(__byte_perm(u1, 0x64646464u, 0x4342), 0x64806480u);
-                        }
+                        unpack<TYPE>(wa[2 * bi], wa[2 * bi + 1], a0);
+                        unpack<TYPE>(wb[2 * bi], wb[2 * bi + 1], a1);
                     }
-                    float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_f16(ch, a[0][0], a[1][0], a[0][1], a[1][1], xh[j].x, xh[j].y);
-                    mma_f16(ch, a[0][2], a[1][2], a[0][3], a[1][3], xh[j].z, xh[j].w);
-                    mma_f16(cl, a[0][0], a[1][0], a[0][1], a[1][1], xl[j].x, xl[j].y);
-                    mma_f16(cl, a[0][2], a[1][2], a[0][3], a[1][3], xl[j].z, xl[j].w);
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_f16(c, a0[0], a1[0], a0[1], a1[1], xh[j].x, xh[j].y);
+                    mma_f16(c, a0[2], a1[2], a0[3], a1[3], xh[j].z, xh[j].w);
+                    mma_f16(c, a0[0], a1[0], a0[1], a1[1], xl[j].x, xl[j].y);
+                    mma_f16(c, a0[2], a1[2], a0[3], a1[3], xl[j].z, xl[j].w);
                     // f16 scale of block j of the slice, rows g and g+8
                     const uint32_t p0 = (j < 2) ? sc0.x : (j < 4) ? sc0.y : (j < 6) ? sc0.z : sc0.w;
                     const uint32_t p1 = (j < 2) ? sc1.x : (j < 4) ? sc1.y : (j < 6) ? sc1.z : sc1.w;
-                    const float d0 = __half2float(__ushort_as_half((unsigned short)((j & 1) ? (p0 >> 16) : (p0 & 0xffff))));
-                    const float d1 = __half2float(__ushort_as_half((unsigned short)((j & 1) ? (p1 >> 16) : (p1 & 0xffff))));
-                    const float k = 1.0f / 2048.0f;
-                    acc[0] = fmaf(d0, fmaf(cl[0], k, ch[0]), acc[0]);
-                    acc[1] = fmaf(d0, fmaf(cl[1], k, ch[1]), acc[1]);
-                    acc[2] = fmaf(d1, fmaf(cl[2], k, ch[2]), acc[2]);
-                    acc[3] = fmaf(d1, fmaf(cl[3], k, ch[3]), acc[3]);
+                    const __half2 h0 = *reinterpret_cast<const __half2 *>(&p0), h1 = *reinterpret_cast<const __half2 *>(&p1);
+                    const float d0 = (j & 1) ? __high2float(h0) : __low2float(h0);
+                    const float d1 = (j & 1) ? __high2float(h1) : __low2float(h1);
+                    acc[0] = fmaf(d0, c[0], acc[0]);
+                    acc[1] = fmaf(d0, c[1], acc[1]);
+                    acc[2] = fmaf(d1, c[2], acc[2]);
+                    acc[3] = fmaf(d1, c[3], acc[3]);
                 }
-                __syncwarp();  // all reads of this entry are done before any lane's next copy reuses it
             }
             // partial sums of this warp's K slice -> shared memory, [buf][warp][rg][m 0..7][row 0..15]
             mine[rg * 128 + (2 * t) * 16 + g] = acc[0];
@@ -370,7 +357,7 @@ extern "C" PG_API void pg_tune_gguf_rows(int r) { g_gguf_rows = r; }
 
 bool pgk_matmul_gguf_mma_supports(const pg_gguf_weight *w, int64_t m)
 {
-    return (w->type == PG_GGUF_Q4_0 || w->type == PG_GGUF_Q8_0) && w->k >= 256 && (w->k % 256 == 0) && m >= 1 && m <= 64 && w->n >= 1;
+    return w->interleaved && m >= 1 && m <= 64 && w->n >= 1;
 }
 
 int32_t pgk_matmul_gguf_mma(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)

@@ -85,6 +85,7 @@ struct pg_gguf_weight {
     uint8_t *d_qs = nullptr;
     uint16_t *d_d = nullptr;
     uint16_t *d_m = nullptr;
+    int interleaved = 0;        // quants stored in the tensor-core kernel's chunk order (see repack_kernel)
 };
 
 int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes);
