@@ -155,6 +155,21 @@ PG_API int32_t pg_matmul_quantized_ex(pg_ctx *ctx, const float *d_x, int64_t m, 
 PG_API int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t k,
                                         const pg_qtensor *w, float *y);
 
+/* ---- the same product for callers that must not allocate (no counterpart in the reference) ----
+ * For hosts that run inside a memory budget fixed before inference starts (a pre-sized arena per
+ * model, a real-time loop in which cudaMalloc is forbidden): identical to pg_matmul_quantized, but
+ * the quantised activations and their row scales live in an array built into the library image
+ * (pg_static_scratch_bytes() bytes on every GPU that loads the library, held until the process
+ * exits) instead of context scratch that grows with cudaMalloc.  The call allocates, frees and
+ * resizes nothing.  Limit: M*K <= 262144 and M <= 256; larger shapes return PG_ERR_UNSUPPORTED.
+ * The first call on each GPU looks up the array's device address: make that call before any
+ * stream capture begins.  All calls on a GPU share the array (it keeps the previous call's bytes;
+ * nothing here needs it zeroed), so calls that can overlap on the GPU race and must be ordered by
+ * the caller. */
+PG_API int32_t pg_matmul_quantized_static(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k,
+                                          const pg_qtensor *w, float *d_y);
+PG_API int64_t pg_static_scratch_bytes(void);
+
 /* ---- the integer GEMM alone: simd_kernels::gemm_i8_sdot (src/simd_kernels.rs:1087-1214),
  *      scalar form src/quant.rs:154-166 ---- */
 PG_API int32_t pg_gemm_i8(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k,

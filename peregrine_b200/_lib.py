@@ -72,6 +72,8 @@ SIGNATURES = {
     "pg_matmul_quantized": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "pg_matmul_quantized_ex": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32]),
     "pg_matmul_quantized_host": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "pg_matmul_quantized_static": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "pg_static_scratch_bytes": (_i64, []),
     "pg_gemm_i8": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32]),
     "pg_dequant_blocks": (_i32, [_vp, _i32, _vp, _sz, _i64, _vp]),
     "pg_dequant_blocks_host": (_i32, [_vp, _i32, _vp, _sz, _i64, _vp]),

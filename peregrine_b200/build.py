@@ -26,6 +26,7 @@ SOURCES = [
     "pg_gemm_tcgen05.cu",
     "pg_gguf.cu",
     "pg_gguf_mma.cu",
+    "pg_noalloc.cu",
 ]
 
 NVCC_FLAGS = [
