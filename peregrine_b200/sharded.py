@@ -1,0 +1,130 @@
+"""Column-sharded quantised linears over the GPUs of one node (one process per GPU).
+
+Each rank keeps the rows [n0, n1) of `data_i8_t [N,K]` (= output columns n0..n1) and the matching
+scales, quantises the replicated activations itself and computes Y[:, n0:n1].  Integer accumulation
+is exact and the epilogue is per column, so the all-gathered matrix is bit-identical to the
+single-GPU product.  The one exchange is an all-gather of output slices over NCCL (gloo in the CPU
+tests), whose API precedent in the reference is `Communicator::allgather`
+(src/comm/communicator.rs:162-191: concatenation of equal chunks in rank order).
+
+For the Llama layer the reference's fused layouts `[Q | K | V]` (src/models/llama/attention.rs:51-71)
+and `[gate | up]` (src/models/llama/decoder.rs:49-67) must not be cut contiguously: `llama_qkv_columns`
+and `llama_gate_up_columns` give each rank whole heads (query heads with the KV head they attend to)
+and matching gate/up column ranges, so attention and SiLU(g)*u stay local to a rank.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+
+def shard_bounds(n: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous, as-equal-as-possible column ranges; the first n % world ranks get one more."""
+    if world < 1 or n < 0:
+        raise ValueError("shard_bounds: need world >= 1 and n >= 0")
+    base, extra = divmod(n, world)
+    out, b = [], 0
+    for r in range(world):
+        e = b + base + (1 if r < extra else 0)
+        out.append((b, e))
+        b = e
+    return out
+
+
+def llama_qkv_columns(n_q_heads: int, n_kv_heads: int, head_dim: int, world: int) -> List[np.ndarray]:
+    """Columns of the fused `[Q | K | V]` weight that rank r owns: its query heads, then the KV
+    heads those query heads use (GQA groups stay together), in Q, K, V order."""
+    if n_kv_heads % world or n_q_heads % n_kv_heads:
+        raise ValueError("llama_qkv_columns: world must divide the KV heads, KV heads must divide the query heads")
+    per_kv = n_q_heads // n_kv_heads
+    kv_per_rank = n_kv_heads // world
+    q_off, k_off, v_off = 0, n_q_heads * head_dim, (n_q_heads + n_kv_heads) * head_dim
+    out = []
+    for r in range(world):
+        kv = range(r * kv_per_rank, (r + 1) * kv_per_rank)
+        qh = [h for g in kv for h in range(g * per_kv, (g + 1) * per_kv)]
+        cols = [q_off + h * head_dim + i for h in qh for i in range(head_dim)]
+        cols += [k_off + g * head_dim + i for g in kv for i in range(head_dim)]
+        cols += [v_off + g * head_dim + i for g in kv for i in range(head_dim)]
+        out.append(np.asarray(cols, np.int64))
+    return out
+
+
+def llama_gate_up_columns(ffn: int, world: int) -> List[np.ndarray]:
+    """Columns of the fused `[gate | up]` weight for rank r: the same range of both halves."""
+    out = []
+    for b, e in shard_bounds(ffn, world):
+        out.append(np.concatenate([np.arange(b, e, dtype=np.int64), np.arange(ffn + b, ffn + e, dtype=np.int64)]))
+    return out
+
+
+def take_columns(qt, cols: Sequence[int]):
+    """A QuantizedTensor-like holding only `cols` (in that order) of `qt` (host arrays)."""
+    cols = np.asarray(cols, np.int64)
+    data_i8 = None if qt.data_i8 is None else np.ascontiguousarray(qt.data_i8[:, cols])
+    return type(qt)(data_i8, np.ascontiguousarray(qt.data_i8_t[cols]), np.ascontiguousarray(qt.scales[cols]), qt.rows, len(cols))
+
+
+def unshard_columns(parts: Sequence[np.ndarray], columns: Sequence[np.ndarray], n: int) -> np.ndarray:
+    """Inverse of a column plan: parts[r] is [M, len(columns[r])]; returns [M, n]."""
+    m = parts[0].shape[0]
+    y = np.empty((m, n), parts[0].dtype)
+    for p, c in zip(parts, columns):
+        y[:, c] = p
+    return y
+
+
+class ColumnShardedLinear:
+    """y = matmul_quantized(x, W) with W's output columns split over the ranks of `group`.
+
+    `columns` is this rank's column index array (default: the contiguous shard).  `compute(x, m,
+    k, shard)` produces the local slice; by default it is the CUDA path (`quant.matmul_quantized`
+    on this rank's GPU).  The CPU tests pass the oracle here to exercise the plan and the gather."""
+
+    def __init__(self, qt, rank: int, world: int, columns: Optional[Sequence[np.ndarray]] = None, gpu=None,
+                 compute: Optional[Callable] = None, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        self.n, self.k = qt.cols, qt.rows
+        if columns is None:
+            columns = [np.arange(b, e, dtype=np.int64) for b, e in shard_bounds(self.n, world)]
+        if len(columns) != world:
+            raise ValueError("ColumnShardedLinear: one column set per rank is required")
+        seen = np.sort(np.concatenate([np.asarray(c) for c in columns]))
+        if seen.size != self.n or not np.array_equal(seen, np.arange(self.n)):
+            raise ValueError("ColumnShardedLinear: the column sets must partition 0..N-1")
+        self.columns = [np.asarray(c, np.int64) for c in columns]
+        self.width = max(len(c) for c in self.columns)     # slices are padded to this for the gather
+        self.shard = take_columns(qt, self.columns[rank])
+        self.gpu = gpu
+        if compute is None:
+            from . import quant
+
+            def compute(x, m, k, shard, _gpu=gpu):
+                return quant.matmul_quantized(x, m, k, shard, _gpu)
+
+        self.compute = compute
+
+    def local(self, x, m: int) -> np.ndarray:
+        return np.asarray(self.compute(x, m, self.k, self.shard), np.float32).reshape(m, len(self.columns[self.rank]))
+
+    def forward(self, x, m: int) -> np.ndarray:
+        """All ranks call this with the same x; every rank returns the full [m, N] result."""
+        import torch
+        import torch.distributed as dist
+
+        mine = self.local(x, m)
+        if self.world == 1:
+            return unshard_columns([mine], self.columns, self.n)
+        pad = np.zeros((m, self.width), np.float32)
+        pad[:, : mine.shape[1]] = mine
+        send = torch.from_numpy(pad)
+        device = None
+        if dist.get_backend(self.group) == "nccl":
+            device = torch.device("cuda", torch.cuda.current_device())
+            send = send.to(device)
+        recv = torch.empty((self.world * m, self.width), dtype=torch.float32, device=send.device)
+        dist.all_gather_into_tensor(recv, send, group=self.group)   # rank-major concatenation
+        full = recv.cpu().numpy().reshape(self.world, m, self.width)
+        parts = [full[r][:, : len(self.columns[r])] for r in range(self.world)]
+        return unshard_columns(parts, self.columns, self.n)
