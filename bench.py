@@ -265,6 +265,9 @@ def run_ours(args):
     stream.synchronize()
     launches_per_step = int(lib.pg_launch_count() - n0)
 
+    # One submission per step at N = 1 (the library's own graph recorder).  With NCCL in the step the
+    # launches stay eager: replaying a captured step that contained the all-gathers did not complete
+    # on this pool, so that form is not used.
     graph = None
     if world == 1:
         with gpu.record() as graph:
