@@ -24,6 +24,7 @@ SOURCES = [
     "pg_gemm_naive.cu",
     "pg_gemv_w8a8.cu",
     "pg_gemm_tcgen05.cu",
+    "pg_gemm_tcgen05_2cta.cu",
     "pg_gguf.cu",
     "pg_gguf_mma.cu",
     "pg_noalloc.cu",

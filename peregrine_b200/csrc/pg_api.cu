@@ -125,8 +125,8 @@ int32_t pg_ctx_create(int32_t device, void *stream, pg_ctx **out)
         }
         ctx->owns_stream = true;
     }
-    cudaError_t me = cudaMalloc(&ctx->d_status, sizeof(int32_t));
-    if (me == cudaSuccess) me = cudaMemset(ctx->d_status, 0, sizeof(int32_t));
+    cudaError_t me = cudaMalloc(&ctx->d_status, 16 * sizeof(int32_t));  // [0] status word; the rest is spare
+    if (me == cudaSuccess) me = cudaMemset(ctx->d_status, 0, 16 * sizeof(int32_t));
     if (me != cudaSuccess) {
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;

@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "pg_internal.cuh"
+#include "pg_tc_epilogue.cuh"
 
 namespace {
 
@@ -172,7 +173,7 @@ struct Cfg {
     static constexpr int STAGE = STAGE_A + STAGE_B;
     static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two >= 32
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * PG_EPI_WARP_BYTES;
 };
 
 template <int BN>
@@ -299,40 +300,40 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + q * 32 + lane;
+            const int row_base = m0 + q * 32;
+            const int row = row_base + lane;
             const float as = (row < M && y) ? a_scales[row] : 0.0f;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+            const uint32_t stage_buf = base + (uint32_t)((size_t)STAGES * C::STAGE) + 256u + (uint32_t)q * PG_EPI_WARP_BYTES;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
-                if (row < M && n0 + c < N) {
-                    const int64_t off = (int64_t)row * N + n0 + c;
-                    if (vec_ok) {
+                if (row_base >= M || n0 + c >= N) continue;   // uniform over the warp
+                const int64_t off0 = (int64_t)row_base * N + n0 + c;
+                if (vec_ok) {
+                    // coalesced: the warp exchanges the block through shared memory and writes whole row segments
+                    if (acc_out) pg_store_block_32x32(reinterpret_cast<uint32_t *>(acc_out + off0), N, M - row_base, N - (n0 + c), stage_buf, lane, v);
+                    if (y) {
+                        uint32_t o[32];
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
-                            if (n0 + c + j < N) {
-                                if (acc_out)
-                                    *reinterpret_cast<int4 *>(acc_out + off + j) =
-                                        make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
-                                if (y) {
-                                    const float4 ws = __ldg(reinterpret_cast<const float4 *>(w_scales + n0 + c + j));
-                                    float4 o;
-                                    o.x = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j]), as), ws.x);
-                                    o.y = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j + 1]), as), ws.y);
-                                    o.z = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j + 2]), as), ws.z);
-                                    o.w = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j + 3]), as), ws.w);
-                                    *reinterpret_cast<float4 *>(y + off + j) = o;
-                                }
-                            }
+                            float4 ws = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (n0 + c + j < N) ws = __ldg(reinterpret_cast<const float4 *>(w_scales + n0 + c + j));
+                            o[j] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn((int)v[j]), as), ws.x));
+                            o[j + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn((int)v[j + 1]), as), ws.y));
+                            o[j + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn((int)v[j + 2]), as), ws.z));
+                            o[j + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn((int)v[j + 3]), as), ws.w));
                         }
-                    } else {
+                        pg_store_block_32x32(reinterpret_cast<uint32_t *>(y + off0), N, M - row_base, N - (n0 + c), stage_buf, lane, o);
+                    }
+                } else if (row < M) {
+                    const int64_t off = off0 + (int64_t)lane * N;
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (n0 + c + j < N) {
-                                if (acc_out) acc_out[off + j] = (int)v[j];
-                                if (y) y[off + j] = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j]), as), __ldg(w_scales + n0 + c + j));
-                            }
+                    for (int j = 0; j < 32; j++) {
+                        if (n0 + c + j < N) {
+                            if (acc_out) acc_out[off + j] = (int)v[j];
+                            if (y) y[off + j] = __fmul_rn(__fmul_rn(__int2float_rn((int)v[j]), as), __ldg(w_scales + n0 + c + j));
                         }
                     }
                 }
@@ -347,6 +348,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
     }
 
+    __syncwarp();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -415,10 +417,12 @@ int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, 
 }
 
 int g_force_bn = 0;
+int g_pair_mode = 0;  // 0 = heuristic, 1 = never use CTA pairs, 2 = always
 
 }  // namespace
 
 extern "C" PG_API void pg_tune_tcgen05_bn(int bn) { g_force_bn = bn; }
+extern "C" PG_API void pg_tune_tcgen05_pair(int mode) { g_pair_mode = mode; }
 
 bool pgk_gemm_i8_tcgen05_supports(int64_t m, int64_t k, int64_t n)
 {
@@ -432,6 +436,11 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     const int64_t n = w->cols;
     if (!pgk_gemm_i8_tcgen05_supports(m, k, n) || ((uintptr_t)d_a & 15) || ((uintptr_t)w->d_data_i8_t & 15))
         PG_FAIL(PG_ERR_UNSUPPORTED, "gemm_i8 tcgen05 kernel needs K%%16==0 and 16-byte aligned operands (K=%lld)", (long long)k);
+    // CTA pairs (256 x 256 tiles) as soon as those tiles can occupy half of the SM pairs: measured
+    // faster than one CTA per tile from M = 512 upwards (2896 vs 2658 TOPS at M 8192, N 14336)
+    const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && !g_force_bn && pair_tiles >= ctx->sm_count / 4);
+    if (pair) return pgk_gemm_i8_tcgen05_2cta(ctx, d_a, d_as, m, k, w, d_y, d_acc);
     // Largest N tile that still gives every SM a tile.
     const int64_t tiles_m = (m + BM - 1) / BM;
     int bn = 64;

@@ -109,6 +109,9 @@ int32_t pgk_gemm_i8_stream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, in
 bool pgk_gemm_i8_tcgen05_supports(int64_t m, int64_t k, int64_t n);
 int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, pg_qtensor *w,
                             float *d_y, int32_t *d_acc);
+// pg_gemm_tcgen05_2cta.cu
+int32_t pgk_gemm_i8_tcgen05_2cta(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, pg_qtensor *w,
+                                 float *d_y, int32_t *d_acc);
 // pg_gguf.cu
 int32_t pgk_dequant_blocks(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t num_blocks, float *d_out);
 int32_t pgk_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float *d_out);

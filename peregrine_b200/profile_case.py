@@ -36,12 +36,14 @@ def main() -> None:
     ap.add_argument("--copies", type=int, default=1, help="rotate over this many copies of the weights")
     ap.add_argument("--ng", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--pair", type=int, default=0, help="tcgen05: 0 heuristic, 1 one CTA per tile, 2 CTA pairs")
     a = ap.parse_args()
 
     gpu = GpuContext(0)
     lib = gpu.lib
     lib.pg_tune_stream_ng(a.ng)
     lib.pg_tune_tcgen05_bn(a.bn)
+    lib.pg_tune_tcgen05_pair(a.pair)
     g = np.random.Generator(np.random.PCG64(1))
     m, k, n = a.m, a.k, a.n
     x = g.standard_normal((m, k), dtype=np.float32)

@@ -228,6 +228,18 @@ def test_tcgen05_every_tile_width(pg, gpu, oracle_mt, bn):
         gpu.lib.pg_tune_tcgen05_bn(0)
 
 
+@pytest.mark.parametrize("m,k,n", [(256, 128, 256), (512, 1024, 768), (300, 1040, 520), (1000, 4096, 1000), (129, 144, 257)])
+def test_tcgen05_cta_pairs(pg, gpu, oracle_mt, m, k, n):
+    """cta_group::2: two CTAs share one 256 x 256 tile; full and ragged tiles in M, N and K."""
+    x, w = linear_inputs(m, k, n, 900 + m + n)
+    gpu.lib.pg_tune_tcgen05_pair(2)
+    try:
+        _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["tcgen05"])
+        assert gpu.device_status() == 0
+    finally:
+        gpu.lib.pg_tune_tcgen05_pair(0)
+
+
 @pytest.mark.parametrize("ng", [1, 2, 4])
 def test_stream_every_column_group(pg, gpu, oracle_mt, ng):
     gpu.lib.pg_tune_stream_ng(ng)
