@@ -245,19 +245,37 @@ def run_ours(args):
     if world > 1 and not even:
         raise SystemExit("column shards must be equal for the all-gather")
 
+    from peregrine_b200.sharded import PeerExchange
+
+    peer = world > 1 and args.collective == "peer"
+    exs = [PeerExchange(gpu, rank, world, MS[mi], SHAPES[si][1]) for mi, si in CASES] if peer else None
+
     def enqueue_products():
         for ci, (mi, si) in enumerate(CASES):
             k, _ = SHAPES[si]
             h = pool[si][mi][0]
             _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
+            if peer:
+                # this rank's slice goes straight into every rank's [M, N] buffer over NVLink
+                exs[ci].store(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
+        if peer:
+            # the nine products of the sweep are independent, so the (bounded) waits for the other ranks'
+            # slices come after the last product: the step ends when every rank holds all nine full results
+            for ex in exs:
+                ex.wait()
 
     def step_eager():
         for ci, (mi, si) in enumerate(CASES):
             k, _ = SHAPES[si]
             h = pool[si][mi][0]
             _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
-            if world > 1:
+            if peer:
+                exs[ci].store(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
+            elif world > 1:
                 dist.all_gather_into_tensor(ys_full[ci], ys[ci])
+        if peer:
+            for ex in exs:
+                ex.wait()
 
     n0 = lib.pg_launch_count()
     with torch.cuda.stream(stream):
@@ -269,7 +287,9 @@ def run_ours(args):
     # launches stay eager: replaying a captured step that contained the all-gathers did not complete
     # on this pool, so that form is not used.
     graph = None
-    if world == 1:
+    if world == 1 or peer:
+        if world > 1:
+            dist.barrier()
         with gpu.record() as graph:
             enqueue_products()
 
@@ -324,9 +344,13 @@ def run_ours(args):
             else:
                 xs[ci].copy_(xs_host[ci], non_blocking=True)
                 _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
-                dist.all_gather_into_tensor(ys_full[ci], ys[ci])
-                ys_host[ci].view(MS[mi], world, -1).copy_(ys_full[ci].permute(1, 0, 2), non_blocking=True)
-                stream.synchronize()
+                if peer:
+                    exs[ci].allgather(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
+                    _lib.check(lib.pg_mem_download(gpu.handle, ys_host[ci].data_ptr(), exs[ci].result_ptr, MS[mi] * n * 4))
+                else:
+                    dist.all_gather_into_tensor(ys_full[ci], ys[ci])
+                    ys_host[ci].view(MS[mi], world, -1).copy_(ys_full[ci].permute(1, 0, 2), non_blocking=True)
+                    stream.synchronize()
 
     with torch.cuda.stream(stream):
         for _ in range(3):
@@ -419,15 +443,17 @@ def run_ours(args):
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
             "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9,
-                       "parallelism": f"column-sharded x{world}" + (", NCCL all-gather of output slices" if world > 1 else ""),
+                       "parallelism": f"column-sharded x{world}" + ((", peer-store all-gather over NVLink (own kernel, bounded flag wait)" if peer
+                                                                     else ", NCCL all-gather of output slices") if world > 1 else ""),
                        "l2": "inputs larger than L2: each case reads its own copy of the weights (3 copies per shape, 402 MB per step)",
                        "submission": "one CUDA graph per step" if graph is not None else "eager launches + NCCL",
+                       "collective": ("peer-store" if peer else "nccl") if world > 1 else None,
                        "bytes_per_step": total_bytes},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_s / e2e_steps * 1e3,
                     "api": "pg_matmul_quantized_host (pinned host x in, host y out, blocking)" if world == 1 else
-                           "pinned H2D + pg_matmul_quantized + all-gather + D2H"},
+                           "pinned H2D + pg_matmul_quantized + all-gather + D2H of the full result"},
             "gpu_launches": launches_per_step * args.steps,
             "kernels_per_step": launches_per_step,
             "roofline": roofline,
@@ -437,6 +463,9 @@ def run_ours(args):
             line["also"] = extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks)
     if world > 1:
         dist.barrier()
+        if exs:
+            for ex in exs:
+                ex.destroy()
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
@@ -520,6 +549,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extra", action="store_true", help="also time the prefill GEMM and the GGUF products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: all-gather by peer stores recorded in the step graph (default) or eager NCCL")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

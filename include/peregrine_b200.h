@@ -48,6 +48,7 @@ typedef struct pg_ctx pg_ctx;
 typedef struct pg_qtensor pg_qtensor;
 typedef struct pg_gguf_weight pg_gguf_weight;
 typedef struct pg_graph pg_graph;
+typedef struct pg_exchange pg_exchange;
 
 typedef enum pg_status {
     PG_OK = 0,
@@ -201,6 +202,30 @@ PG_API int32_t pg_matmul_gguf_host(pg_ctx *ctx, const float *x, int64_t m, const
  * dequantise -> quantize_weights(rows, cols), all on the device. */
 PG_API int32_t pg_qtensor_from_q8_0(pg_ctx *ctx, const uint8_t *raw, size_t raw_len, int64_t rows, int64_t cols,
                                     pg_qtensor **out);
+
+/* ---- all-gather of output slices between the GPUs of one node; API precedent:
+ *      Communicator::allgather (src/comm/communicator.rs:162-191, a CPU shared-memory ring) ----
+ * One process per GPU.  Every rank creates an exchange (a result buffer of y_bytes plus control words,
+ * shareable through CUDA IPC), the ranks swap the 64-byte handles by any means (the tests use
+ * torch.distributed), and connect.  pg_exchange_allgather then stores this rank's slice
+ * [M, n_local] into columns [col0, col0+n_local) of EVERY rank's [M, n_total] buffer with plain
+ * stores over NVLink and waits, bounded (about a second; PG_ERR_DEVICE_TIMEOUT in the status word on
+ * expiry), until all ranks have delivered theirs; pg_exchange_result is then the full matrix.  The
+ * kernels count exchanges on the device, so the call can be recorded with pg_graph_begin/end.  An
+ * exchange may be reused only after every rank has consumed its previous result (use one per
+ * linear of a layer, or alternate two). */
+PG_API int32_t pg_exchange_create(pg_ctx *ctx, int32_t rank, int32_t world, size_t y_bytes, void *handle_out,
+                                  pg_exchange **out);
+PG_API int32_t pg_exchange_connect(pg_ctx *ctx, pg_exchange *ex, const void *handles);
+PG_API float *pg_exchange_result(const pg_exchange *ex);
+PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local,
+                                     int64_t n_total, int64_t col0);
+/* The two halves of pg_exchange_allgather, for callers that have independent work to enqueue between
+ * handing over their slice and needing everybody's: one wait per store, same order on every rank. */
+PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local,
+                                 int64_t n_total, int64_t col0);
+PG_API int32_t pg_exchange_wait(pg_ctx *ctx, pg_exchange *ex);
+PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex);
 
 /* ---- Tensor::matmul, naive branch (src/tensor.rs:1342-1354): [M,K] x [K,N] f32,
  *      ascending-p accumulation with separately rounded multiply and add ---- */

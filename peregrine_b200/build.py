@@ -28,6 +28,7 @@ SOURCES = [
     "pg_gguf.cu",
     "pg_gguf_mma.cu",
     "pg_noalloc.cu",
+    "pg_peer.cu",
 ]
 
 NVCC_FLAGS = [

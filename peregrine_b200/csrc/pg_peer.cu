@@ -16,6 +16,10 @@
 // Counting on the device (not in kernel arguments) keeps the kernels replayable from a graph.
 // The consumer's wait is bounded (about a second): on expiry it records PG_ERR_DEVICE_TIMEOUT in the
 // context's status word and returns, so a missing peer never hangs a GPU.
+#include <string.h>
+
+#include <new>
+
 #include "pg_internal.cuh"
 
 namespace {
@@ -58,9 +62,11 @@ __global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *
             for (int p = 0; p < world; p++) dst.y[p][m * n_total + col0 + c] = v;
         }
     }
-    __threadfence_system();  // this thread's peer stores are visible system-wide before it is counted
+    // The CTA barrier orders every thread's peer stores before thread 0's system-scope fence, which
+    // (fences are cumulative) makes them visible to the other GPUs before the CTA is counted.
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         uint32_t *ctl = dst.ctl[rank];
         if (atomicAdd(&ctl[PG_MAX_PEERS + 2], 1u) == gridDim.x - 1) {
             ctl[PG_MAX_PEERS + 2] = 0;
@@ -170,15 +176,15 @@ PG_API int32_t pg_exchange_connect(pg_ctx *ctx, pg_exchange *ex, const void *han
 
 PG_API float *pg_exchange_result(const pg_exchange *ex) { return ex ? ex->y_local : nullptr; }
 
-// Enqueues: copy slice [M, n_local] into columns [col0, col0 + n_local) of every rank's result buffer
-// ([M, n_total]), publish, then wait (bounded) until every rank has delivered its slice of this exchange.
-PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local, int64_t n_total,
-                                     int64_t col0)
+// Enqueues the store half: copy slice [M, n_local] into columns [col0, col0 + n_local) of every rank's
+// result buffer ([M, n_total]) and publish.  Returns without waiting for the other ranks.
+PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local, int64_t n_total,
+                                 int64_t col0)
 {
-    PG_REQUIRE(ctx && ex, "exchange_allgather: null argument");
-    PG_REQUIRE(m >= 0 && n_local >= 0 && col0 >= 0 && col0 + n_local <= n_total, "exchange_allgather: bad column range");
-    PG_REQUIRE((size_t)m * (size_t)n_total * sizeof(float) <= ex->y_bytes, "exchange_allgather: result does not fit the exchange buffer");
-    PG_REQUIRE(ex->dst.y[ex->world - 1] != nullptr, "exchange_allgather: pg_exchange_connect has not been called");
+    PG_REQUIRE(ctx && ex, "exchange_store: null argument");
+    PG_REQUIRE(m >= 0 && n_local >= 0 && col0 >= 0 && col0 + n_local <= n_total, "exchange_store: bad column range");
+    PG_REQUIRE((size_t)m * (size_t)n_total * sizeof(float) <= ex->y_bytes, "exchange_store: result does not fit the exchange buffer");
+    PG_REQUIRE(ex->dst.y[ex->world - 1] != nullptr, "exchange_store: pg_exchange_connect has not been called");
     const int64_t total = m * n_local;
     int64_t blocks = (total / 4 + 255) / 256;
     if (blocks < 1) blocks = 1;
@@ -194,6 +200,17 @@ PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *
     cfg.numAttrs = 1;
     PG_CUDA(cudaLaunchKernelEx(&cfg, peer_allgather_store_kernel, d_slice, (int)m, n_local, n_total, col0, ex->dst, ex->world, ex->rank));
     PG_LAUNCHED();
+    return PG_OK;
+}
+
+// Enqueues the wait half: a bounded wait until every rank has delivered its slice of this rank's next
+// exchange on `ex`.  One wait per store, in the same order on every rank.
+PG_API int32_t pg_exchange_wait(pg_ctx *ctx, pg_exchange *ex)
+{
+    PG_REQUIRE(ctx && ex, "exchange_wait: null argument");
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t wc = {};
     wc.gridDim = dim3(1);
     wc.blockDim = dim3(32);
@@ -203,6 +220,15 @@ PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *
     PG_CUDA(cudaLaunchKernelEx(&wc, peer_wait_kernel, ex->ctl_local, ex->world, ctx->d_status));
     PG_LAUNCHED();
     return PG_OK;
+}
+
+// store + wait
+PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local, int64_t n_total,
+                                     int64_t col0)
+{
+    const int32_t rc = pg_exchange_store(ctx, ex, d_slice, m, n_local, n_total, col0);
+    if (rc != PG_OK) return rc;
+    return pg_exchange_wait(ctx, ex);
 }
 
 PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex)

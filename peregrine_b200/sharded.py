@@ -128,3 +128,69 @@ class ColumnShardedLinear:
         full = recv.cpu().numpy().reshape(self.world, m, self.width)
         parts = [full[r][:, : len(self.columns[r])] for r in range(self.world)]
         return unshard_columns(parts, self.columns, self.n)
+
+
+class PeerExchange:
+    """All-gather of output slices by direct stores into the other GPUs' result buffers
+    (`pg_exchange_*`): no library collective in the step, so a whole sharded step can be recorded
+    into one CUDA graph.  Handles are swapped once through `torch.distributed` (any backend)."""
+
+    def __init__(self, gpu, rank: int, world: int, m_max: int, n_total: int, group=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+
+        from . import _lib
+
+        self.gpu, self.rank, self.world, self.n_total = gpu, rank, world, n_total
+        handle = (C.c_ubyte * 64)()
+        h = C.c_void_p()
+        _lib.check(gpu.lib.pg_exchange_create(gpu.handle, rank, world, m_max * n_total * 4, handle, C.byref(h)))
+        self.handle = h
+        mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8)
+        if world > 1:
+            dev = torch.device("cuda", gpu.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+            allh = torch.empty(world * 64, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(allh, mine.to(dev), group=group)
+            blob = bytes(allh.cpu().numpy().tobytes())
+        else:
+            blob = bytes(handle)
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        _lib.check(gpu.lib.pg_exchange_connect(gpu.handle, h, buf))
+        if world > 1:
+            dist.barrier(group=group)   # nobody stores into a peer before that peer exists
+        self.result_ptr = gpu.lib.pg_exchange_result(h)
+
+    def allgather(self, d_slice, m: int, n_local: int, col0: int) -> None:
+        """Enqueue on the context's stream; afterwards `result_ptr` holds the full [m, n_total] matrix."""
+        from . import _lib
+        from .runtime import _ptr
+
+        _lib.check(self.gpu.lib.pg_exchange_allgather(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, self.n_total, col0))
+
+    def store(self, d_slice, m: int, n_local: int, col0: int) -> None:
+        """The first half of `allgather`: hand this rank's slice to every rank, do not wait."""
+        from . import _lib
+        from .runtime import _ptr
+
+        _lib.check(self.gpu.lib.pg_exchange_store(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, self.n_total, col0))
+
+    def wait(self) -> None:
+        """The second half: bounded wait for every rank's slice of the oldest store not yet waited for."""
+        from . import _lib
+
+        _lib.check(self.gpu.lib.pg_exchange_wait(self.gpu.handle, self.handle))
+
+    def read(self, m: int) -> np.ndarray:
+        from . import _lib
+        from .runtime import _ptr
+
+        out = np.empty((m, self.n_total), np.float32)
+        _lib.check(self.gpu.lib.pg_mem_download(self.gpu.handle, _ptr(out), self.result_ptr, out.nbytes))
+        return out
+
+    def destroy(self) -> None:
+        if self.handle is not None and self.gpu.handle:
+            self.gpu.lib.pg_exchange_destroy(self.gpu.handle, self.handle)
+        self.handle = None

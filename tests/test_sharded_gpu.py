@@ -45,6 +45,26 @@ def _worker(rank, world, port, out_dir):
             lin = sharded.ColumnShardedLinear(qt, rank, world, columns=plan, gpu=gpu)
             y = lin.forward(x, m)
             assert np.array_equal(y.view(np.uint32), full.view(np.uint32))
+        # the same product with the peer-store all-gather: slices computed on the device, stored into every
+        # rank's result buffer over NVLink, two exchanges in a row on the same object pair
+        from peregrine_b200 import _lib
+
+        b, e = sharded.shard_bounds(n, world)[rank]
+        shard = pg.quant.QuantizedTensor(None, np.ascontiguousarray(ref.data_i8_t[b:e]), np.ascontiguousarray(ref.scales[b:e]), k, e - b)
+        shard.to_gpu(gpu)
+        exs = [sharded.PeerExchange(gpu, rank, world, m, n) for _ in range(2)]
+        d_x = gpu.upload(x.reshape(-1))
+        d_slice = gpu.alloc(m * (e - b), np.float32)
+        for it in range(4):
+            ex = exs[it & 1]
+            _lib.check(gpu.lib.pg_matmul_quantized(gpu.handle, d_x.ptr, m, k, shard._gpu, d_slice.ptr))
+            ex.allgather(d_slice, m, e - b, b)
+            y = ex.read(m)
+            assert gpu.device_status() == 0
+            assert np.array_equal(y.view(np.uint32), full.view(np.uint32)), f"exchange {it}"
+        dist.barrier()
+        for ex in exs:
+            ex.destroy()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
