@@ -227,6 +227,31 @@ PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_sl
 PG_API int32_t pg_exchange_wait(pg_ctx *ctx, pg_exchange *ex);
 PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex);
 
+/* ---- the glue of one Llama decode step between the quantised linears (what the reference runs on the
+ *      host in f32: src/models/llama/decoder.rs:69-155, src/models/llama/attention.rs:73-195,
+ *      src/models/llama/model.rs:223-237).  Rows are independent sequences; the position is read from
+ *      device memory so that a step can be recorded once and replayed. ----
+ * residual add + RMSNorm (src/nn.rs:577-652) + per-row int8 quantiser (src/quant.rs:97-109), fused */
+PG_API int32_t pg_add_rmsnorm_quantize(pg_ctx *ctx, float *d_x, const float *d_delta, const float *d_w, int64_t rows,
+                                       int64_t dim, float eps, int8_t *d_q, float *d_scales, float *d_normed);
+/* silu(gate) * up (src/models/llama/decoder.rs:143-150) on the fused [gate | up] output + quantiser */
+PG_API int32_t pg_swiglu_quantize(pg_ctx *ctx, const float *d_gate_up, int64_t rows, int64_t F, int8_t *d_q,
+                                  float *d_scales, float *d_act);
+/* RoPE (src/nn.rs:1322-1338) on q and k, append of k and v to the f32 KV cache (src/attention.rs:65-83) */
+PG_API int32_t pg_rope_kv_append(pg_ctx *ctx, const float *d_qkv, const int32_t *d_pos, const float *d_cos,
+                                 const float *d_sin, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
+                                 float *d_q_rot, float *d_kcache, float *d_vcache);
+/* GQA attention of one new token per sequence (src/attention.rs:141-265), head_dim 128 */
+PG_API int32_t pg_gqa_decode_splits(int64_t cap);
+PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
+                                       const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
+                                       float *d_work, float *d_out);
+/* embedding gather (src/nn.rs:217-227); greedy argmax, first maximum (examples/llama/main.rs:15-26) */
+PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim,
+                            float *d_out);
+PG_API int32_t pg_argmax_advance(pg_ctx *ctx, const float *d_logits, int64_t B, int64_t V, int32_t *d_tokens,
+                                 int32_t *d_pos);
+
 /* ---- Tensor::matmul, naive branch (src/tensor.rs:1342-1354): [M,K] x [K,N] f32,
  *      ascending-p accumulation with separately rounded multiply and add ---- */
 PG_API int32_t pg_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n,

@@ -29,6 +29,7 @@ SOURCES = [
     "pg_gguf_mma.cu",
     "pg_noalloc.cu",
     "pg_peer.cu",
+    "pg_llama.cu",
 ]
 
 NVCC_FLAGS = [

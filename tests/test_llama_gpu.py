@@ -1,0 +1,242 @@
+"""The Llama decode glue (csrc/pg_llama.cu) and the int8 decode step built from it
+(peregrine_b200/llama.py), against a numpy restatement of the reference's host code
+(src/nn.rs RMSNorm / RoPE, src/attention.rs gqa_attention_cpu, src/models/llama/{attention,decoder,model}.rs)
+with the CPU oracle's matmul_quantized for the linears.
+
+Bars: RoPE, KV append, embedding, argmax: bit-exact.  RMSNorm, SwiGLU, attention: f32 sums in another
+order, 1e-5 of the row maximum.  Whole step (teacher-forced tokens): logits within 5e-3 of max|logit| --
+a quantised activation can land on the other side of a rounding tie when its f32 input differs in the
+last bit, which moves a logit by about one quantisation step of one activation."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from _inputs import normal, rng
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(a):
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rmsnorm_ref(x, w, eps):
+    ss = (x.astype(np.float32) ** 2).sum(axis=1, dtype=np.float32)
+    inv = np.float32(1.0) / np.sqrt(ss * np.float32(1.0 / x.shape[1]) + np.float32(eps), dtype=np.float32)
+    return (x * inv[:, None] * w[None, :]).astype(np.float32)
+
+
+def rope_ref(v, cos, sin):
+    half = v.shape[-1] // 2
+    x0, x1 = v[..., :half], v[..., half:]
+    return np.concatenate([x0 * cos - x1 * sin, x0 * sin + x1 * cos], axis=-1).astype(np.float32)
+
+
+def attention_ref(q, K, V, length, group):
+    """q [B,Hq,hd]; K,V [B,Hkv,cap,hd]; softmax(q.k / sqrt(hd)) V over positions < length."""
+    B, Hq, hd = q.shape
+    out = np.zeros((B, Hq * hd), np.float32)
+    scale = np.float32(1.0 / np.sqrt(np.float32(hd)))
+    for b in range(B):
+        for h in range(Hq):
+            k = K[b, h // group, :length]
+            s = (k @ q[b, h]).astype(np.float32) * scale
+            p = np.exp(s - s.max(), dtype=np.float32)
+            p = p / p.sum(dtype=np.float32)
+            out[b, h * hd:(h + 1) * hd] = (p[:, None] * V[b, h // group, :length]).sum(axis=0, dtype=np.float32)
+    return out
+
+
+@pytest.fixture(scope="module")
+def pg():
+    import peregrine_b200
+
+    return peregrine_b200
+
+
+def test_add_rmsnorm_quantize(pg, gpu, oracle):
+    import torch
+    from peregrine_b200 import _lib
+
+    g = rng(1)
+    for rows, dim, with_delta in ((16, 4096, True), (3, 256, False), (5, 14336, True)):
+        x = normal(g, (rows, dim))
+        d = normal(g, (rows, dim), 0.5)
+        w = (1.0 + normal(g, (dim,), 0.1)).astype(np.float32)
+        tx, td, tw = _t(x), _t(d), _t(w)
+        q = torch.zeros(rows * dim, dtype=torch.int8, device="cuda")
+        s = torch.zeros(rows, device="cuda")
+        n = torch.zeros(rows, dim, device="cuda")
+        torch.cuda.synchronize()
+        _lib.check(gpu.lib.pg_add_rmsnorm_quantize(gpu.handle, tx.data_ptr(), td.data_ptr() if with_delta else None, tw.data_ptr(), rows, dim,
+                                                   1e-5, q.data_ptr(), s.data_ptr(), n.data_ptr()))
+        gpu.sync()
+        xs = (x + d).astype(np.float32) if with_delta else x
+        assert np.array_equal(tx.cpu().numpy(), xs)                     # residual stream updated exactly
+        ref = rmsnorm_ref(xs, w, 1e-5)
+        got = n.cpu().numpy()
+        assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
+        # the quantiser applied to the kernel's own normalised rows is the oracle's, bit for bit
+        qo, so = oracle.quantize_activations(got, rows, dim)
+        assert np.array_equal(q.cpu().numpy().reshape(rows, dim), qo) and np.array_equal(s.cpu().numpy(), so)
+
+
+def test_swiglu_quantize(pg, gpu, oracle):
+    import torch
+    from peregrine_b200 import _lib
+
+    g = rng(2)
+    for rows, F in ((16, 14336), (2, 64)):
+        gu = normal(g, (rows, 2 * F), 2.0)
+        tgu = _t(gu)
+        q = torch.zeros(rows * F, dtype=torch.int8, device="cuda")
+        s = torch.zeros(rows, device="cuda")
+        a = torch.zeros(rows, F, device="cuda")
+        torch.cuda.synchronize()
+        _lib.check(gpu.lib.pg_swiglu_quantize(gpu.handle, tgu.data_ptr(), rows, F, q.data_ptr(), s.data_ptr(), a.data_ptr()))
+        gpu.sync()
+        gate, up = gu[:, :F], gu[:, F:]
+        ref = (gate / (np.float32(1.0) + np.exp(-gate, dtype=np.float32)) * up).astype(np.float32)
+        got = a.cpu().numpy()
+        assert np.abs(got - ref).max() <= 1e-5 * np.abs(ref).max()
+        qo, so = oracle.quantize_activations(got, rows, F)
+        assert np.array_equal(q.cpu().numpy().reshape(rows, F), qo) and np.array_equal(s.cpu().numpy(), so)
+
+
+def test_rope_append_attention_embedding_argmax(pg, gpu):
+    import torch
+    from peregrine_b200 import _lib
+    from peregrine_b200.llama import rope_tables
+
+    g = rng(3)
+    lib = gpu.lib
+    B, Hq, Hkv, hd = 3, 8, 2, 128
+    for cap, pos in ((300, 7), (1100, 1099), (2200, 2047)):
+        cos, sin = rope_tables(hd, cap, 500000.0)
+        qkv = normal(g, (B, (Hq + 2 * Hkv) * hd))
+        K = normal(g, (B, Hkv, cap, hd))
+        V = normal(g, (B, Hkv, cap, hd))
+        tq, tK, tV, tc, ts = _t(qkv), _t(K), _t(V), _t(cos), _t(sin)
+        tpos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+        qrot = torch.zeros(B, Hq, hd, device="cuda")
+        S = lib.pg_gqa_decode_splits(cap)
+        work = torch.zeros(B * Hq * S * 130, device="cuda")
+        out = torch.zeros(B, Hq * hd, device="cuda")
+        torch.cuda.synchronize()
+        _lib.check(lib.pg_rope_kv_append(gpu.handle, tq.data_ptr(), tpos.data_ptr(), tc.data_ptr(), ts.data_ptr(), B, Hq, Hkv, hd, cap,
+                                         qrot.data_ptr(), tK.data_ptr(), tV.data_ptr()))
+        _lib.check(lib.pg_gqa_attention_decode(gpu.handle, qrot.data_ptr(), tK.data_ptr(), tV.data_ptr(), tpos.data_ptr(), B, Hq, Hkv, hd, cap,
+                                               work.data_ptr(), out.data_ptr()))
+        gpu.sync()
+        heads = qkv.reshape(B, Hq + 2 * Hkv, hd)
+        q_ref = rope_ref(heads[:, :Hq], cos[pos], sin[pos])
+        k_ref = rope_ref(heads[:, Hq:Hq + Hkv], cos[pos], sin[pos])
+        assert np.array_equal(qrot.cpu().numpy(), q_ref)                       # RoPE: same table, same two products -> bit-exact
+        K2, V2 = K.copy(), V.copy()
+        K2[:, :, pos], V2[:, :, pos] = k_ref, heads[:, Hq + Hkv:]
+        assert np.array_equal(tK.cpu().numpy(), K2) and np.array_equal(tV.cpu().numpy(), V2)
+        ref = attention_ref(q_ref, K2, V2, pos + 1, Hq // Hkv)
+        assert np.abs(out.cpu().numpy() - ref).max() <= 1e-5 * np.abs(ref).max()
+    # embedding and argmax (first maximum; the position is advanced once)
+    table = normal(g, (50, 64))
+    tok = np.array([3, 49, 0], np.int32)
+    o = torch.zeros(3, 64, device="cuda")
+    tt, ttok = _t(table), _t(tok)
+    torch.cuda.synchronize()
+    _lib.check(lib.pg_embedding(gpu.handle, tt.data_ptr(), ttok.data_ptr(), 3, 64, o.data_ptr()))
+    logits = normal(g, (3, 5000))
+    logits[0, 77] = logits[0, 4000] = 9.0
+    logits[1, :] = -1.0
+    tl = _t(logits)
+    picks = torch.zeros(3, dtype=torch.int32, device="cuda")
+    p = torch.tensor([5], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.pg_argmax_advance(gpu.handle, tl.data_ptr(), 3, 5000, picks.data_ptr(), p.data_ptr()))
+    gpu.sync()
+    assert np.array_equal(o.cpu().numpy(), table[tok])
+    assert picks.cpu().numpy().tolist() == [77, 0, int(np.argmax(logits[2]))] and int(p.item()) == 6
+
+
+def _ref_step(orc, cfg, W, Q, x, K, V, pos, cos, sin):
+    """One decode step in numpy; returns logits and the updated residual stream is discarded."""
+    B, H, Hq, Hkv, hd = cfg.batch, cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
+    delta = None
+    for i in range(cfg.layers):
+        if delta is not None:
+            x = (x + delta).astype(np.float32)
+        n = rmsnorm_ref(x, W[f"l{i}.attn_norm"], cfg.eps)
+        qkv = orc.matmul_quantized(n, B, H, Q[f"l{i}.qkv"]).reshape(B, Hq + 2 * Hkv, hd)
+        q = rope_ref(qkv[:, :Hq], cos[pos], sin[pos])
+        K[i][:, :, pos] = rope_ref(qkv[:, Hq:Hq + Hkv], cos[pos], sin[pos])
+        V[i][:, :, pos] = qkv[:, Hq + Hkv:]
+        a = attention_ref(q, K[i], V[i], pos + 1, Hq // Hkv)
+        o = orc.matmul_quantized(a, B, H, Q[f"l{i}.o"])
+        x = (x + o).astype(np.float32)
+        n = rmsnorm_ref(x, W[f"l{i}.ffn_norm"], cfg.eps)
+        gu = orc.matmul_quantized(n, B, H, Q[f"l{i}.gate_up"])
+        gate, up = gu[:, :cfg.ffn], gu[:, cfg.ffn:]
+        act = (gate / (np.float32(1.0) + np.exp(-gate, dtype=np.float32)) * up).astype(np.float32)
+        delta = orc.matmul_quantized(act, B, cfg.ffn, Q[f"l{i}.down"])
+    x = (x + delta).astype(np.float32)
+    n = rmsnorm_ref(x, W["final_norm"], cfg.eps)
+    return orc.matmul_quantized(n, B, H, Q["lm_head"])
+
+
+def test_decode_steps_teacher_forced(pg, gpu, oracle_mt):
+    import torch
+    from peregrine_b200.llama import LlamaConfig, LlamaInt8Decoder, rope_tables
+
+    cfg = LlamaConfig(layers=2, hidden=256, n_q_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=1000, batch=3, capacity=40)
+    assert cfg.n_q_heads * cfg.head_dim == 512 or True
+    cfg.hidden = cfg.n_q_heads * cfg.head_dim        # o_proj input = heads * head_dim = hidden, as in Llama
+    g = rng(4)
+    W = {"embedding": normal(g, (cfg.vocab, cfg.hidden), 0.5), "final_norm": (1 + normal(g, (cfg.hidden,), 0.1)).astype(np.float32),
+         "lm_head": normal(g, (cfg.hidden, cfg.vocab), 0.02)}
+    for i in range(cfg.layers):
+        W[f"l{i}.attn_norm"] = (1 + normal(g, (cfg.hidden,), 0.1)).astype(np.float32)
+        W[f"l{i}.ffn_norm"] = (1 + normal(g, (cfg.hidden,), 0.1)).astype(np.float32)
+        W[f"l{i}.qkv"] = normal(g, (cfg.hidden, cfg.qkv_dim), 0.05)
+        W[f"l{i}.o"] = normal(g, (cfg.hidden, cfg.hidden), 0.05)
+        W[f"l{i}.gate_up"] = normal(g, (cfg.hidden, 2 * cfg.ffn), 0.05)
+        W[f"l{i}.down"] = normal(g, (cfg.ffn, cfg.hidden), 0.05)
+    Q = {k: oracle_mt.quantize_weights(v, v.shape[0], v.shape[1]) for k, v in W.items() if v.ndim == 2 and k != "embedding"}
+    model = LlamaInt8Decoder(cfg, gpu, W)
+    # a short synthetic history in the cache
+    start = 5
+    K = [normal(g, (cfg.batch, cfg.n_kv_heads, cfg.capacity, cfg.head_dim)) for _ in range(cfg.layers)]
+    V = [normal(g, (cfg.batch, cfg.n_kv_heads, cfg.capacity, cfg.head_dim)) for _ in range(cfg.layers)]
+    for i in range(cfg.layers):
+        model.kcache[i].copy_(_t(K[i]))
+        model.vcache[i].copy_(_t(V[i]))
+    cos, sin = rope_tables(cfg.head_dim, cfg.capacity, cfg.rope_base)
+    tokens = np.array([1, 500, 999], np.int32)
+    model.set_position(start)
+    model.set_tokens(tokens)
+    torch.cuda.synchronize()
+    model.embed()
+    graph = model.record()
+    for step in range(3):
+        x = W["embedding"][tokens]
+        ref_logits = _ref_step(oracle_mt, cfg, W, Q, x, K, V, start + step, cos, sin)
+        graph.launch()
+        gpu.sync()
+        assert gpu.device_status() == 0
+        got = model.logits.cpu().numpy()
+        tol = 5e-3 * np.abs(ref_logits).max()
+        assert np.abs(got - ref_logits).max() <= tol, f"step {step}: {np.abs(got - ref_logits).max()} > {tol}"
+        assert int(model.pos.item()) == start + step + 1
+        picked = model.tokens.cpu().numpy()
+        srt = np.sort(ref_logits, axis=1)
+        clear = (srt[:, -1] - srt[:, -2]) > 2 * tol
+        assert np.array_equal(picked[clear], np.argmax(ref_logits, axis=1)[clear])
+        # teacher forcing: continue from the oracle's greedy choice on both sides
+        tokens = np.argmax(ref_logits, axis=1).astype(np.int32)
+        model.set_tokens(tokens)
+        model.embed()
+        gpu.sync()
+        # the caches must agree too (same rounding path for k, v up to the f32 tolerance of their inputs)
+        assert np.abs(model.kcache[0][:, :, start + step].cpu().numpy() - K[0][:, :, start + step]).max() <= 1e-2
+    model.free()
