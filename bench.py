@@ -461,6 +461,8 @@ def run_ours(args):
         }
         if args.extra:
             line["also"] = extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks)
+        if world == 1 and not args.no_llama:
+            line.setdefault("also", {})["llama8b_int8_decode"] = llama_decode_measurement(gpu, torch, stream, dev, hbm_peak)
     if world > 1:
         dist.barrier()
         if exs:
@@ -541,6 +543,76 @@ def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
     return out
 
 
+def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmup=8, layers=32):
+    """Llama-3-8B-shape int8 decode stack: 32 layers, hidden 4096, GQA 32/8 heads of 128, SwiGLU 14336,
+    vocab 128256, all linears ~N(0,0.02) quantised per column, batch 16, KV cache pre-filled with N(0,1)
+    to context 2048, greedy decode of `steps` tokens from one recorded graph."""
+    from peregrine_b200.llama import LlamaConfig, LlamaInt8Decoder
+
+    cfg = LlamaConfig(layers=layers, capacity=2048 + 128)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4000)
+
+    class Lazy(dict):
+        """weights are drawn on the device when the model asks for them, so only one f32 matrix lives at a time"""
+
+        def __getitem__(self, k):
+            if k == "embedding":
+                return torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=dev) * 0.02
+            if k.endswith("norm"):
+                return torch.ones(cfg.hidden, device=dev)            # nn.rs:569: RMSNorm weights start at 1
+            shape = {"lm_head": (cfg.hidden, cfg.vocab), "qkv": (cfg.hidden, cfg.qkv_dim), "o": (cfg.hidden, cfg.hidden),
+                     "gate_up": (cfg.hidden, 2 * cfg.ffn), "down": (cfg.ffn, cfg.hidden)}[k.split(".")[-1]]
+            return torch.randn(*shape, generator=gen, device=dev) * 0.02
+
+    with torch.cuda.stream(stream):
+        model = LlamaInt8Decoder(cfg, gpu, Lazy(), device_index=dev.index)
+        ctx0 = 2048
+        for i in range(cfg.layers):
+            model.kcache[i, :, :, :ctx0].normal_(generator=gen)
+            model.vcache[i, :, :, :ctx0].normal_(generator=gen)
+        model.set_position(ctx0)
+        model.set_tokens(np.random.Generator(np.random.PCG64(4000)).integers(0, cfg.vocab, cfg.batch).astype(np.int32))
+        torch.cuda.synchronize()
+        model.embed()
+        graph = model.record()
+        for _ in range(warmup):
+            graph.launch()
+        stream.synchronize()
+        model.set_position(ctx0)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.launch()
+        e1.record(stream)
+        stream.synchronize()
+        ms = e0.elapsed_time(e1)
+        assert gpu.device_status() == 0
+        # end to end: tokens leave and enter through host memory every step
+        host_tok = torch.zeros(cfg.batch, dtype=torch.int32).pin_memory()
+        model.set_position(ctx0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            graph.launch()
+            host_tok.copy_(model.tokens, non_blocking=True)
+            stream.synchronize()
+        e2e_s = time.perf_counter() - t0
+    mean_len = ctx0 + (steps + 1) / 2.0
+    bytes_per_step = model.weight_bytes() + model.kv_bytes(int(mean_len))
+    out = {"tok_s": cfg.batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps, "batch": cfg.batch, "context": ctx0,
+           "layers": cfg.layers, "kernels_per_step": graph.kernels,
+           "bytes_per_step": bytes_per_step, "weight_bytes": model.weight_bytes(), "kv_bytes_mean": model.kv_bytes(int(mean_len)),
+           "hbm_gbs": bytes_per_step / (ms / steps * 1e-3) / 1e9, "frac_of_measured_hbm": bytes_per_step / (ms / steps * 1e-3) / 1e9 / hbm_peak,
+           "e2e_tok_s": cfg.batch * steps / e2e_s}
+    graph.free()
+    model.free()
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -549,6 +621,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extra", action="store_true", help="also time the prefill GEMM and the GGUF products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-llama", action="store_true", help="skip the Llama-8B-shape decode stack measurement (N = 1 only)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: all-gather by peer stores recorded in the step graph (default) or eager NCCL")
     args = ap.parse_args()
