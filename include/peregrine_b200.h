@@ -64,10 +64,12 @@ typedef enum pg_gguf_type { PG_GGUF_Q4_0 = 2, PG_GGUF_Q4_1 = 3, PG_GGUF_Q8_0 = 8
 
 /* Kernel selection for pg_gemm_i8 / pg_matmul_quantized_algo. */
 typedef enum pg_gemm_algo {
-    PG_ALGO_AUTO = 0,      /* M <= 64: streaming kernel; otherwise tcgen05 */
+    PG_ALGO_AUTO = 0,      /* M <= 16: warp-stream kernel; M <= 64: streaming kernel; otherwise tcgen05 */
     PG_ALGO_NAIVE = 1,     /* one thread per output, dp4a; the on-device checker */
     PG_ALGO_STREAM = 2,    /* bandwidth-bound decode kernel (128-bit loads + int8 MMA), M <= 64 */
-    PG_ALGO_TCGEN05 = 3    /* tcgen05.mma kind::i8, TMEM accumulators, TMA-fed */
+    PG_ALGO_TCGEN05 = 3,   /* tcgen05.mma kind::i8, TMEM accumulators, TMA-fed */
+    PG_ALGO_WSTREAM = 4    /* persistent decode kernel, M <= 16, K % 64 == 0: bulk copies into per-warp rings, activations
+                              resident in shared memory, split-K through an int32 workspace */
 } pg_gemm_algo;
 
 PG_API const char *pg_last_error(void);
@@ -242,7 +244,8 @@ PG_API int32_t pg_rope_kv_append(pg_ctx *ctx, const float *d_qkv, const int32_t 
                                  const float *d_sin, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
                                  float *d_q_rot, float *d_kcache, float *d_vcache);
 /* GQA attention of one new token per sequence (src/attention.rs:141-265), head_dim 128 */
-PG_API int32_t pg_gqa_decode_splits(int64_t cap);
+/* slices of the context per (sequence, KV head); the work buffer of pg_gqa_attention_decode holds B * Hq * S * 130 floats */
+PG_API int32_t pg_gqa_decode_splits(pg_ctx *ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t cap);
 PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
                                        const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
                                        float *d_work, float *d_out);

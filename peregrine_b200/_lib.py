@@ -19,7 +19,7 @@ PG_ERR_UNSUPPORTED = -4
 PG_ERR_DEVICE_TIMEOUT = -5
 
 GGUF_Q4_0, GGUF_Q4_1, GGUF_Q8_0 = 2, 3, 8
-ALGO_AUTO, ALGO_NAIVE, ALGO_STREAM, ALGO_TCGEN05 = 0, 1, 2, 3
+ALGO_AUTO, ALGO_NAIVE, ALGO_STREAM, ALGO_TCGEN05, ALGO_WSTREAM = 0, 1, 2, 3, 4
 
 
 class PeregrineError(RuntimeError):
@@ -95,7 +95,7 @@ SIGNATURES = {
     "pg_add_rmsnorm_quantize": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _vp, _vp, _vp]),
     "pg_swiglu_quantize": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "pg_rope_kv_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
-    "pg_gqa_decode_splits": (_i32, [_i64]),
+    "pg_gqa_decode_splits": (_i32, [_vp, _i64, _i64, _i64, _i64]),
     "pg_gqa_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "pg_embedding": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "pg_argmax_advance": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
@@ -122,7 +122,7 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    for name in ("pg_tune_stream_ng", "pg_tune_stream_depth", "pg_tune_stream_carveout", "pg_tune_stream_split", "pg_tune_tcgen05_bn", "pg_tune_tcgen05_pair", "pg_tune_gguf_simple", "pg_tune_gguf_rows"):
+    for name in ("pg_tune_stream_ng", "pg_tune_stream_depth", "pg_tune_stream_carveout", "pg_tune_stream_split", "pg_tune_wstream_kw", "pg_tune_tcgen05_bn", "pg_tune_tcgen05_pair", "pg_tune_gguf_simple", "pg_tune_gguf_rows"):
         getattr(lib, name).argtypes = [C.c_int]
         getattr(lib, name).restype = None
     _lib = lib

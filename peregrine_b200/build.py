@@ -22,14 +22,14 @@ SOURCES = [
     "pg_api.cu",
     "pg_quantize.cu",
     "pg_gemm_naive.cu",
-    "pg_gemv_w8a8.cu",
+    "pg_gemv_w8a8.cu", "pg_gemv_wstream.cu",
     "pg_gemm_tcgen05.cu",
     "pg_gemm_tcgen05_2cta.cu",
     "pg_gguf.cu",
     "pg_gguf_mma.cu",
     "pg_noalloc.cu",
     "pg_peer.cu",
-    "pg_llama.cu",
+    "pg_llama.cu", "pg_llama_attn.cu",
 ]
 
 NVCC_FLAGS = [

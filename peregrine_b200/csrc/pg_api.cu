@@ -50,6 +50,22 @@ int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes)
     return PG_OK;
 }
 
+int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes)
+{
+    if (bytes <= ctx->splitk_bytes) return PG_OK;
+    if (ctx->capturing) PG_FAIL(PG_ERR_INVALID, "split-K workspace would have to grow while a graph is being recorded; run the call once before recording");
+    PG_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->splitk) PG_CUDA(cudaFree(ctx->splitk));
+    ctx->splitk = nullptr;
+    ctx->splitk_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    want = (want + 255) & ~(size_t)255;
+    PG_CUDA(cudaMalloc(&ctx->splitk, want));
+    PG_CUDA(cudaMemsetAsync(ctx->splitk, 0, want, ctx->stream));
+    ctx->splitk_bytes = want;
+    return PG_OK;
+}
+
 int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes)
 {
     if (bytes <= ctx->h_pinned_bytes) return PG_OK;
@@ -143,6 +159,7 @@ int32_t pg_ctx_destroy(pg_ctx *ctx)
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->staging) cudaFree(ctx->staging);
+    if (ctx->splitk) cudaFree(ctx->splitk);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -510,7 +527,11 @@ static int32_t gemm_dispatch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, 
             return pgk_gemm_i8_stream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
         case PG_ALGO_TCGEN05:
             return pgk_gemm_i8_tcgen05(ctx, d_a, d_as, m, k, const_cast<pg_qtensor *>(w), d_y, d_acc);
+        case PG_ALGO_WSTREAM:
+            return pgk_gemm_i8_wstream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
         case PG_ALGO_AUTO:
+            if (aligned && pgk_gemm_i8_wstream_supports(m, k, n))
+                return pgk_gemm_i8_wstream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
             if (aligned && pgk_gemm_i8_stream_supports(m, k, n))
                 return pgk_gemm_i8_stream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
             if (aligned && pgk_gemm_i8_tcgen05_supports(m, k, n))

@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     // [D][NG][THREADS] uint4, reused as int32 [WARPS][ROWS][NT] for the reduction; then, never
     // aliased with the FIFO, int32 [S-1][ROWS][NT] that the other CTAs of the cluster write into
     extern __shared__ uint4 fifo[];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr uint32_t FIFO_BYTES = (uint32_t)D * NG * THREADS * 16;
     constexpr uint32_t RED_BYTES = (uint32_t)WARPS * ROWS * NT * 4;
     constexpr uint32_t XBUF_OFF = FIFO_BYTES > RED_BYTES ? FIFO_BYTES : RED_BYTES;
@@ -139,7 +140,6 @@ __global__ void __launch_bounds__(WARPS * 32)
 
     // Everything above reads only the weights.  The activations come from the preceding kernel.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int8_t *alo[MB], *ahi[MB];
     bool oklo[MB], okhi[MB];

@@ -112,8 +112,8 @@ __global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restric
                                                            float *__restrict__ row_scale)
 {
     __shared__ float red[32];
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int g = blockIdx.x;  // row inside the tile
     const int m = m0 + g;
     const int nblk = K >> 5;
@@ -219,8 +219,8 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     for (int i = 0; i < D - 1; i++) issue();
 
     // the activation fragments come from the preceding kernel
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     uint4 xh[G_SLICE], xl[G_SLICE];
 #pragma unroll

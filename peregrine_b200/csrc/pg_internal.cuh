@@ -53,6 +53,10 @@ struct pg_ctx {
     // kernels launched inside those calls may resize or overwrite
     void *staging = nullptr;
     size_t staging_bytes = 0;
+    // zero-initialised workspace of the split-K paths (int32 partial sums + arrival counters); every
+    // kernel that uses it leaves it zeroed again
+    void *splitk = nullptr;
+    size_t splitk_bytes = 0;
     int32_t *d_status = nullptr;  // device status word for bounded waits
     void *h_pinned = nullptr;     // pinned staging for *_host calls
     size_t h_pinned_bytes = 0;
@@ -91,6 +95,7 @@ struct pg_gguf_weight {
 int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes);
+int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes);
 
 // ------------------------------------------------------- kernel launchers ----
 // pg_quantize.cu
@@ -105,6 +110,15 @@ int32_t pgk_gemm_i8_naive(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int
 bool pgk_gemm_i8_stream_supports(int64_t m, int64_t k, int64_t n);
 int32_t pgk_gemm_i8_stream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
                            const float *d_ws, int64_t n, float *d_y, int32_t *d_acc);
+// pg_gemv_wstream.cu
+bool pgk_gemm_i8_wstream_supports(int64_t m, int64_t k, int64_t n);
+int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                            const float *d_ws, int64_t n, float *d_y, int32_t *d_acc);
+// pg_llama_attn.cu
+int pgk_gqa_stream_splits(const pg_ctx *ctx, int64_t B, int64_t Hkv, int64_t cap);
+bool pgk_gqa_stream_supports(int64_t G);
+int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, const int32_t *d_pos, int64_t B,
+                              int64_t Hq, int64_t Hkv, int64_t cap, int S, float scale, float *part_o, float *part_ml);
 // pg_gemm_tcgen05.cu
 bool pgk_gemm_i8_tcgen05_supports(int64_t m, int64_t k, int64_t n);
 int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, pg_qtensor *w,

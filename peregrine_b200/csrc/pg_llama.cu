@@ -65,8 +65,8 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
                                                                 float *__restrict__ normed)
 {
     __shared__ float red[32];
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t row = blockIdx.x;
     const int nvec = dim >> 2;
     float4 *xr = reinterpret_cast<float4 *>(x + row * dim);
@@ -120,8 +120,8 @@ __global__ void __launch_bounds__(LT) swiglu_quant_kernel(const float *__restric
                                                            float *__restrict__ scales, float *__restrict__ act_out)
 {
     __shared__ float red[32];
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t row = blockIdx.x;
     const int nvec = F >> 2;
     const float4 *g4 = reinterpret_cast<const float4 *>(gu + row * 2 * F);
@@ -157,8 +157,8 @@ __global__ void rope_kv_append_kernel(const float *__restrict__ qkv, const int *
                                       const float *__restrict__ sin_t, int Hq, int Hkv, int hd, int cap,
                                       float *__restrict__ q_rot, float *__restrict__ kc, float *__restrict__ vc)
 {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = hd >> 1;
     const int pos = *pos_ptr;
     const float *src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + head) * hd;
@@ -193,8 +193,8 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
     extern __shared__ float sm[];  // sc[chunk][G], then red[8][G][HD]
     float *sc = sm;
     float *red = sm + (size_t)chunk * G;
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int split = blockIdx.x, S = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int len = *pos_ptr + 1;
@@ -301,8 +301,8 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
 __global__ void __launch_bounds__(128) gqa_decode_combine_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int Hq,
                                                                   int S, float *__restrict__ out)
 {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int qh = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const float *ml = part_ml + ((int64_t)b * Hq + qh) * S * 2;
     const float *po = part_o + ((int64_t)b * Hq + qh) * S * 128;
@@ -322,8 +322,8 @@ __global__ void __launch_bounds__(128) gqa_decode_combine_kernel(const float *__
 
 __global__ void embedding_kernel(const float *__restrict__ table, const int *__restrict__ tokens, int dim, float *__restrict__ out)
 {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
     const float4 *src = reinterpret_cast<const float4 *>(table + (int64_t)tokens[b] * dim);
     float4 *dst = reinterpret_cast<float4 *>(out + (int64_t)b * dim);
@@ -335,8 +335,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
 {
     __shared__ float bv[32];
     __shared__ int bi[32];
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
     const float *row = logits + (int64_t)b * V;
     float best = -INFINITY;
@@ -433,8 +433,12 @@ PG_API int32_t pg_rope_kv_append(pg_ctx *ctx, const float *d_qkv, const int32_t 
 }
 
 // Attention of one new token per sequence over positions 0..*d_pos (the new one included).
-// d_work: B * Hq * S * 130 floats with S = pg_gqa_decode_splits(cap).
-PG_API int32_t pg_gqa_decode_splits(int64_t cap) { return cap <= 512 ? 1 : (cap <= 2048 ? 4 : 8); }
+// d_work: B * Hq * S * 130 floats with S = pg_gqa_decode_splits(ctx, B, Hq, Hkv, cap).
+PG_API int32_t pg_gqa_decode_splits(pg_ctx *ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t cap)
+{
+    if (ctx && Hkv > 0 && Hq % Hkv == 0 && pgk_gqa_stream_supports(Hq / Hkv)) return pgk_gqa_stream_splits(ctx, B, Hkv, cap);
+    return cap <= 512 ? 1 : (cap <= 2048 ? 4 : 8);
+}
 
 PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
                                        const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_work,
@@ -446,11 +450,17 @@ PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const 
     const int64_t G = Hq / Hkv;
     PG_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, "gqa_attention_decode: %lld query heads per KV head is not supported (1, 2, 4, 8)", (long long)G);
     if (B == 0) return PG_OK;
-    const int S = pg_gqa_decode_splits(cap);
+    const int S = pg_gqa_decode_splits(ctx, B, Hq, Hkv, cap);
     const int chunk = (int)((cap + S - 1) / S);
     const float scale = 1.0f / sqrtf((float)hd);
     float *part_o = d_work;
     float *part_ml = d_work + B * Hq * S * 128;
+    if (pgk_gqa_stream_supports(G)) {
+        int32_t rc = pgk_gqa_decode_stream(ctx, d_q_rot, d_kcache, d_vcache, d_pos, B, Hq, Hkv, cap, S, scale, part_o, part_ml);
+        if (rc) return rc;
+        return launch_pdl(ctx, gqa_decode_combine_kernel, dim3((unsigned)Hq, (unsigned)B), dim3(128), 0, (const float *)part_o,
+                          (const float *)part_ml, (int)Hq, S, d_out);
+    }
     const size_t smem = ((size_t)chunk * G + 8 * G * 128) * sizeof(float);
     const dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
     int32_t rc;

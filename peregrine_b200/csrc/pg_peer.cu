@@ -44,8 +44,8 @@ __device__ __forceinline__ unsigned long long globaltimer_ns()
 __global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *__restrict__ slice, int M, int64_t n_local,
                                                                    int64_t n_total, int64_t col0, PeerDst dst, int world, int rank)
 {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t total = (int64_t)M * n_local;
     const bool vec = ((n_local | n_total | col0) & 3) == 0;
     if (vec) {
@@ -83,8 +83,8 @@ __global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *
 // one warp: lane r waits until rank r has delivered this rank's next exchange
 __global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t *ctl, int world, int32_t *status)
 {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x;
     uint32_t want = 0;
     if (lane == 0) want = ++ctl[PG_MAX_PEERS + 1];

@@ -39,8 +39,8 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
     __shared__ float red[32];
     // x comes from the preceding kernel; once this grid runs, the one after it may start its own
     // independent prologue (the product kernel prefetches weights)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t row = blockIdx.x;
     const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols);
     const int64_t nvec = cols >> 2;

@@ -116,7 +116,7 @@ class LlamaInt8Decoder:
         self.gate_up = torch.zeros(B, 2 * c.ffn, dtype=f32, device=dev)
         self.down = torch.zeros(B, c.hidden, dtype=f32, device=dev)
         self.logits = torch.zeros(B, c.vocab, dtype=f32, device=dev)
-        S = self.lib.pg_gqa_decode_splits(c.capacity)
+        S = self.lib.pg_gqa_decode_splits(gpu.handle, B, c.n_q_heads, c.n_kv_heads, c.capacity)
         self.work = torch.zeros(B * c.n_q_heads * S * 130, dtype=f32, device=dev)
         self.graph = None
         torch.cuda.synchronize()   # torch filled the buffers on its own stream; the kernels use the context's

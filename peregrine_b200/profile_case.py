@@ -4,6 +4,7 @@
     python -m peregrine_b200.profile_case --op w8a8 --algo tcgen05 --m 2048 --k 4096 --n 4096
     python -m peregrine_b200.profile_case --op gguf --kind q4_0 --m 1 --k 4096 --n 32768
     python -m peregrine_b200.profile_case --op quant --m 8192 --k 4096
+    python -m peregrine_b200.profile_case --op llama --layers 2 --m 16 --context 2048 --reps 2
 
 Inputs are seeded random values generated on the host; weights for `w8a8` are random int8 (no
 quantisation pass), so start-up stays short.  Prints the mean time per call in microseconds
@@ -21,12 +22,54 @@ from . import _lib
 from .gguf import BLOCK_BYTES, TYPE_BY_NAME, GgufWeight
 from .runtime import GpuContext
 
-ALGOS = {"auto": _lib.ALGO_AUTO, "naive": _lib.ALGO_NAIVE, "stream": _lib.ALGO_STREAM, "tcgen05": _lib.ALGO_TCGEN05}
+ALGOS = {"auto": _lib.ALGO_AUTO, "naive": _lib.ALGO_NAIVE, "stream": _lib.ALGO_STREAM, "tcgen05": _lib.ALGO_TCGEN05, "wstream": _lib.ALGO_WSTREAM}
+
+
+def llama_case(a) -> None:
+    """Eager decode steps (one launch per kernel, batch = --m) of a Llama-3-8B-shaped stack cut to --layers layers."""
+    import torch
+
+    from .llama import LlamaConfig, LlamaInt8Decoder
+
+    dev = torch.device("cuda", 0)
+    cfg = LlamaConfig(layers=a.layers, batch=a.m, capacity=a.context + 64)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1)
+
+    class Lazy(dict):
+        def __getitem__(self, key):
+            if key == "embedding":
+                return torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=dev) * 0.02
+            if key.endswith("norm"):
+                return torch.ones(cfg.hidden, device=dev)
+            shape = {"lm_head": (cfg.hidden, cfg.vocab), "qkv": (cfg.hidden, cfg.qkv_dim), "o": (cfg.hidden, cfg.hidden),
+                     "gate_up": (cfg.hidden, 2 * cfg.ffn), "down": (cfg.ffn, cfg.hidden)}[key.split(".")[-1]]
+            return torch.randn(*shape, generator=gen, device=dev) * 0.02
+
+    gpu = GpuContext(0)
+    model = LlamaInt8Decoder(cfg, gpu, Lazy())
+    model.kcache[:, :, :, :a.context].normal_(generator=gen)
+    model.vcache[:, :, :, :a.context].normal_(generator=gen)
+    model.set_position(a.context)
+    model.set_tokens(np.arange(cfg.batch) * 977 % cfg.vocab)
+    model.embed()
+    model.enqueue_step()
+    gpu.sync()
+    t0 = time.perf_counter()
+    for _ in range(a.reps):
+        model.enqueue_step()
+    gpu.sync()
+    us = (time.perf_counter() - t0) / a.reps * 1e6
+    status = gpu.device_status()
+    print(f"op=llama layers={cfg.layers} batch={cfg.batch} context={a.context}: {us:.1f} us/step eager, device_status={status}")
+    model.free()
+    if status != 0:
+        raise SystemExit(1)
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["w8a8", "gguf", "quant"], default="w8a8")
+    ap.add_argument("--op", choices=["w8a8", "gguf", "quant", "llama"], default="w8a8")
     ap.add_argument("--algo", choices=list(ALGOS), default="auto")
     ap.add_argument("--kind", choices=list(TYPE_BY_NAME), default="q4_0")
     ap.add_argument("--m", type=int, default=16)
@@ -37,7 +80,11 @@ def main() -> None:
     ap.add_argument("--ng", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--pair", type=int, default=0, help="tcgen05: 0 heuristic, 1 one CTA per tile, 2 CTA pairs")
+    ap.add_argument("--layers", type=int, default=2, help="llama: decoder layers (Llama-3-8B shapes otherwise)")
+    ap.add_argument("--context", type=int, default=2048, help="llama: KV positions already filled")
     a = ap.parse_args()
+    if a.op == "llama":
+        return llama_case(a)
 
     gpu = GpuContext(0)
     lib = gpu.lib

@@ -113,8 +113,11 @@ def test_rope_append_attention_embedding_argmax(pg, gpu):
 
     g = rng(3)
     lib = gpu.lib
-    B, Hq, Hkv, hd = 3, 8, 2, 128
-    for cap, pos in ((300, 7), (1100, 1099), (2200, 2047)):
+    hd = 128
+    # 4 and 8 query heads per KV head take the streaming kernel, 1 and 2 the chunked one; first position, ragged slices,
+    # more (sequence, head, slice) units than the GPU has warps
+    for B, Hq, Hkv, cap, pos in ((3, 8, 2, 300, 7), (3, 8, 2, 1100, 1099), (3, 8, 2, 2200, 2047), (2, 16, 2, 700, 0), (2, 16, 2, 700, 650),
+                                 (1, 4, 2, 600, 333), (2, 2, 2, 300, 299), (40, 32, 8, 200, 130), (16, 32, 8, 2176, 2048)):
         cos, sin = rope_tables(hd, cap, 500000.0)
         qkv = normal(g, (B, (Hq + 2 * Hkv) * hd))
         K = normal(g, (B, Hkv, cap, hd))
@@ -122,7 +125,7 @@ def test_rope_append_attention_embedding_argmax(pg, gpu):
         tq, tK, tV, tc, ts = _t(qkv), _t(K), _t(V), _t(cos), _t(sin)
         tpos = torch.tensor([pos], dtype=torch.int32, device="cuda")
         qrot = torch.zeros(B, Hq, hd, device="cuda")
-        S = lib.pg_gqa_decode_splits(cap)
+        S = lib.pg_gqa_decode_splits(gpu.handle, B, Hq, Hkv, cap)
         work = torch.zeros(B * Hq * S * 130, device="cuda")
         out = torch.zeros(B, Hq * hd, device="cuda")
         torch.cuda.synchronize()

@@ -12,7 +12,7 @@ from _inputs import bits_equal, linear_inputs, normal, rng
 
 pytestmark = pytest.mark.gpu
 
-ALGOS = {"naive": 1, "stream": 2, "tcgen05": 3}
+ALGOS = {"naive": 1, "stream": 2, "tcgen05": 3, "wstream": 4}
 
 
 @pytest.fixture(scope="module")
@@ -196,7 +196,34 @@ def test_single_linear_config(pg, gpu, oracle_mt):
 def test_decode_gemv_sweep(pg, gpu, oracle_mt, idx, m, k, n):
     """Llama-3-8B projection shapes, activations with 1 % outlier channels (x20)."""
     x, w = linear_inputs(m, k, n, 1000 + idx, outliers=True)
-    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["stream", "tcgen05"])
+    # 16 rows of K = 14336 do not fit in the warp-stream kernel's shared memory
+    algos = ["stream", "tcgen05"] + ([] if (m > 8 and k > 4096) else ["wstream"])
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, algos)
+
+
+@pytest.mark.parametrize("m,k,n", [
+    (1, 64, 1), (2, 128, 9), (8, 192, 8), (9, 64, 17), (16, 576, 24), (16, 4096 + 64, 100), (5, 1088, 1000), (12, 2048, 130),
+    (3, 8192, 40), (8, 8192 + 128, 33), (16, 4160, 3000), (8, 14336, 100), (2, 65536 - 64, 20), (7, 512, 2369 * 8 + 3),
+])
+def test_warp_stream_kernel_ragged_shapes(pg, gpu, oracle_mt, m, k, n):
+    """Edges of the persistent decode kernel: N not a multiple of the 8-column tile, K not a multiple of the 512-byte
+    ring segment, K beyond one shared-memory range of activations (forced split), more tiles than warps."""
+    x, w = linear_inputs(m, k, n, 177 + m + n)
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive", "wstream"])
+    assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("kw", [1, 2, 4, 8, 16])
+def test_warp_stream_every_k_split(pg, gpu, oracle_mt, kw):
+    """1..16 warps share a tile, each with its own part of K (uneven last parts included); run twice back to back."""
+    gpu.lib.pg_tune_wstream_kw(kw)
+    try:
+        for m, k, n in ((1, 4096, 520), (16, 4096, 72), (7, 1984, 33), (16, 2048, 3000), (4, 14336, 264), (8, 14336, 40)):
+            x, w = linear_inputs(m, k, n, 800 + kw + m)
+            _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["wstream", "wstream"])
+        assert gpu.device_status() == 0
+    finally:
+        gpu.lib.pg_tune_wstream_kw(0)
 
 
 @pytest.mark.parametrize("m,k,n", [
