@@ -248,7 +248,9 @@ PG_API int32_t pg_rope_kv_append(pg_ctx *ctx, const float *d_qkv, const int32_t 
 PG_API int32_t pg_gqa_decode_splits(pg_ctx *ctx, int64_t B, int64_t Hq, int64_t Hkv, int64_t cap);
 PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
                                        const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
-                                       float *d_work, float *d_out);
+                                       float *d_work, float *d_out /* [B, Hq*hd] f32, nullable when the int8 form is taken */,
+                                       int8_t *d_out_i8 /* nullable: the same rows through the activation quantiser */,
+                                       float *d_out_scales /* [B], with d_out_i8 */);
 /* embedding gather (src/nn.rs:217-227); greedy argmax, first maximum (examples/llama/main.rs:15-26) */
 PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim,
                             float *d_out);

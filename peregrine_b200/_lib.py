@@ -96,7 +96,7 @@ SIGNATURES = {
     "pg_swiglu_quantize": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "pg_rope_kv_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "pg_gqa_decode_splits": (_i32, [_vp, _i64, _i64, _i64, _i64]),
-    "pg_gqa_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "pg_gqa_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "pg_embedding": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "pg_argmax_advance": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "pg_matmul_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),

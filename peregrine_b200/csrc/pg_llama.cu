@@ -24,6 +24,52 @@ namespace {
 
 constexpr int LT = 256;  // threads per CTA of the row kernels
 
+// ---- a row spread over the CTAs of a thread-block cluster ----------------------------------------
+// With a handful of sequences per step a kernel of one CTA per row leaves most SMs idle and is bound
+// by the latency of one CTA walking its row.  The row kernels below therefore cut a row into `cs`
+// column segments (cs = cluster size, 1..8), one CTA each, and exchange their partial sums / maxima
+// through distributed shared memory: every CTA stores its value into slot [rank] of every peer, one
+// cluster barrier, every CTA reduces the cs slots itself.
+__device__ __forceinline__ uint32_t cl_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cl_size()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cl_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cl_store_f32(float *local_slot, uint32_t cta, float v)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_slot)), "r"(cta));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cl_store_s32(int *local_slot, uint32_t cta, int v)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_slot)), "r"(cta));
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(remote), "r"(v) : "memory");
+}
+// v: this CTA's value (the same in every thread).  slots: 8 floats of shared memory not used by another exchange in flight.
+template <bool MAX>
+__device__ __forceinline__ float cl_allreduce(float v, float *slots, uint32_t cs, uint32_t rank)
+{
+    if (cs == 1) return v;
+    if (threadIdx.x < cs) cl_store_f32(slots + rank, threadIdx.x, v);
+    cl_sync();
+    float r = slots[0];
+    for (uint32_t i = 1; i < cs; i++) r = MAX ? fmaxf(r, slots[i]) : r + slots[i];
+    return r;
+}
+
 __device__ __forceinline__ float block_sum(float v, float *smem)
 {
 #pragma unroll
@@ -57,7 +103,7 @@ __device__ __forceinline__ uint32_t pack_i8x4(float a, float b, float c, float d
     return (uint32_t)(qa & 0xff) | ((uint32_t)(qb & 0xff) << 8) | ((uint32_t)(qc & 0xff) << 16) | ((uint32_t)(qd & 0xff) << 24);
 }
 
-// one CTA per row; VPT float4 per thread (dim <= LT * 4 * VPT)
+// a cluster of cs CTAs per row, each with dim / cs columns; VPT float4 per thread (dim / cs <= LT * 4 * VPT)
 template <int VPT>
 __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict__ x, const float *__restrict__ delta,
                                                                 const float *__restrict__ w, int dim, float eps,
@@ -65,10 +111,13 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
                                                                 float *__restrict__ normed)
 {
     __shared__ float red[32];
+    __shared__ float xs[8], xm[8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int64_t row = blockIdx.x;
-    const int nvec = dim >> 2;
+    const uint32_t cs = cl_size(), rank = cl_rank();
+    const int64_t row = blockIdx.x / cs;
+    const int nseg = (dim >> 2) / (int)cs;       // float4 per segment
+    const int c0 = (int)rank * nseg;
     float4 *xr = reinterpret_cast<float4 *>(x + row * dim);
     float4 v[VPT];
     float ss = 0.0f;
@@ -76,56 +125,59 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
     for (int i = 0; i < VPT; i++) {
         const int c = i * LT + threadIdx.x;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < nvec) {
-            v[i] = xr[c];
+        if (c < nseg) {
+            v[i] = xr[c0 + c];
             if (delta) {
-                const float4 d = __ldg(reinterpret_cast<const float4 *>(delta + row * dim) + c);
+                const float4 d = __ldg(reinterpret_cast<const float4 *>(delta + row * dim) + c0 + c);
                 v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
-                xr[c] = v[i];
+                xr[c0 + c] = v[i];
             }
             ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
         }
     }
-    ss = block_sum(ss, red);
+    ss = cl_allreduce<false>(block_sum(ss, red), xs, cs, rank);
     const float inv_rms = __fdiv_rn(1.0f, sqrtf(__fmul_rn(ss, __fdiv_rn(1.0f, (float)dim)) + eps));
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const int c = i * LT + threadIdx.x;
-        if (c < nvec) {
-            const float4 ww = __ldg(reinterpret_cast<const float4 *>(w) + c);
+        if (c < nseg) {
+            const float4 ww = __ldg(reinterpret_cast<const float4 *>(w) + c0 + c);
             v[i].x = __fmul_rn(__fmul_rn(v[i].x, inv_rms), ww.x);
             v[i].y = __fmul_rn(__fmul_rn(v[i].y, inv_rms), ww.y);
             v[i].z = __fmul_rn(__fmul_rn(v[i].z, inv_rms), ww.z);
             v[i].w = __fmul_rn(__fmul_rn(v[i].w, inv_rms), ww.w);
-            if (normed) reinterpret_cast<float4 *>(normed + row * dim)[c] = v[i];
+            if (normed) reinterpret_cast<float4 *>(normed + row * dim)[c0 + c] = v[i];
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
         }
     }
-    amax = block_max(amax, red);
+    amax = cl_allreduce<true>(block_max(amax, red), xm, cs, rank);
     const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
     const float inv = __fdiv_rn(1.0f, scale);
-    if (threadIdx.x == 0) scales[row] = scale;
+    if (threadIdx.x == 0 && rank == 0) scales[row] = scale;
     uint32_t *qr = reinterpret_cast<uint32_t *>(q + row * dim);
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const int c = i * LT + threadIdx.x;
-        if (c < nvec) qr[c] = pack_i8x4(v[i].x, v[i].y, v[i].z, v[i].w, inv);
+        if (c < nseg) qr[c0 + c] = pack_i8x4(v[i].x, v[i].y, v[i].z, v[i].w, inv);
     }
 }
 
-// gate_up [rows, 2F]: gate = [:, :F], up = [:, F:]; one CTA per row
+// gate_up [rows, 2F]: gate = [:, :F], up = [:, F:]; a cluster of cs CTAs per row, each with F / cs columns
 template <int VPT>
 __global__ void __launch_bounds__(LT) swiglu_quant_kernel(const float *__restrict__ gu, int F, int8_t *__restrict__ q,
                                                            float *__restrict__ scales, float *__restrict__ act_out)
 {
     __shared__ float red[32];
+    __shared__ float xm[8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int64_t row = blockIdx.x;
-    const int nvec = F >> 2;
-    const float4 *g4 = reinterpret_cast<const float4 *>(gu + row * 2 * F);
-    const float4 *u4 = reinterpret_cast<const float4 *>(gu + row * 2 * F + F);
+    const uint32_t cs = cl_size(), rank = cl_rank();
+    const int64_t row = blockIdx.x / cs;
+    const int nseg = (F >> 2) / (int)cs;
+    const int c0 = (int)rank * nseg;
+    const float4 *g4 = reinterpret_cast<const float4 *>(gu + row * 2 * F) + c0;
+    const float4 *u4 = reinterpret_cast<const float4 *>(gu + row * 2 * F + F) + c0;
     float4 v[VPT];
     float amax = 0.0f;
     auto silu_mul = [](float g, float u) { return __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u); };
@@ -133,22 +185,22 @@ __global__ void __launch_bounds__(LT) swiglu_quant_kernel(const float *__restric
     for (int i = 0; i < VPT; i++) {
         const int c = i * LT + threadIdx.x;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < nvec) {
+        if (c < nseg) {
             const float4 g = __ldg(g4 + c), u = __ldg(u4 + c);
             v[i] = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
-            if (act_out) reinterpret_cast<float4 *>(act_out + row * F)[c] = v[i];
+            if (act_out) reinterpret_cast<float4 *>(act_out + row * F)[c0 + c] = v[i];
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
         }
     }
-    amax = block_max(amax, red);
+    amax = cl_allreduce<true>(block_max(amax, red), xm, cs, rank);
     const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
     const float inv = __fdiv_rn(1.0f, scale);
-    if (threadIdx.x == 0) scales[row] = scale;
-    uint32_t *qr = reinterpret_cast<uint32_t *>(q + row * F);
+    if (threadIdx.x == 0 && rank == 0) scales[row] = scale;
+    uint32_t *qr = reinterpret_cast<uint32_t *>(q + row * F) + c0;
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const int c = i * LT + threadIdx.x;
-        if (c < nvec) qr[c] = pack_i8x4(v[i].x, v[i].y, v[i].z, v[i].w, inv);
+        if (c < nseg) qr[c] = pack_i8x4(v[i].x, v[i].y, v[i].z, v[i].w, inv);
     }
 }
 
@@ -330,18 +382,24 @@ __global__ void embedding_kernel(const float *__restrict__ table, const int *__r
     for (int i = threadIdx.x; i < (dim >> 2); i += blockDim.x) dst[i] = __ldg(src + i);
 }
 
-// one CTA per row; the first maximum wins (examples/llama/main.rs:15-26).  Block 0 also advances the position.
+// a cluster of cs CTAs per row, each scanning V / cs logits; the first maximum wins (examples/llama/main.rs:15-26).
+// The first CTA of row 0 also advances the position.
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ tokens, int *pos_ptr)
 {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    __shared__ float xv[8];
+    __shared__ int xi[8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int b = blockIdx.x;
+    const uint32_t cs = cl_size(), rank = cl_rank();
+    const int b = blockIdx.x / cs;
     const float *row = logits + (int64_t)b * V;
+    const int seg = (V + (int)cs - 1) / (int)cs;
+    const int i0 = (int)rank * seg, i1 = min(V, i0 + seg);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const float v = row[i];
         if (v > best || (v == best && i < idx)) {
             best = v;
@@ -368,9 +426,102 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
                 best = bv[w];
                 idx = bi[w];
             }
+        if (cs > 1) {
+            cl_store_f32(xv + rank, 0, best);     // everything meets in the first CTA of the cluster
+            cl_store_s32(xi + rank, 0, idx);
+        }
+    }
+    if (cs > 1) cl_sync();
+    if (threadIdx.x == 0 && rank == 0) {
+        for (uint32_t c = 1; c < cs; c++)
+            if (xv[c] > best || (xv[c] == best && xi[c] < idx)) {
+                best = xv[c];
+                idx = xi[c];
+            }
         tokens[b] = (idx == 0x7fffffff) ? 0 : idx;   // all-NaN row: the reference keeps index 0
         if (b == 0 && pos_ptr) *pos_ptr += 1;
     }
+}
+
+// Merge of the S partial attention outputs of every (sequence, query head), optionally followed by the per-row int8
+// quantiser of src/quant.rs:97-109 over the whole row [Hq * 128] (what the output projection takes).
+// A cluster of cs CTAs per sequence, each with Hq / cs heads: blockDim = (128, Hq / cs).
+__global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int Hq,
+                                                                  int S, float *__restrict__ out, int8_t *__restrict__ q8,
+                                                                  float *__restrict__ q8_scales)
+{
+    __shared__ float red[32];
+    __shared__ float xm[8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t cs = cl_size(), rank = cl_rank();
+    const int b = blockIdx.x / cs, d = threadIdx.x, qh = (int)rank * blockDim.y + threadIdx.y;
+    const float *ml = part_ml + ((int64_t)b * Hq + qh) * S * 2;
+    const float *po = part_o + ((int64_t)b * Hq + qh) * S * 128;
+    float m = -INFINITY;
+    for (int s = 0; s < S; s++) m = fmaxf(m, ml[2 * s]);
+    float denom = 0.0f, acc = 0.0f;
+    for (int s = 0; s < S; s++) {
+        const float l = ml[2 * s + 1];
+        if (l > 0.0f) {
+            const float e = expf(ml[2 * s] - m);
+            denom = fmaf(e, l, denom);
+            acc = fmaf(e, po[(int64_t)s * 128 + d], acc);
+        }
+    }
+    const float o = (denom > 0.0f) ? __fdiv_rn(acc, denom) : 0.0f;
+    const int64_t at = ((int64_t)b * Hq + qh) * 128 + d;
+    if (out) out[at] = o;
+    if (!q8) return;                              // uniform over the cluster: nobody waits at the barrier below
+    float amax = fabsf(o);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const int tid = threadIdx.y * 128 + threadIdx.x, nwarps = (blockDim.x * blockDim.y) >> 5;
+    if ((tid & 31) == 0) red[tid >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+    for (int i = 1; i < nwarps; i++) amax = fmaxf(amax, red[i]);
+    if (cs > 1) {
+        if (tid < (int)cs) cl_store_f32(xm + rank, tid, amax);
+        cl_sync();
+        amax = xm[0];
+        for (uint32_t i = 1; i < cs; i++) amax = fmaxf(amax, xm[i]);
+    }
+    const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
+    const float inv = __fdiv_rn(1.0f, scale);
+    if (tid == 0 && rank == 0) q8_scales[b] = scale;
+    q8[at] = (int8_t)pg_round_clamp_i8(__fmul_rn(o, inv));
+}
+
+template <typename K, typename... Args>
+int32_t launch_pdl_cluster(pg_ctx *ctx, K kern, dim3 grid, dim3 block, size_t smem, int cs, Args... args)
+{
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cs;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = cs > 1 ? 2 : 1;
+    PG_CUDA(cudaLaunchKernelEx(&cfg, kern, args...));
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
+// CTAs per row for the row kernels: as many (up to 8) as keep the grid within about two CTAs per SM, divide the row's
+// `units` evenly and leave each CTA at least `min_units`.
+int row_cluster(const pg_ctx *ctx, int64_t rows, int64_t units, int64_t min_units)
+{
+    int cs = 8;
+    while (cs > 1 && (rows * cs > 2 * (int64_t)ctx->sm_count || units % cs != 0 || units / cs < min_units)) cs >>= 1;
+    return cs;
 }
 
 template <typename K, typename... Args>
@@ -403,9 +554,11 @@ PG_API int32_t pg_add_rmsnorm_quantize(pg_ctx *ctx, float *d_x, const float *d_d
     PG_REQUIRE(ctx && d_x && d_w && d_q && d_scales, "add_rmsnorm_quantize: null pointer");
     PG_REQUIRE(rows >= 0 && dim > 0 && dim % 4 == 0 && dim <= LT * 4 * 16, "add_rmsnorm_quantize: dim must be a multiple of 4, at most %d", LT * 64);
     if (rows == 0) return PG_OK;
-    const dim3 g((unsigned)rows), b(LT);
-    if (dim <= LT * 16) return launch_pdl(ctx, add_rmsnorm_quant_kernel<4>, g, b, 0, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
-    return launch_pdl(ctx, add_rmsnorm_quant_kernel<16>, g, b, 0, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
+    const int cs = row_cluster(ctx, rows, dim / 4, 128);
+    const dim3 g((unsigned)(rows * cs)), b(LT);
+    if (dim / cs <= LT * 4) return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<1>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
+    if (dim / cs <= LT * 16) return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<4>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
+    return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<16>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
 }
 
 // gate_up [rows, 2F] -> q [rows, F] i8 + scales [rows] of silu(gate) * up; `act` (nullable) receives the f32 rows.
@@ -414,9 +567,11 @@ PG_API int32_t pg_swiglu_quantize(pg_ctx *ctx, const float *d_gate_up, int64_t r
     PG_REQUIRE(ctx && d_gate_up && d_q && d_scales, "swiglu_quantize: null pointer");
     PG_REQUIRE(rows >= 0 && F > 0 && F % 4 == 0 && F <= LT * 4 * 16, "swiglu_quantize: F must be a multiple of 4, at most %d", LT * 64);
     if (rows == 0) return PG_OK;
-    const dim3 g((unsigned)rows), b(LT);
-    if (F <= LT * 16) return launch_pdl(ctx, swiglu_quant_kernel<4>, g, b, 0, d_gate_up, (int)F, d_q, d_scales, d_act);
-    return launch_pdl(ctx, swiglu_quant_kernel<16>, g, b, 0, d_gate_up, (int)F, d_q, d_scales, d_act);
+    const int cs = row_cluster(ctx, rows, F / 4, 128);
+    const dim3 g((unsigned)(rows * cs)), b(LT);
+    if (F / cs <= LT * 8) return launch_pdl_cluster(ctx, swiglu_quant_kernel<2>, g, b, 0, cs, d_gate_up, (int)F, d_q, d_scales, d_act);
+    if (F / cs <= LT * 16) return launch_pdl_cluster(ctx, swiglu_quant_kernel<4>, g, b, 0, cs, d_gate_up, (int)F, d_q, d_scales, d_act);
+    return launch_pdl_cluster(ctx, swiglu_quant_kernel<16>, g, b, 0, cs, d_gate_up, (int)F, d_q, d_scales, d_act);
 }
 
 // qkv [B, (Hq + 2 Hkv) * hd] -> q_rot [B, Hq, hd]; k (rotated) and v written at position *d_pos of the caches
@@ -442,39 +597,51 @@ PG_API int32_t pg_gqa_decode_splits(pg_ctx *ctx, int64_t B, int64_t Hq, int64_t 
 
 PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
                                        const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_work,
-                                       float *d_out)
+                                       float *d_out, int8_t *d_out_i8, float *d_out_scales)
 {
-    PG_REQUIRE(ctx && d_q_rot && d_kcache && d_vcache && d_pos && d_work && d_out, "gqa_attention_decode: null pointer");
+    PG_REQUIRE(ctx && d_q_rot && d_kcache && d_vcache && d_pos && d_work, "gqa_attention_decode: null pointer");
+    PG_REQUIRE(d_out || d_out_i8, "gqa_attention_decode: no output");
+    PG_REQUIRE((d_out_i8 == nullptr) == (d_out_scales == nullptr), "gqa_attention_decode: quantised output needs both buffers");
     PG_REQUIRE(hd == 128, "gqa_attention_decode: head_dim %lld is not supported (128 only)", (long long)hd);
     PG_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "gqa_attention_decode: Hkv must divide Hq");
     const int64_t G = Hq / Hkv;
     PG_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, "gqa_attention_decode: %lld query heads per KV head is not supported (1, 2, 4, 8)", (long long)G);
     if (B == 0) return PG_OK;
     const int S = pg_gqa_decode_splits(ctx, B, Hq, Hkv, cap);
-    const int chunk = (int)((cap + S - 1) / S);
     const float scale = 1.0f / sqrtf((float)hd);
     float *part_o = d_work;
     float *part_ml = d_work + B * Hq * S * 128;
-    if (pgk_gqa_stream_supports(G)) {
-        int32_t rc = pgk_gqa_decode_stream(ctx, d_q_rot, d_kcache, d_vcache, d_pos, B, Hq, Hkv, cap, S, scale, part_o, part_ml);
-        if (rc) return rc;
-        return launch_pdl(ctx, gqa_decode_combine_kernel, dim3((unsigned)Hq, (unsigned)B), dim3(128), 0, (const float *)part_o,
-                          (const float *)part_ml, (int)Hq, S, d_out);
-    }
-    const size_t smem = ((size_t)chunk * G + 8 * G * 128) * sizeof(float);
-    const dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
     int32_t rc;
+    if (pgk_gqa_stream_supports(G)) {
+        rc = pgk_gqa_decode_stream(ctx, d_q_rot, d_kcache, d_vcache, d_pos, B, Hq, Hkv, cap, S, scale, part_o, part_ml);
+    } else {
+        const int chunk = (int)((cap + S - 1) / S);
+        const size_t smem = ((size_t)chunk * G + 8 * G * 128) * sizeof(float);
+        const dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
 #define PG_ATT(GG)                                                                                                              \
     {                                                                                                                           \
         if (smem > 48 * 1024) PG_CUDA(cudaFuncSetAttribute(gqa_decode_partial_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         rc = launch_pdl(ctx, gqa_decode_partial_kernel<GG>, grid, dim3(256), smem, d_q_rot, d_kcache, d_vcache, (const int *)d_pos, (int)Hq, \
                         (int)Hkv, (int)cap, chunk, scale, part_o, part_ml);                                                     \
     }
-    if (G == 1) PG_ATT(1) else if (G == 2) PG_ATT(2) else if (G == 4) PG_ATT(4) else PG_ATT(8)
+        if (G == 1) PG_ATT(1) else PG_ATT(2)
 #undef PG_ATT
+    }
     if (rc) return rc;
-    return launch_pdl(ctx, gqa_decode_combine_kernel, dim3((unsigned)Hq, (unsigned)B), dim3(128), 0, (const float *)part_o, (const float *)part_ml,
-                      (int)Hq, S, d_out);
+    // merge of the partials (+ the quantiser of the output projection's input): a cluster of CTAs per sequence
+    int cs = 8;
+    while (cs > 1 && (B * cs > 2 * (int64_t)ctx->sm_count || Hq % cs != 0)) cs >>= 1;
+    const int64_t hpc = Hq / cs;
+    if (hpc <= 8)
+        return launch_pdl_cluster(ctx, gqa_combine_quant_kernel, dim3((unsigned)(B * cs)), dim3(128, (unsigned)hpc), 0, cs, (const float *)part_o,
+                                  (const float *)part_ml, (int)Hq, S, d_out, d_out_i8, d_out_scales);
+    // many sequences with many heads: merge per head, quantise the rows afterwards
+    float *merged = d_out;
+    PG_REQUIRE(d_out != nullptr, "gqa_attention_decode: this shape needs the f32 output buffer as well");
+    rc = launch_pdl(ctx, gqa_decode_combine_kernel, dim3((unsigned)Hq, (unsigned)B), dim3(128), 0, (const float *)part_o, (const float *)part_ml,
+                    (int)Hq, S, merged);
+    if (rc || !d_out_i8) return rc;
+    return pgk_quantize_activations(ctx, merged, B, Hq * 128, d_out_i8, d_out_scales);
 }
 
 PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim, float *d_out)
@@ -489,7 +656,8 @@ PG_API int32_t pg_argmax_advance(pg_ctx *ctx, const float *d_logits, int64_t B, 
 {
     PG_REQUIRE(ctx && d_logits && d_tokens && V > 0, "argmax: bad arguments");
     if (B == 0) return PG_OK;
-    return launch_pdl(ctx, argmax_kernel, dim3((unsigned)B), dim3(1024), 0, d_logits, (int)V, (int *)d_tokens, (int *)d_pos);
+    const int cs = row_cluster(ctx, B, V, 4096);
+    return launch_pdl_cluster(ctx, argmax_kernel, dim3((unsigned)(B * cs)), dim3(1024), 0, cs, d_logits, (int)V, (int *)d_tokens, (int *)d_pos);
 }
 
 }  // extern "C"

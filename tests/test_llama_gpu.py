@@ -106,7 +106,7 @@ def test_swiglu_quantize(pg, gpu, oracle):
         assert np.array_equal(q.cpu().numpy().reshape(rows, F), qo) and np.array_equal(s.cpu().numpy(), so)
 
 
-def test_rope_append_attention_embedding_argmax(pg, gpu):
+def test_rope_append_attention_embedding_argmax(pg, gpu, oracle):
     import torch
     from peregrine_b200 import _lib
     from peregrine_b200.llama import rope_tables
@@ -131,8 +131,10 @@ def test_rope_append_attention_embedding_argmax(pg, gpu):
         torch.cuda.synchronize()
         _lib.check(lib.pg_rope_kv_append(gpu.handle, tq.data_ptr(), tpos.data_ptr(), tc.data_ptr(), ts.data_ptr(), B, Hq, Hkv, hd, cap,
                                          qrot.data_ptr(), tK.data_ptr(), tV.data_ptr()))
+        o8 = torch.zeros(B, Hq * hd, dtype=torch.int8, device="cuda")
+        o8s = torch.zeros(B, device="cuda")
         _lib.check(lib.pg_gqa_attention_decode(gpu.handle, qrot.data_ptr(), tK.data_ptr(), tV.data_ptr(), tpos.data_ptr(), B, Hq, Hkv, hd, cap,
-                                               work.data_ptr(), out.data_ptr()))
+                                               work.data_ptr(), out.data_ptr(), o8.data_ptr(), o8s.data_ptr()))
         gpu.sync()
         heads = qkv.reshape(B, Hq + 2 * Hkv, hd)
         q_ref = rope_ref(heads[:, :Hq], cos[pos], sin[pos])
@@ -143,6 +145,9 @@ def test_rope_append_attention_embedding_argmax(pg, gpu):
         assert np.array_equal(tK.cpu().numpy(), K2) and np.array_equal(tV.cpu().numpy(), V2)
         ref = attention_ref(q_ref, K2, V2, pos + 1, Hq // Hkv)
         assert np.abs(out.cpu().numpy() - ref).max() <= 1e-5 * np.abs(ref).max()
+        # the fused quantiser: bit-exact with the oracle's quantiser applied to the f32 rows the kernel produced
+        qo, so = oracle.quantize_activations(out.cpu().numpy(), B, Hq * hd)
+        assert np.array_equal(o8.cpu().numpy(), qo) and np.array_equal(o8s.cpu().numpy(), so)
     # embedding and argmax (first maximum; the position is advanced once)
     table = normal(g, (50, 64))
     tok = np.array([3, 49, 0], np.int32)
@@ -161,6 +166,18 @@ def test_rope_append_attention_embedding_argmax(pg, gpu):
     gpu.sync()
     assert np.array_equal(o.cpu().numpy(), table[tok])
     assert picks.cpu().numpy().tolist() == [77, 0, int(np.argmax(logits[2]))] and int(p.item()) == 6
+    # a vocabulary wide enough for the row to be spread over a cluster: ties across segment borders, maximum in the last segment
+    big = normal(g, (5, 128256))
+    big[0, 100] = big[0, 128255] = 11.0
+    big[1, 128255] = 12.0
+    big[2, 16031] = big[2, 16032] = 13.0
+    big[3, :] = 0.5
+    tb = _t(big)
+    picks = torch.zeros(5, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    _lib.check(lib.pg_argmax_advance(gpu.handle, tb.data_ptr(), 5, 128256, picks.data_ptr(), p.data_ptr()))
+    gpu.sync()
+    assert picks.cpu().numpy().tolist() == [100, 128255, 16031, 0, int(np.argmax(big[4]))] and int(p.item()) == 7
 
 
 def _ref_step(orc, cfg, W, Q, x, K, V, pos, cos, sin):
