@@ -44,7 +44,8 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr)
 __device__ __forceinline__ uint4 ld_cached_v4(const void *p)
 {
     uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    // written by the preceding kernel (the quantiser): L2, not the non-coherent path
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 #pragma unroll
         for (int j = 0; j < S - 1; j++) sum += xsum[j * (ROWS * NT) + idx];
         if (acc_out) acc_out[(int64_t)m * N + n] = sum;
-        if (y) y[(int64_t)m * N + n] = __fmul_rn(__fmul_rn(__int2float_rn(sum), a_scales[m]), __ldg(w_scales + n));
+        if (y) y[(int64_t)m * N + n] = __fmul_rn(__fmul_rn(__int2float_rn(sum), pg_ld_fresh(a_scales + m)), __ldg(w_scales + n));
     }
 }
 

@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
                             if (n + c < N) {
                                 const int32_t sum = acc[2 * h + c];
                                 if (acc_out) acc_out[(int64_t)m * N + n + c] = sum;
-                                if (y) y[(int64_t)m * N + n + c] = __fmul_rn(__fmul_rn(__int2float_rn(sum), a_scales[m]), __ldg(w_scales + n + c));
+                                if (y) y[(int64_t)m * N + n + c] = __fmul_rn(__fmul_rn(__int2float_rn(sum), pg_ld_fresh(a_scales + m)), __ldg(w_scales + n + c));
                             }
                         }
                     }

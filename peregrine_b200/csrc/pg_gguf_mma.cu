@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restric
     const float *xr = x + (int64_t)(live ? m : 0) * K;
     float amax = 0.0f;
     if (live)
-        for (int i = threadIdx.x; i < K; i += 256) amax = fmaxf(amax, fabsf(xr[i]));
+        for (int i = threadIdx.x; i < K; i += 256) amax = fmaxf(amax, fabsf(pg_ld_fresh(xr + i)));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restric
         const int b = i >> 2, t = i & 3;
         float v[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) v[j] = live ? xr[b * 32 + t * 8 + j] * s : 0.0f;
+        for (int j = 0; j < 8; j++) v[j] = live ? pg_ld_fresh(xr + b * 32 + t * 8 + j) * s : 0.0f;
         float o[8];
         if (TYPE == PG_GGUF_Q4_0) {
             const float h = 0.0625f;
@@ -227,8 +227,8 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     for (int j = 0; j < G_SLICE; j++) {
         const int b = wblk + j;
         if (b < nblk_chunk) {
-            xh[j] = __ldg(xs + ((int64_t)(blk0 + b) * 2 + 0) * 32 + lane);
-            xl[j] = __ldg(xs + ((int64_t)(blk0 + b) * 2 + 1) * 32 + lane);
+            xh[j] = pg_ld_fresh(xs + ((int64_t)(blk0 + b) * 2 + 0) * 32 + lane);
+            xl[j] = pg_ld_fresh(xs + ((int64_t)(blk0 + b) * 2 + 1) * 32 + lane);
         } else {
             xh[j] = xl[j] = make_uint4(0u, 0u, 0u, 0u);
         }
@@ -298,9 +298,9 @@ __global__ void __launch_bounds__(G_THREADS, 1)
             float sum = 0.0f;
 #pragma unroll
             for (int w = 0; w < G_WARPS; w++) sum += src[(size_t)w * (R * 128)];
-            sum *= row_scale[mm];
+            sum *= pg_ld_fresh(row_scale + mm);
             float *dst = y + (int64_t)(m0 + mm) * N + n;
-            *dst = accumulate ? (*dst + sum) : sum;
+            *dst = accumulate ? (pg_ld_fresh(dst) + sum) : sum;
         }
     }
     cp_wait<0>();

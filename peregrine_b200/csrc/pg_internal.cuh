@@ -40,6 +40,21 @@ extern std::atomic<uint64_t> g_pg_launches;
         PG_CUDA(cudaGetLastError());        \
     } while (0)
 
+// ------------------------------------------------- loads across kernels ----
+// The kernels of this library are launched with programmatic stream serialisation and signal
+// griddepcontrol.launch_dependents first thing, so a kernel is usually resident while its
+// predecessor still runs (and while older kernels' lines sit in that SM's L1).  Data that a
+// preceding kernel of the stream produced is therefore read, after griddepcontrol.wait, with
+// loads that go to L2: never through the non-coherent path (ld.global.nc / __ldg, which the
+// compiler also chooses by itself for `const __restrict__` pointers) and never from L1.
+#ifdef __CUDACC__
+template <typename T>
+__device__ __forceinline__ T pg_ld_fresh(const T *p)
+{
+    return __ldcg(p);
+}
+#endif
+
 // --------------------------------------------------------------- objects ----
 struct pg_ctx {
     int device = 0;

@@ -126,9 +126,9 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
         const int c = i * LT + threadIdx.x;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c < nseg) {
-            v[i] = xr[c0 + c];
+            v[i] = pg_ld_fresh(xr + c0 + c);
             if (delta) {
-                const float4 d = __ldg(reinterpret_cast<const float4 *>(delta + row * dim) + c0 + c);
+                const float4 d = pg_ld_fresh(reinterpret_cast<const float4 *>(delta + row * dim) + c0 + c);
                 v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
                 xr[c0 + c] = v[i];
             }
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(LT) swiglu_quant_kernel(const float *__restric
         const int c = i * LT + threadIdx.x;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c < nseg) {
-            const float4 g = __ldg(g4 + c), u = __ldg(u4 + c);
+            const float4 g = pg_ld_fresh(g4 + c), u = pg_ld_fresh(u4 + c);
             v[i] = make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w));
             if (act_out) reinterpret_cast<float4 *>(act_out + row * F)[c0 + c] = v[i];
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
@@ -212,10 +212,10 @@ __global__ void rope_kv_append_kernel(const float *__restrict__ qkv, const int *
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = hd >> 1;
-    const int pos = *pos_ptr;
+    const int pos = pg_ld_fresh(pos_ptr);
     const float *src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + head) * hd;
     if (head < Hq + Hkv) {
-        const float x0 = src[i], x1 = src[half + i];
+        const float x0 = pg_ld_fresh(src + i), x1 = pg_ld_fresh(src + half + i);
         const float c = cos_t[(int64_t)pos * half + i], s = sin_t[(int64_t)pos * half + i];
         const float r0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
         const float r1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
@@ -225,8 +225,8 @@ __global__ void rope_kv_append_kernel(const float *__restrict__ qkv, const int *
         dst[half + i] = r1;
     } else {
         float *dst = vc + (((int64_t)b * Hkv + (head - Hq - Hkv)) * cap + pos) * hd;
-        dst[i] = src[i];
-        dst[half + i] = src[half + i];
+        dst[i] = pg_ld_fresh(src + i);
+        dst[half + i] = pg_ld_fresh(src + half + i);
     }
 }
 
@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int split = blockIdx.x, S = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int len = *pos_ptr + 1;
+    const int len = pg_ld_fresh(pos_ptr) + 1;
     const int t0 = split * chunk, t1 = min(len, t0 + chunk);
     const int n = t1 - t0;
     float *po = part_o + (((int64_t)b * Hq + kvh * G) * S + split) * HD;   // + h * S * HD
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
     const float4 *vbase = reinterpret_cast<const float4 *>(vc + (((int64_t)b * Hkv + kvh) * cap + t0) * HD);
     float4 qv[G];
 #pragma unroll
-    for (int h = 0; h < G; h++) qv[h] = __ldg(reinterpret_cast<const float4 *>(q + ((int64_t)b * Hq + kvh * G + h) * HD) + lane);
+    for (int h = 0; h < G; h++) qv[h] = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * Hq + kvh * G + h) * HD) + lane);
 
     // scores
     for (int i0 = warp; i0 < n; i0 += 8 * 4) {
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int i = i0 + u * 8;
-            kv[u] = (i < n) ? __ldg(kbase + (int64_t)i * (HD / 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            kv[u] = (i < n) ? pg_ld_fresh(kbase + (int64_t)i * (HD / 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             const int i = i0 + u * 8;
-            vv[u] = (i < n) ? __ldg(vbase + (int64_t)i * (HD / 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            vv[u] = (i < n) ? pg_ld_fresh(vbase + (int64_t)i * (HD / 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) {
@@ -359,14 +359,14 @@ __global__ void __launch_bounds__(128) gqa_decode_combine_kernel(const float *__
     const float *ml = part_ml + ((int64_t)b * Hq + qh) * S * 2;
     const float *po = part_o + ((int64_t)b * Hq + qh) * S * 128;
     float m = -INFINITY;
-    for (int s = 0; s < S; s++) m = fmaxf(m, ml[2 * s]);
+    for (int s = 0; s < S; s++) m = fmaxf(m, pg_ld_fresh(ml + 2 * s));
     float denom = 0.0f, acc = 0.0f;
     for (int s = 0; s < S; s++) {
-        const float l = ml[2 * s + 1];
+        const float l = pg_ld_fresh(ml + 2 * s + 1);
         if (l > 0.0f) {
-            const float e = expf(ml[2 * s] - m);
+            const float e = expf(pg_ld_fresh(ml + 2 * s) - m);
             denom = fmaf(e, l, denom);
-            acc = fmaf(e, po[(int64_t)s * 128 + d], acc);
+            acc = fmaf(e, pg_ld_fresh(po + (int64_t)s * 128 + d), acc);
         }
     }
     out[((int64_t)b * Hq + qh) * 128 + d] = (denom > 0.0f) ? __fdiv_rn(acc, denom) : 0.0f;
@@ -377,7 +377,7 @@ __global__ void embedding_kernel(const float *__restrict__ table, const int *__r
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
-    const float4 *src = reinterpret_cast<const float4 *>(table + (int64_t)tokens[b] * dim);
+    const float4 *src = reinterpret_cast<const float4 *>(table + (int64_t)pg_ld_fresh(tokens + b) * dim);
     float4 *dst = reinterpret_cast<float4 *>(out + (int64_t)b * dim);
     for (int i = threadIdx.x; i < (dim >> 2); i += blockDim.x) dst[i] = __ldg(src + i);
 }
@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
     float best = -INFINITY;
     int idx = 0x7fffffff;
     for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-        const float v = row[i];
+        const float v = pg_ld_fresh(row + i);
         if (v > best || (v == best && i < idx)) {
             best = v;
             idx = i;
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
                 idx = xi[c];
             }
         tokens[b] = (idx == 0x7fffffff) ? 0 : idx;   // all-NaN row: the reference keeps index 0
-        if (b == 0 && pos_ptr) *pos_ptr += 1;
+        if (b == 0 && pos_ptr) *pos_ptr = pg_ld_fresh(pos_ptr) + 1;
     }
 }
 
@@ -450,24 +450,42 @@ __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__
                                                                   int S, float *__restrict__ out, int8_t *__restrict__ q8,
                                                                   float *__restrict__ q8_scales)
 {
+    constexpr int MAXS = 64;                      // slices per (sequence, KV head) never exceed this (checked on the host)
     __shared__ float red[32];
     __shared__ float xm[8];
+    __shared__ float wgt[8][MAXS];                // per head of this CTA: exp(m_s - m), 0 for an empty slice
+    __shared__ float den[8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t cs = cl_size(), rank = cl_rank();
     const int b = blockIdx.x / cs, d = threadIdx.x, qh = (int)rank * blockDim.y + threadIdx.y;
     const float *ml = part_ml + ((int64_t)b * Hq + qh) * S * 2;
     const float *po = part_o + ((int64_t)b * Hq + qh) * S * 128;
-    float m = -INFINITY;
-    for (int s = 0; s < S; s++) m = fmaxf(m, ml[2 * s]);
-    float denom = 0.0f, acc = 0.0f;
-    for (int s = 0; s < S; s++) {
-        const float l = ml[2 * s + 1];
-        if (l > 0.0f) {
-            const float e = expf(ml[2 * s] - m);
-            denom = fmaf(e, l, denom);
-            acc = fmaf(e, po[(int64_t)s * 128 + d], acc);
+    // the first warp of every head turns the S (max, sum) pairs into weights, so that the loads of the partial outputs
+    // below do not hang off a chain of exponentials
+    if (d < 32) {
+        float m = -INFINITY;
+        for (int s = d; s < S; s += 32) m = fmaxf(m, pg_ld_fresh(ml + 2 * s));
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        float dn = 0.0f;
+        for (int s = d; s < S; s += 32) {
+            const float l = pg_ld_fresh(ml + 2 * s + 1);
+            const float e = (l > 0.0f) ? expf(pg_ld_fresh(ml + 2 * s) - m) : 0.0f;
+            wgt[threadIdx.y][s] = e;
+            dn = fmaf(e, l, dn);
         }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dn += __shfl_xor_sync(0xffffffffu, dn, off);
+        if (d == 0) den[threadIdx.y] = dn;
+    }
+    __syncthreads();
+    const float denom = den[threadIdx.y];
+    float acc = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < S; s++) {
+        const float e = wgt[threadIdx.y][s];
+        if (e != 0.0f) acc = fmaf(e, pg_ld_fresh(po + (int64_t)s * 128 + d), acc);
     }
     const float o = (denom > 0.0f) ? __fdiv_rn(acc, denom) : 0.0f;
     const int64_t at = ((int64_t)b * Hq + qh) * 128 + d;
@@ -632,7 +650,7 @@ PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const 
     int cs = 8;
     while (cs > 1 && (B * cs > 2 * (int64_t)ctx->sm_count || Hq % cs != 0)) cs >>= 1;
     const int64_t hpc = Hq / cs;
-    if (hpc <= 8)
+    if (hpc <= 8 && S <= 64)
         return launch_pdl_cluster(ctx, gqa_combine_quant_kernel, dim3((unsigned)(B * cs)), dim3(128, (unsigned)hpc), 0, cs, (const float *)part_o,
                                   (const float *)part_ml, (int)Hq, S, d_out, d_out_i8, d_out_scales);
     // many sequences with many heads: merge per head, quantise the rows afterwards

@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     // the newest K/V row, q and the position come from the preceding kernels
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const int len = *pos_ptr + 1;
+    const int len = pg_ld_fresh(pos_ptr) + 1;
     const int chunk = at_chunk(len, S, P);
     const int units = B * Hkv * S;
     const int my_p = lane / G;             // lane i holds pair (position i / G, head i % G) after the butterfly
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         float4 qv[G];
 #pragma unroll
         for (int h = 0; h < G; h++) {
-            qv[h] = __ldg(reinterpret_cast<const float4 *>(q + ((int64_t)b * Hq + kvh * G + h) * AT_HD) + lane);
+            qv[h] = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * Hq + kvh * G + h) * AT_HD) + lane);
         }
         float m_run = -INFINITY, l_run = 0.0f;
         float4 acc[G];
@@ -258,6 +258,7 @@ int pgk_gqa_stream_splits(const pg_ctx *ctx, int64_t B, int64_t Hkv, int64_t cap
     const int64_t warps = (int64_t)ctx->sm_count * AT_WARPS;
     int64_t S = std::max<int64_t>(1, warps / pairs);
     S = std::min<int64_t>(S, std::max<int64_t>(1, cap / 64));
+    S = std::min<int64_t>(S, 64);                 // the merge kernel keeps one weight per slice in shared memory
     return (int)S;
 }
 

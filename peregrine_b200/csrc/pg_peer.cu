@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *
     } else {
         for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
             const int64_t m = i / n_local, c = i - m * n_local;
-            const float v = slice[i];
+            const float v = pg_ld_fresh(slice + i);
             for (int p = 0; p < world; p++) dst.y[p][m * n_total + col0 + c] = v;
         }
     }

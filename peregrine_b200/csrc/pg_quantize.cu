@@ -49,11 +49,11 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
-        v[i] = (c < nvec) ? __ldg(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i] = (c < nvec) ? pg_ld_fresh(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
     }
     for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) {
-        const float4 t = __ldg(xr + c);
+        const float4 t = pg_ld_fresh(xr + c);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
     }
     amax = block_max(amax, red);
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
         const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
         if (c < nvec) qr[c] = pack(v[i]);
     }
-    for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) qr[c] = pack(__ldg(xr + c));
+    for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) qr[c] = pack(pg_ld_fresh(xr + c));
 }
 
 // Any cols / any alignment: scalar loads, two passes.
