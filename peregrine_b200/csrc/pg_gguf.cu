@@ -274,7 +274,7 @@ int32_t pgk_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_
 {
     if (m == 0 || w->n == 0) return PG_OK;
     PG_REQUIRE(((uintptr_t)d_x & 15) == 0, "matmul_gguf: x must be 16-byte aligned");
-    if (!g_gguf_force_simple && pgk_matmul_gguf_mma_supports(w, m)) return pgk_matmul_gguf_mma(ctx, d_x, m, w, d_y);
+    if (!g_gguf_force_simple && pgk_matmul_gguf_mma_supports(w, m) && ((uintptr_t)d_x & 15) == 0) return pgk_matmul_gguf_mma(ctx, d_x, m, w, d_y);
     switch (w->type) {
         case PG_GGUF_Q8_0: return launch_matmul<PG_GGUF_Q8_0>(ctx, d_x, m, w, d_y);
         case PG_GGUF_Q4_0: return launch_matmul<PG_GGUF_Q4_0>(ctx, d_x, m, w, d_y);

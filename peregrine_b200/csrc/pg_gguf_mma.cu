@@ -9,25 +9,28 @@
 // the HBM rate already at M = 8.  Here
 //   * the quants go to the MMA as exact fp16 integers, built with two logic ops per pair from the
 //     packed nibbles/bytes (exponent-bias trick: 0x6400 | u is the half 1024 + u);
-//   * each f32 activation is split into two fp16 parts, x * 2^s = hi + lo (s a per-row power of
-//     two that brings the row's largest element into [8,16), so that lo keeps an absolute
-//     precision of 2^-25 on that scale); every product quant x part is exact and the sums
-//     accumulate in f32 inside the MMA;
+//   * each f32 activation is split into two fp16 parts, x * 2^s = hi + lo (s a power of two, per
+//     activation row and per 256-element slice of K, that brings the slice's largest element into
+//     [8,16), so that lo keeps an absolute precision of 2^-25 on that scale); every product
+//     quant x part is exact and the sums accumulate in f32 inside the MMA;
 //   * per 32-element block the partial sum is multiplied by the block's f16 scale: y += d * sum.
 // The result differs from the reference's strictly sequential f32 loop only in summation order
 // and in the 2^-28 relative truncation of the activations (documented tolerance: 1e-5 of max|y|;
 // measured a few 1e-6, which is also the sequential f32 loop's own distance from an f64 sum).
 //
-// Data flow, per CTA of 16 warps (one CTA per SM, persistent over tiles of 16*R weight rows):
-//   * warp w owns a fixed slice of eight 32-element blocks of K and keeps the activation
-//     fragments of that slice in registers for the whole kernel, so activations cost no memory
-//     traffic in the main loop whatever M is;
+// Data flow, per CTA of 16 warps (one CTA per SM, persistent over tiles of 16*R weight rows), ONE
+// launch per eight activation rows whatever K is:
+//   * K is walked in chunks of 128 blocks (4096 elements).  Inside a chunk warp w owns a fixed
+//     slice of eight 32-element blocks and builds the activation fragments of that slice itself,
+//     straight from the f32 activations (slice maximum, power-of-two scale, hi/lo split), and
+//     keeps them in registers for all the CTA's tiles: activations cost no memory traffic in the
+//     main loop whatever M is, and no separate preparation kernel runs;
 //   * the quants stream through a lane-private cp.async FIFO in shared memory (128-bit copies,
 //     L2 only), several entries deep, so HBM requests stay in flight across tile boundaries.  The
 //     upload interleaves each 64-byte group of quants so that the 16 bytes a lane needs for the
 //     group's blocks are contiguous: a lane copies exactly what it will read back;
-//   * per tile the 16 warps' partial sums meet in shared memory (fixed order: deterministic).
-// K longer than 128 blocks is handled by one launch per 4096-element chunk, accumulating into y.
+//   * per tile the 16 warps' partial sums meet in shared memory (fixed order: deterministic);
+//     chunks after the first add onto y (the same CTA owns a tile in every chunk).
 #include <cuda_fp16.h>
 
 #include "pg_internal.cuh"
@@ -101,65 +104,33 @@ __device__ __forceinline__ void unpack(uint32_t w0, uint32_t w1, uint32_t (&a)[4
 }
 
 // ---- activation fragments -------------------------------------------------------------------
-// One CTA per activation row of the 8-row tile (rows past M are written as zeros).  Output, per
-// 32-element block b and part p (0 = hi, 1 = lo): 32 lanes x 16 bytes, lane = (row % 8) * 4 + t
+// B operand of one 32-element block b, part p (0 = hi, 1 = lo): 32 lanes x 16 bytes, lane = (row % 8) * 4 + t
 // holding the eight elements 8t..8t+7 of the block in the order the weight unpacking produces them:
 //   Q8_0: e0 e1 e2 e3 e4 e5 e6 e7
 //   Q4_0: e0 e4 e1' e5' e2 e6 e3' e7'   (' = divided by 16: the high nibbles are unpacked as 16*q)
-// row_scale[m] = 2^-s undoes the per-row power-of-two scaling.
 template <int TYPE>
-__global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restrict__ x, int M, int K, int m0, uint4 *__restrict__ xs,
-                                                           float *__restrict__ row_scale)
+__device__ __forceinline__ void make_fragment(const float (&v)[8], uint4 &hi4, uint4 &lo4)
 {
-    __shared__ float red[32];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int g = blockIdx.x;  // row inside the tile
-    const int m = m0 + g;
-    const int nblk = K >> 5;
-    const bool live = m < M;
-    const float *xr = x + (int64_t)(live ? m : 0) * K;
-    float amax = 0.0f;
-    if (live)
-        for (int i = threadIdx.x; i < K; i += 256) amax = fmaxf(amax, fabsf(pg_ld_fresh(xr + i)));
+    float o[8];
+    if (TYPE == PG_GGUF_Q4_0) {
+        const float h = 0.0625f;
+        o[0] = v[0]; o[1] = v[4]; o[2] = v[1] * h; o[3] = v[5] * h;
+        o[4] = v[2]; o[5] = v[6]; o[6] = v[3] * h; o[7] = v[7] * h;
+    } else {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = 0.0f;
-#pragma unroll
-    for (int wv = 0; wv < 8; wv++) amax = fmaxf(amax, red[wv]);  // every thread needs the row maximum
-    int e = 0;
-    if (amax > 0.0f && amax < INFINITY) e = max(-100, min(100, ilogbf(amax)));
-    const float s = scalbnf(1.0f, 3 - e);  // |x| * s < 16
-    if (threadIdx.x == 0 && live) row_scale[g] = scalbnf(1.0f, e - 3);
-    for (int i = threadIdx.x; i < nblk * 4; i += 256) {
-        const int b = i >> 2, t = i & 3;
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) v[j] = live ? pg_ld_fresh(xr + b * 32 + t * 8 + j) * s : 0.0f;
-        float o[8];
-        if (TYPE == PG_GGUF_Q4_0) {
-            const float h = 0.0625f;
-            o[0] = v[0]; o[1] = v[4]; o[2] = v[1] * h; o[3] = v[5] * h;
-            o[4] = v[2]; o[5] = v[6]; o[6] = v[3] * h; o[7] = v[7] * h;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; j++) o[j] = v[j];
-        }
-        uint32_t hi[4], lo[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const __half h0 = __float2half_rn(o[2 * j]), h1 = __float2half_rn(o[2 * j + 1]);
-            const __half l0 = __float2half_rn(o[2 * j] - __half2float(h0));
-            const __half l1 = __float2half_rn(o[2 * j + 1] - __half2float(h1));
-            hi[j] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-            lo[j] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
-        }
-        const int lane = g * 4 + t;
-        xs[((int64_t)b * 2 + 0) * 32 + lane] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        xs[((int64_t)b * 2 + 1) * 32 + lane] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        for (int j = 0; j < 8; j++) o[j] = v[j];
     }
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const __half h0 = __float2half_rn(o[2 * j]), h1 = __float2half_rn(o[2 * j + 1]);
+        const __half l0 = __float2half_rn(o[2 * j] - __half2float(h0));
+        const __half l1 = __float2half_rn(o[2 * j + 1] - __half2float(h1));
+        hi[j] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        lo[j] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+    }
+    hi4 = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    lo4 = make_uint4(lo[0], lo[1], lo[2], lo[3]);
 }
 
 // ---- the product -----------------------------------------------------------------------------
@@ -169,9 +140,8 @@ __global__ void __launch_bounds__(256) gguf_prep_x_kernel(const float *__restric
 //   Q8_0: bytes 8t..8t+7 of block 0, then of block 1.
 template <int TYPE, int R, int D>
 __global__ void __launch_bounds__(G_THREADS, 1)
-    gguf_mma_kernel(const uint4 *__restrict__ xs, const float *__restrict__ row_scale, const uint8_t *__restrict__ qs,
-                    const uint16_t *__restrict__ dd, int64_t N, int nblk_row, int blk0, int nblk_chunk, int M, int m0,
-                    float *__restrict__ y, int accumulate)
+    gguf_mma_kernel(const float *__restrict__ x, const uint8_t *__restrict__ qs, const uint16_t *__restrict__ dd, int64_t N,
+                    int nblk_row, int M, int m0, float *__restrict__ y)
 {
     constexpr int BPS = (TYPE == PG_GGUF_Q4_0) ? 4 : 2;
     constexpr int STEPS = G_SLICE / BPS;          // steps per warp per row group
@@ -183,25 +153,26 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     const int g = lane >> 2, t = lane & 3;
     const uint32_t wbase = (uint32_t)__cvta_generic_to_shared(smem_g) + warp * G_WSLOT;
     float *red = reinterpret_cast<float *>(reinterpret_cast<char *>(smem_g) + (size_t)D * G_SLOT_BYTES);
-    const int wblk = warp * G_SLICE;              // first block of this warp's slice inside the chunk
+    const int wblk = warp * G_SLICE;              // first block of this warp's slice inside a chunk
     const int64_t tiles = (N + TROWS - 1) / TROWS;
     const int my_tiles = (tiles > blockIdx.x) ? (int)((tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+    const int nchunks = (nblk_row + G_CHUNK - 1) / G_CHUNK;
 
-    // Issue side of the FIFO: walks (tile, row group, step) in the order the consumer does.  Each lane
+    // Issue side of the FIFO: walks (chunk, tile, row group, step) in the order the consumer does.  Each lane
     // copies its own 16 bytes of rows g and g+8; the first step of a row group also brings the block
-    // scales of the warp's whole K slice for those rows (lanes t = 0, 1 copy them for g and g+8).
-    int i_tile = 0, i_step = 0, i_rg = 0, i_slot = 0;
+    // scales of the warp's K slice for those rows (lanes t = 0, 1 copy them for g and g+8).
+    int i_chunk = 0, i_tile = 0, i_step = 0, i_rg = 0, i_slot = 0;
     auto issue = [&]() {
         const int64_t tile = blockIdx.x + (int64_t)i_tile * gridDim.x;
-        const int b = wblk + i_step * BPS;        // first block of the step inside the chunk
-        const bool kok = (i_tile < my_tiles) && (b < nblk_chunk);
+        const int b = i_chunk * G_CHUNK + wblk + i_step * BPS;   // first block of the step inside the row
+        const bool kok = (i_chunk < nchunks) && (i_tile < my_tiles) && (b < nblk_row);
         const uint32_t slot = wbase + (uint32_t)i_slot * G_SLOT_BYTES;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             int64_t row = tile * TROWS + i_rg * 16 + g + h * 8;
             const bool ok = kok && (row < N);
             row = ok ? row : 0;
-            const int64_t blk = row * nblk_row + blk0 + (ok ? b : 0);
+            const int64_t blk = row * nblk_row + (ok ? b : 0);
             cp_async16(slot + (h * 32 + lane) * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
             if (i_step == 0 && t == h) cp_async16(slot + G_QAREA + (h * 8 + g) * 16, dd + blk, ok ? 16u : 0u);
         }
@@ -211,96 +182,129 @@ __global__ void __launch_bounds__(G_THREADS, 1)
             i_step = 0;
             if (++i_rg == R) {
                 i_rg = 0;
-                ++i_tile;
+                if (++i_tile >= my_tiles) {
+                    i_tile = 0;
+                    ++i_chunk;
+                }
             }
         }
     };
-#pragma unroll
-    for (int i = 0; i < D - 1; i++) issue();
-
-    // the activation fragments come from the preceding kernel
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    uint4 xh[G_SLICE], xl[G_SLICE];
+    if (my_tiles > 0) {
 #pragma unroll
-    for (int j = 0; j < G_SLICE; j++) {
-        const int b = wblk + j;
-        if (b < nblk_chunk) {
-            xh[j] = pg_ld_fresh(xs + ((int64_t)(blk0 + b) * 2 + 0) * 32 + lane);
-            xl[j] = pg_ld_fresh(xs + ((int64_t)(blk0 + b) * 2 + 1) * 32 + lane);
-        } else {
-            xh[j] = xl[j] = make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int i = 0; i < D - 1; i++) issue();
     }
-    int c_slot = 0;
-    for (int ti = 0; ti < my_tiles; ti++) {
-        float *mine = red + ((size_t)(ti & 1) * G_WARPS + warp) * (R * 128);
+    // the activations come from the preceding kernel
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (my_tiles == 0) return;
+
+    const int xrow = m0 + g;                       // as B-operand owner this lane holds activation row g, elements 8t..8t+7
+    const bool live = xrow < M;
+    const float *xr = x + (int64_t)(live ? xrow : 0) * nblk_row * 32 + t * 8;
+    int c_slot = 0, ti_all = 0;
+    for (int chunk = 0; chunk < nchunks; chunk++) {
+        const int blk0 = chunk * G_CHUNK;
+        // ---- this warp's activation fragments for the chunk: slice maximum, power-of-two scale, hi/lo split
+        float amax = 0.0f;
 #pragma unroll
-        for (int rg = 0; rg < R; rg++) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            uint4 sc0, sc1;  // eight f16 block scales of rows g and g+8 (this warp's K slice)
-#pragma unroll
-            for (int step = 0; step < STEPS; step++) {
-                issue();
-                cp_wait<D - 1>();
-                const uint32_t slot = wbase + (uint32_t)c_slot * G_SLOT_BYTES;
-                if (++c_slot == D) c_slot = 0;
-                if (step == 0) {
-                    __syncwarp();  // the scales were copied by other lanes of the group
-                    sc0 = lds128(slot + G_QAREA + g * 16);
-                    sc1 = lds128(slot + G_QAREA + (8 + g) * 16);
-                }
-                const uint4 qa = lds128(slot + lane * 16), qb = lds128(slot + (32 + lane) * 16);  // rows g, g+8
-                const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-                for (int bi = 0; bi < BPS; bi++) {
-                    const int j = step * BPS + bi;  // block inside the warp's slice
-                    uint32_t a0[4], a1[4];          // rows g and g+8
-                    if (TYPE == PG_GGUF_Q4_0) {
-                        unpack<TYPE>(wa[bi], 0u, a0);
-                        unpack<TYPE>(wb[bi], 0u, a1);
-                    } else {
-                        unpack<TYPE>(wa[2 * bi], wa[2 * bi + 1], a0);
-                        unpack<TYPE>(wb[2 * bi], wb[2 * bi + 1], a1);
-                    }
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_f16(c, a0[0], a1[0], a0[1], a1[1], xh[j].x, xh[j].y);
-                    mma_f16(c, a0[2], a1[2], a0[3], a1[3], xh[j].z, xh[j].w);
-                    mma_f16(c, a0[0], a1[0], a0[1], a1[1], xl[j].x, xl[j].y);
-                    mma_f16(c, a0[2], a1[2], a0[3], a1[3], xl[j].z, xl[j].w);
-                    // f16 scale of block j of the slice, rows g and g+8
-                    const uint32_t p0 = (j < 2) ? sc0.x : (j < 4) ? sc0.y : (j < 6) ? sc0.z : sc0.w;
-                    const uint32_t p1 = (j < 2) ? sc1.x : (j < 4) ? sc1.y : (j < 6) ? sc1.z : sc1.w;
-                    const __half2 h0 = *reinterpret_cast<const __half2 *>(&p0), h1 = *reinterpret_cast<const __half2 *>(&p1);
-                    const float d0 = (j & 1) ? __high2float(h0) : __low2float(h0);
-                    const float d1 = (j & 1) ? __high2float(h1) : __low2float(h1);
-                    acc[0] = fmaf(d0, c[0], acc[0]);
-                    acc[1] = fmaf(d0, c[1], acc[1]);
-                    acc[2] = fmaf(d1, c[2], acc[2]);
-                    acc[3] = fmaf(d1, c[3], acc[3]);
-                }
+        for (int j = 0; j < G_SLICE; j++) {
+            const int b = blk0 + wblk + j;
+            if (live && b < nblk_row) {
+                const float4 p = pg_ld_fresh(reinterpret_cast<const float4 *>(xr + (int64_t)b * 32));
+                const float4 q = pg_ld_fresh(reinterpret_cast<const float4 *>(xr + (int64_t)b * 32) + 1);
+                amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(p.x), fabsf(p.y)), fmaxf(fabsf(p.z), fabsf(p.w))),
+                                         fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w)))));
             }
-            // partial sums of this warp's K slice -> shared memory, [buf][warp][rg][m 0..7][row 0..15]
-            mine[rg * 128 + (2 * t) * 16 + g] = acc[0];
-            mine[rg * 128 + (2 * t + 1) * 16 + g] = acc[1];
-            mine[rg * 128 + (2 * t) * 16 + g + 8] = acc[2];
-            mine[rg * 128 + (2 * t + 1) * 16 + g + 8] = acc[3];
         }
-        __syncthreads();
-        const int64_t tile = blockIdx.x + (int64_t)ti * gridDim.x;
-        for (int idx = threadIdx.x; idx < 8 * TROWS; idx += G_THREADS) {
-            const int mm = idx / TROWS, nn = idx - mm * TROWS;     // consecutive threads -> consecutive n
-            const int rg = nn >> 4, row = nn & 15;
-            const int64_t n = tile * TROWS + nn;
-            if (m0 + mm >= M || n >= N) continue;
-            const float *src = red + (size_t)(ti & 1) * G_WARPS * (R * 128) + rg * 128 + mm * 16 + row;
-            float sum = 0.0f;
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        int e = 0;
+        if (amax > 0.0f && amax < INFINITY) e = max(-100, min(100, ilogbf(amax)));
+        const float sc = scalbnf(1.0f, 3 - e);    // |x| * sc < 16 on the slice
+        const float unscale = scalbnf(1.0f, e - 3);
+        uint4 xh[G_SLICE], xl[G_SLICE];
 #pragma unroll
-            for (int w = 0; w < G_WARPS; w++) sum += src[(size_t)w * (R * 128)];
-            sum *= pg_ld_fresh(row_scale + mm);
-            float *dst = y + (int64_t)(m0 + mm) * N + n;
-            *dst = accumulate ? (pg_ld_fresh(dst) + sum) : sum;
+        for (int j = 0; j < G_SLICE; j++) {
+            const int b = blk0 + wblk + j;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (live && b < nblk_row) {
+                const float4 p = pg_ld_fresh(reinterpret_cast<const float4 *>(xr + (int64_t)b * 32));
+                const float4 q = pg_ld_fresh(reinterpret_cast<const float4 *>(xr + (int64_t)b * 32) + 1);
+                v[0] = p.x * sc; v[1] = p.y * sc; v[2] = p.z * sc; v[3] = p.w * sc;
+                v[4] = q.x * sc; v[5] = q.y * sc; v[6] = q.z * sc; v[7] = q.w * sc;
+            }
+            make_fragment<TYPE>(v, xh[j], xl[j]);
+        }
+        // as accumulator owner this lane holds activation rows 2t and 2t+1: their scales live in lanes 8t and 8t+4
+        const float us0 = __shfl_sync(0xffffffffu, unscale, 8 * t), us1 = __shfl_sync(0xffffffffu, unscale, 8 * t + 4);
+
+        for (int ti = 0; ti < my_tiles; ti++, ti_all++) {
+            float *mine = red + ((size_t)(ti_all & 1) * G_WARPS + warp) * (R * 128);
+#pragma unroll
+            for (int rg = 0; rg < R; rg++) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                uint4 sc0, sc1;  // eight f16 block scales of rows g and g+8 (this warp's K slice)
+#pragma unroll
+                for (int step = 0; step < STEPS; step++) {
+                    issue();
+                    cp_wait<D - 1>();
+                    const uint32_t slot = wbase + (uint32_t)c_slot * G_SLOT_BYTES;
+                    if (++c_slot == D) c_slot = 0;
+                    if (step == 0) {
+                        __syncwarp();  // the scales were copied by other lanes of the group
+                        sc0 = lds128(slot + G_QAREA + g * 16);
+                        sc1 = lds128(slot + G_QAREA + (8 + g) * 16);
+                    }
+                    const uint4 qa = lds128(slot + lane * 16), qb = lds128(slot + (32 + lane) * 16);  // rows g, g+8
+                    const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+                    for (int bi = 0; bi < BPS; bi++) {
+                        const int j = step * BPS + bi;  // block inside the warp's slice
+                        uint32_t a0[4], a1[4];          // rows g and g+8
+                        if (TYPE == PG_GGUF_Q4_0) {
+                            unpack<TYPE>(wa[bi], 0u, a0);
+                            unpack<TYPE>(wb[bi], 0u, a1);
+                        } else {
+                            unpack<TYPE>(wa[2 * bi], wa[2 * bi + 1], a0);
+                            unpack<TYPE>(wb[2 * bi], wb[2 * bi + 1], a1);
+                        }
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_f16(c, a0[0], a1[0], a0[1], a1[1], xh[j].x, xh[j].y);
+                        mma_f16(c, a0[2], a1[2], a0[3], a1[3], xh[j].z, xh[j].w);
+                        mma_f16(c, a0[0], a1[0], a0[1], a1[1], xl[j].x, xl[j].y);
+                        mma_f16(c, a0[2], a1[2], a0[3], a1[3], xl[j].z, xl[j].w);
+                        // f16 scale of block j of the slice, rows g and g+8
+                        const uint32_t p0 = (j < 2) ? sc0.x : (j < 4) ? sc0.y : (j < 6) ? sc0.z : sc0.w;
+                        const uint32_t p1 = (j < 2) ? sc1.x : (j < 4) ? sc1.y : (j < 6) ? sc1.z : sc1.w;
+                        const __half2 h0 = *reinterpret_cast<const __half2 *>(&p0), h1 = *reinterpret_cast<const __half2 *>(&p1);
+                        const float d0 = (j & 1) ? __high2float(h0) : __low2float(h0);
+                        const float d1 = (j & 1) ? __high2float(h1) : __low2float(h1);
+                        acc[0] = fmaf(d0, c[0], acc[0]);
+                        acc[1] = fmaf(d0, c[1], acc[1]);
+                        acc[2] = fmaf(d1, c[2], acc[2]);
+                        acc[3] = fmaf(d1, c[3], acc[3]);
+                    }
+                }
+                // partial sums of this warp's K slice (scaling undone) -> shared memory, [buf][warp][rg][m 0..7][row 0..15]
+                mine[rg * 128 + (2 * t) * 16 + g] = acc[0] * us0;
+                mine[rg * 128 + (2 * t + 1) * 16 + g] = acc[1] * us1;
+                mine[rg * 128 + (2 * t) * 16 + g + 8] = acc[2] * us0;
+                mine[rg * 128 + (2 * t + 1) * 16 + g + 8] = acc[3] * us1;
+            }
+            __syncthreads();
+            const int64_t tile = blockIdx.x + (int64_t)ti * gridDim.x;
+            for (int idx = threadIdx.x; idx < 8 * TROWS; idx += G_THREADS) {
+                const int mm = idx / TROWS, nn = idx - mm * TROWS;     // consecutive threads -> consecutive n
+                const int rg = nn >> 4, row = nn & 15;
+                const int64_t n = tile * TROWS + nn;
+                if (m0 + mm >= M || n >= N) continue;
+                const float *src = red + (size_t)(ti_all & 1) * G_WARPS * (R * 128) + rg * 128 + mm * 16 + row;
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < G_WARPS; w++) sum += src[(size_t)w * (R * 128)];
+                float *dst = y + (int64_t)(m0 + mm) * N + n;
+                *dst = (chunk > 0) ? (*dst + sum) : sum;   // the same thread wrote *dst in the chunk before
+            }
         }
     }
     cp_wait<0>();
@@ -310,12 +314,6 @@ template <int TYPE, int R, int D>
 int32_t run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
 {
     const int K = (int)w->k, nblk = K / 32, M = (int)m;
-    // scratch: activation fragments of one 8-row tile (nblk * 2 parts * 512 B) + 8 row scales
-    const size_t xs_bytes = (size_t)nblk * 2 * 32 * sizeof(uint4);
-    int32_t rc = pg_scratch_reserve(ctx, xs_bytes + 256);
-    if (rc) return rc;
-    uint4 *xs = reinterpret_cast<uint4 *>(ctx->scratch);
-    float *row_scale = reinterpret_cast<float *>(reinterpret_cast<char *>(ctx->scratch) + xs_bytes);
     const size_t smem = (size_t)D * G_SLOT_BYTES + 2 * G_WARPS * R * 128 * sizeof(float);
     auto kern = gguf_mma_kernel<TYPE, R, D>;
     PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -325,27 +323,15 @@ int32_t run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, f
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     for (int m0 = 0; m0 < M; m0 += 8) {
-        cudaLaunchConfig_t pc = {};
-        pc.gridDim = dim3(8);
-        pc.blockDim = dim3(256);
-        pc.stream = ctx->stream;
-        pc.attrs = attr;
-        pc.numAttrs = 1;
-        PG_CUDA(cudaLaunchKernelEx(&pc, gguf_prep_x_kernel<TYPE>, d_x, M, K, m0, xs, row_scale));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(G_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        PG_CUDA(cudaLaunchKernelEx(&cfg, kern, d_x, (const uint8_t *)w->d_qs, (const uint16_t *)w->d_d, w->n, nblk, M, m0, d_y));
         PG_LAUNCHED();
-        for (int blk0 = 0; blk0 < nblk; blk0 += G_CHUNK) {
-            const int chunk = (nblk - blk0 < G_CHUNK) ? (nblk - blk0) : G_CHUNK;
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(grid);
-            cfg.blockDim = dim3(G_THREADS);
-            cfg.dynamicSmemBytes = smem;
-            cfg.stream = ctx->stream;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
-            PG_CUDA(cudaLaunchKernelEx(&cfg, kern, (const uint4 *)xs, (const float *)row_scale, (const uint8_t *)w->d_qs,
-                                       (const uint16_t *)w->d_d, w->n, nblk, blk0, chunk, M, m0, d_y, blk0 > 0 ? 1 : 0));
-            PG_LAUNCHED();
-        }
     }
     return PG_OK;
 }
