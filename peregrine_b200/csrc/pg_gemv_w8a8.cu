@@ -44,8 +44,10 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr)
 __device__ __forceinline__ uint4 ld_cached_v4(const void *p)
 {
     uint4 v;
-    // written by the preceding kernel (the quantiser): L2, not the non-coherent path
-    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    // Written by the preceding kernel (the quantiser) and re-read by every CTA of an SM: an ordinary coherent load
+    // that allocates in L1 (griddepcontrol.wait makes the predecessor's stores visible to these), never the
+    // non-coherent path, whose lines may predate the predecessor's stores.
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
@@ -176,6 +178,9 @@ __global__ void __launch_bounds__(WARPS * 32)
         }
     }
     cp_async_wait<0>();
+    // the activation scales were written by the preceding kernel: one L2 load each, not one per output
+    __shared__ float as_s[MB * 16];
+    if (threadIdx.x < ROWS) as_s[threadIdx.x] = ((int)threadIdx.x < M) ? pg_ld_fresh(a_scales + threadIdx.x) : 0.0f;
     __syncthreads();  // every lane is done with its FIFO: the memory becomes the reduction buffer
 
     // C fragment: c0,c1 -> (row r, cols 2t, 2t+1); c2,c3 -> (row r+8, same cols)
@@ -218,7 +223,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 #pragma unroll
         for (int j = 0; j < S - 1; j++) sum += xsum[j * (ROWS * NT) + idx];
         if (acc_out) acc_out[(int64_t)m * N + n] = sum;
-        if (y) y[(int64_t)m * N + n] = __fmul_rn(__fmul_rn(__int2float_rn(sum), pg_ld_fresh(a_scales + m)), __ldg(w_scales + n));
+        if (y) y[(int64_t)m * N + n] = __fmul_rn(__fmul_rn(__int2float_rn(sum), as_s[m]), __ldg(w_scales + n));
     }
 }
 

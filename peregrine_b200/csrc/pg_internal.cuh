@@ -55,6 +55,54 @@ __device__ __forceinline__ T pg_ld_fresh(const T *p)
 }
 #endif
 
+#ifdef __CUDACC__
+// ---- a row spread over the CTAs of a thread-block cluster ----------------------------------------
+// With a handful of sequences per step a kernel of one CTA per row leaves most SMs idle and is bound
+// by the latency of one CTA walking its row.  The row kernels below therefore cut a row into `cs`
+// column segments (cs = cluster size, 1..8), one CTA each, and exchange their partial sums / maxima
+// through distributed shared memory: every CTA stores its value into slot [rank] of every peer, one
+// cluster barrier, every CTA reduces the cs slots itself.
+__device__ __forceinline__ uint32_t cl_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cl_size()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cl_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cl_store_f32(float *local_slot, uint32_t cta, float v)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_slot)), "r"(cta));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cl_store_s32(int *local_slot, uint32_t cta, int v)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_slot)), "r"(cta));
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(remote), "r"(v) : "memory");
+}
+// v: this CTA's value (the same in every thread).  slots: 8 floats of shared memory not used by another exchange in flight.
+template <bool MAX>
+__device__ __forceinline__ float cl_allreduce(float v, float *slots, uint32_t cs, uint32_t rank)
+{
+    if (cs == 1) return v;
+    if (threadIdx.x < cs) cl_store_f32(slots + rank, threadIdx.x, v);
+    cl_sync();
+    float r = slots[0];
+    for (uint32_t i = 1; i < cs; i++) r = MAX ? fmaxf(r, slots[i]) : r + slots[i];
+    return r;
+}
+#endif
+
 // --------------------------------------------------------------- objects ----
 struct pg_ctx {
     int device = 0;

@@ -24,52 +24,6 @@ namespace {
 
 constexpr int LT = 256;  // threads per CTA of the row kernels
 
-// ---- a row spread over the CTAs of a thread-block cluster ----------------------------------------
-// With a handful of sequences per step a kernel of one CTA per row leaves most SMs idle and is bound
-// by the latency of one CTA walking its row.  The row kernels below therefore cut a row into `cs`
-// column segments (cs = cluster size, 1..8), one CTA each, and exchange their partial sums / maxima
-// through distributed shared memory: every CTA stores its value into slot [rank] of every peer, one
-// cluster barrier, every CTA reduces the cs slots itself.
-__device__ __forceinline__ uint32_t cl_rank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t cl_size()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cl_sync()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cl_store_f32(float *local_slot, uint32_t cta, float v)
-{
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_slot)), "r"(cta));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
-__device__ __forceinline__ void cl_store_s32(int *local_slot, uint32_t cta, int v)
-{
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local_slot)), "r"(cta));
-    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(remote), "r"(v) : "memory");
-}
-// v: this CTA's value (the same in every thread).  slots: 8 floats of shared memory not used by another exchange in flight.
-template <bool MAX>
-__device__ __forceinline__ float cl_allreduce(float v, float *slots, uint32_t cs, uint32_t rank)
-{
-    if (cs == 1) return v;
-    if (threadIdx.x < cs) cl_store_f32(slots + rank, threadIdx.x, v);
-    cl_sync();
-    float r = slots[0];
-    for (uint32_t i = 1; i < cs; i++) r = MAX ? fmaxf(r, slots[i]) : r + slots[i];
-    return r;
-}
-
 __device__ __forceinline__ float block_sum(float v, float *smem)
 {
 #pragma unroll
@@ -464,17 +418,16 @@ __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__
     // the first warp of every head turns the S (max, sum) pairs into weights, so that the loads of the partial outputs
     // below do not hang off a chain of exponentials
     if (d < 32) {
-        float m = -INFINITY;
-        for (int s = d; s < S; s += 32) m = fmaxf(m, pg_ld_fresh(ml + 2 * s));
+        // S <= 64: a lane holds at most two (max, sum) pairs, loaded once
+        const float2 p0 = (d < S) ? pg_ld_fresh(reinterpret_cast<const float2 *>(ml) + d) : make_float2(-INFINITY, 0.0f);
+        const float2 p1 = (d + 32 < S) ? pg_ld_fresh(reinterpret_cast<const float2 *>(ml) + d + 32) : make_float2(-INFINITY, 0.0f);
+        float m = fmaxf(p0.x, p1.x);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
-        float dn = 0.0f;
-        for (int s = d; s < S; s += 32) {
-            const float l = pg_ld_fresh(ml + 2 * s + 1);
-            const float e = (l > 0.0f) ? expf(pg_ld_fresh(ml + 2 * s) - m) : 0.0f;
-            wgt[threadIdx.y][s] = e;
-            dn = fmaf(e, l, dn);
-        }
+        const float e0 = (p0.y > 0.0f) ? expf(p0.x - m) : 0.0f, e1 = (p1.y > 0.0f) ? expf(p1.x - m) : 0.0f;
+        if (d < S) wgt[threadIdx.y][d] = e0;
+        if (d + 32 < S) wgt[threadIdx.y][d + 32] = e1;
+        float dn = fmaf(e0, p0.y, e1 * p1.y);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) dn += __shfl_xor_sync(0xffffffffu, dn, off);
         if (d == 0) den[threadIdx.y] = dn;

@@ -28,22 +28,26 @@ __device__ __forceinline__ float block_max(float v, float *smem)
     return r;  // every thread holds the block maximum
 }
 
-// One CTA per row.  The row is read once with 128-bit loads and kept in registers
-// (up to VPT float4 per thread); the absmax is a warp-shuffle + shared-memory reduction
-// (max is order-independent, fmaxf drops NaN like f32::max); the i8 results leave as
-// packed 32-bit stores.  Columns past THREADS*VPT*4 are re-read in the second pass.
+// A cluster of cs CTAs (1..8) per row, each with cols / cs columns: with a handful of rows one CTA per
+// row would leave the GPU idle and be bound by one CTA's walk along its row.  The segment is read
+// once with 128-bit loads and kept in registers (up to VPT float4 per thread); the absmax is a
+// warp-shuffle + shared-memory reduction, then an exchange through distributed shared memory (max is
+// order-independent, fmaxf drops NaN like f32::max); the i8 results leave as packed 32-bit stores.
+// Columns of a segment past THREADS*VPT*4 are re-read in the second pass.
 template <int VPT>
 __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *__restrict__ x, int64_t cols,
                                                                     int8_t *__restrict__ q, float *__restrict__ scales)
 {
     __shared__ float red[32];
+    __shared__ float xm[8];
     // x comes from the preceding kernel; once this grid runs, the one after it may start its own
     // independent prologue (the product kernel prefetches weights)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int64_t row = blockIdx.x;
-    const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols);
-    const int64_t nvec = cols >> 2;
+    const uint32_t cs = cl_size(), rank = cl_rank();
+    const int64_t row = blockIdx.x / cs;
+    const int64_t nvec = (cols >> 2) / cs;        // float4 per segment (the host picks cs so that this is exact)
+    const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols) + rank * nvec;
     float4 v[VPT];
     float amax = 0.0f;
 #pragma unroll
@@ -56,11 +60,11 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
         const float4 t = pg_ld_fresh(xr + c);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
     }
-    amax = block_max(amax, red);
+    amax = cl_allreduce<true>(block_max(amax, red), xm, cs, rank);
     const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
     const float inv = __fdiv_rn(1.0f, scale);
-    if (threadIdx.x == 0) scales[row] = scale;
-    uint32_t *qr = reinterpret_cast<uint32_t *>(q + row * cols);
+    if (threadIdx.x == 0 && rank == 0) scales[row] = scale;
+    uint32_t *qr = reinterpret_cast<uint32_t *>(q + row * cols) + rank * nvec;
     auto pack = [&](const float4 &t) -> uint32_t {
         const int a = pg_round_clamp_i8(__fmul_rn(t.x, inv));
         const int b = pg_round_clamp_i8(__fmul_rn(t.y, inv));
@@ -184,16 +188,29 @@ int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, in
     } else if (!vec) {
         quantize_rows_scalar_kernel<<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, cols, d_q, d_scales);
     } else {
+        // CTAs per row: one, unless the row is long enough (8192 columns per CTA) for the exchange between the CTAs
+        // of a cluster to cost less than one CTA's walk along the row (measured: at 4096 and 14336 columns one CTA wins)
+        int cs = 8;
+        const int64_t nvec = cols / 4;
+        while (cs > 1 && (rows * cs > 2 * (int64_t)ctx->sm_count || nvec % cs != 0 || nvec / cs < 2048)) cs >>= 1;
+        PG_REQUIRE(rows * cs <= 0x7fffffff, "quantize_activations: rows=%lld exceeds the grid limit", (long long)rows);
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)rows);
+        cfg.gridDim = dim3((unsigned)(rows * cs));
         cfg.blockDim = dim3(QR_THREADS);
         cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = (unsigned)cs;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (cols <= 4 * QR_THREADS * 4)
+        cfg.numAttrs = cs > 1 ? 2 : 1;
+        const int64_t seg = cols / cs;
+        if (seg <= 4 * QR_THREADS)
+            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<1>, d_x, cols, d_q, d_scales));
+        else if (seg <= 4 * QR_THREADS * 4)
             PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<4>, d_x, cols, d_q, d_scales));
         else
             PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<16>, d_x, cols, d_q, d_scales));

@@ -196,9 +196,7 @@ def test_single_linear_config(pg, gpu, oracle_mt):
 def test_decode_gemv_sweep(pg, gpu, oracle_mt, idx, m, k, n):
     """Llama-3-8B projection shapes, activations with 1 % outlier channels (x20)."""
     x, w = linear_inputs(m, k, n, 1000 + idx, outliers=True)
-    # 16 rows of K = 14336 do not fit in the warp-stream kernel's shared memory
-    algos = ["stream", "tcgen05"] + ([] if (m > 8 and k > 4096) else ["wstream"])
-    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, algos)
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["wstream", "stream", "tcgen05"])
 
 
 @pytest.mark.parametrize("m,k,n", [
@@ -211,6 +209,30 @@ def test_warp_stream_kernel_ragged_shapes(pg, gpu, oracle_mt, m, k, n):
     x, w = linear_inputs(m, k, n, 177 + m + n)
     _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive", "wstream"])
     assert gpu.device_status() == 0
+
+
+@pytest.mark.parametrize("cs", [2, 4])
+@pytest.mark.parametrize("kw", [0, 1, 4, 16])
+def test_warp_stream_k_split_over_a_cluster(pg, gpu, oracle_mt, kw, cs):
+    """K split over the 2 or 4 CTAs of a cluster (each holds its part of the activations; the other CTAs add their sums
+    into the first one's shared memory once per round of tiles): forced on small shapes, several rounds included, and
+    taken by itself when the rows of K do not fit beside the ring in one CTA."""
+    gpu.lib.pg_tune_wstream_kw(kw)
+    gpu.lib.pg_tune_wstream_cluster(cs)
+    try:
+        for m, k, n in ((1, 4096, 520), (16, 4096, 8), (7, 4032, 33), (16, 4096, 3000), (9, 4096, 2369 * 8 + 5)):
+            x, w = linear_inputs(m, k, n, 850 + kw + m)
+            _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["wstream", "wstream"])
+        gpu.lib.pg_tune_wstream_cluster(0)
+        gpu.lib.pg_tune_wstream_kw(0)
+        if cs == 2 and kw == 0:
+            for m, k, n in ((16, 14336, 264), (8, 14336, 100), (12, 8192 + 512, 100), (16, 16384 - 64, 40)):
+                x, w = linear_inputs(m, k, n, 870 + kw + m)
+                _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive", "wstream"])
+        assert gpu.device_status() == 0
+    finally:
+        gpu.lib.pg_tune_wstream_kw(0)
+        gpu.lib.pg_tune_wstream_cluster(0)
 
 
 @pytest.mark.parametrize("kw", [1, 2, 4, 8, 16])
