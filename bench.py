@@ -409,12 +409,12 @@ def run_ours(args):
         k_ms = e0.elapsed_time(e1) / reps
         kern_bytes = sum(bytes_gemv_kernel(MS[mi], SHAPES[si][0], shard[si][1] - shard[si][0]) for mi, si in CASES)
         achieved = kern_bytes / (k_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "gemv_w8a8_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+        roofline = {"bound": "hbm", "kernel": "gemv_wstream_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": achieved / hbm_peak,
                     # dram__bytes_read + dram__bytes_write of one ncu capture of this kernel (K 4096, N 32768, M 16:
-                    # 139.6 MB for 136.5 MB algorithmic, see profiles/gemv_w8a8_K4096_N32768.md), scaled by the bytes
+                    # 139.3 MB for 136.5 MB algorithmic), scaled by the bytes
                     # an average launch of the sweep moves (traffic grows in proportion to K*N)
-                    "traffic": 1.023 * kern_bytes / 9, "traffic_source": "ncu capture scaled by algorithmic bytes",
+                    "traffic": 1.02 * kern_bytes / 9, "traffic_source": "ncu capture scaled by algorithmic bytes",
                     "peak_source": peak_src,
                     "bytes_per_launch_avg": kern_bytes / 9, "us_per_launch_avg": k_ms * 1e3 / 9,
                     "how": f"{reps} replays of a graph holding only the nine product launches, CUDA events on the launch stream"}

@@ -124,7 +124,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     const int my_p = lane / G;             // lane i holds pair (position i / G, head i % G) after the butterfly
     uint32_t fills = 0;                       // ring fills so far: slot = fills % 2, parity = (fills / 2) & 1
 
-    for (int u = blockIdx.x * AT_WARPS + warp; u < units; u += gridDim.x * AT_WARPS) {
+    // unit -> (CTA u % grid, warp u / grid): every SM gets work even when the units do not fill the last CTAs' warps
+    for (int u = warp * gridDim.x + blockIdx.x; u < units; u += gridDim.x * AT_WARPS) {
         const int pair = u / S, split = u - pair * S;
         const int b = pair / Hkv, kvh = pair - b * Hkv;
         const int t0 = split * chunk, n = min(len, t0 + chunk) - t0;
@@ -270,7 +271,7 @@ int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, const float *d_k, c
     const int G = (int)(Hq / Hkv);
     const int64_t units = B * Hkv * S;
     PG_REQUIRE(units <= 0x7fffffff, "gqa_attention_decode: too many (sequence, head, slice) units");
-    const int grid = (int)std::min<int64_t>(ctx->sm_count, (units + AT_WARPS - 1) / AT_WARPS);
+    const int grid = (int)std::min<int64_t>(ctx->sm_count, units);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
