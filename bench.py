@@ -210,6 +210,11 @@ def run_ours(args):
     gpu = pg.GpuContext(local, stream.cuda_stream)
     lib = gpu.lib
     warmup = max(args.warmup, 3)
+    # N > 1: "shard" splits every weight matrix by output column over the ranks and all-gathers the slices (strong
+    # scaling of one sweep); "replicas" gives every rank the whole matrices and its own copy of the sweep, with no
+    # data-path collective (weak scaling: what a server does with independent batches when the model fits one GPU)
+    replicas = world > 1 and args.parallel == "replicas"
+    sw, srank = (1, 0) if replicas else (world, rank)
 
     # ---- weights: quantise on the GPU, keep this rank's column shard, three copies per shape ----
     COPIES = 3
@@ -218,7 +223,7 @@ def run_ours(args):
     for si, (k, n) in enumerate(SHAPES):
         w = make_weight(si, k, n)
         qt = pg.quant.quantize_weights(w, k, n, gpu)
-        b, e = (n * rank) // world, (n * (rank + 1)) // world
+        b, e = (n * srank) // sw, (n * (srank + 1)) // sw
         shard.append((b, e))
         t_w = torch.from_numpy(np.ascontiguousarray(qt.data_i8_t[b:e])).to(dev)
         t_s = torch.from_numpy(np.ascontiguousarray(qt.scales[b:e])).to(dev)
@@ -238,16 +243,16 @@ def run_ours(args):
     xs_host = [torch.from_numpy(make_inputs(ci, MS[mi], SHAPES[si][0])).pin_memory() for ci, (mi, si) in enumerate(CASES)]
     xs = [x.to(dev) for x in xs_host]
     ys = [torch.empty(MS[mi], shard[si][1] - shard[si][0], dtype=torch.float32, device=dev) for mi, si in CASES]
-    ys_full = [torch.empty(world, MS[mi], shard[si][1] - shard[si][0], dtype=torch.float32, device=dev) if world > 1 else None
+    ys_full = [torch.empty(sw, MS[mi], shard[si][1] - shard[si][0], dtype=torch.float32, device=dev) if sw > 1 else None
                for mi, si in CASES]
     ys_host = [torch.empty(MS[mi], SHAPES[si][1], dtype=torch.float32).pin_memory() for mi, si in CASES]
-    even = all(SHAPES[si][1] % world == 0 for si in range(3))
-    if world > 1 and not even:
+    even = all(SHAPES[si][1] % sw == 0 for si in range(3))
+    if sw > 1 and not even:
         raise SystemExit("column shards must be equal for the all-gather")
 
     from peregrine_b200.sharded import PeerExchange
 
-    peer = world > 1 and args.collective == "peer"
+    peer = sw > 1 and args.collective == "peer"
     exs = [PeerExchange(gpu, rank, world, MS[mi], SHAPES[si][1]) for mi, si in CASES] if peer else None
 
     def enqueue_products():
@@ -271,7 +276,7 @@ def run_ours(args):
             _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
             if peer:
                 exs[ci].store(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
-            elif world > 1:
+            elif sw > 1:
                 dist.all_gather_into_tensor(ys_full[ci], ys[ci])
         if peer:
             for ex in exs:
@@ -287,7 +292,7 @@ def run_ours(args):
     # launches stay eager: replaying a captured step that contained the all-gathers did not complete
     # on this pool, so that form is not used.
     graph = None
-    if world == 1 or peer:
+    if sw == 1 or peer:
         if world > 1:
             dist.barrier()
         with gpu.record() as graph:
@@ -325,7 +330,7 @@ def run_ours(args):
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    total_bytes = sweep_bytes()
+    total_bytes = sweep_bytes() * (world if replicas else 1)   # every replica runs the whole sweep
     value = total_bytes * args.steps / (ms * 1e-3) / 1e9
     assert gpu.device_status() == 0
 
@@ -338,7 +343,7 @@ def run_ours(args):
         for ci, (mi, si) in enumerate(CASES):
             k, n = SHAPES[si]
             h = pool[si][mi][0]
-            if world == 1:
+            if sw == 1:
                 # the C-ABI call with the exact shape of quant::matmul_quantized: copies x up, runs, copies y back, blocks
                 _lib.check(lib.pg_matmul_quantized_host(gpu.handle, xs_host[ci].data_ptr(), MS[mi], k, h, ys_host[ci].data_ptr()))
             else:
@@ -349,7 +354,7 @@ def run_ours(args):
                     _lib.check(lib.pg_mem_download(gpu.handle, ys_host[ci].data_ptr(), exs[ci].result_ptr, MS[mi] * n * 4))
                 else:
                     dist.all_gather_into_tensor(ys_full[ci], ys[ci])
-                    ys_host[ci].view(MS[mi], world, -1).copy_(ys_full[ci].permute(1, 0, 2), non_blocking=True)
+                    ys_host[ci].view(MS[mi], sw, -1).copy_(ys_full[ci].permute(1, 0, 2), non_blocking=True)
                     stream.synchronize()
 
     with torch.cuda.stream(stream):
@@ -440,19 +445,20 @@ def run_ours(args):
 
         line = {
             "metric": "w8a8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if replicas else "strong",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
             "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9,
-                       "parallelism": f"column-sharded x{world}" + ((", peer-store all-gather over NVLink (own kernel, bounded flag wait)" if peer
-                                                                     else ", NCCL all-gather of output slices") if world > 1 else ""),
+                       "parallelism": (f"{world} replicas, one sweep each, no collective" if replicas else
+                                       f"column-sharded x{world}" + ((", peer-store all-gather over NVLink (own kernel, bounded flag wait)" if peer
+                                                                      else ", NCCL all-gather of output slices") if world > 1 else "")),
                        "l2": "inputs larger than L2: each case reads its own copy of the weights (3 copies per shape, 402 MB per step)",
                        "submission": "one CUDA graph per step" if graph is not None else "eager launches + NCCL",
-                       "collective": ("peer-store" if peer else "nccl") if world > 1 else None,
+                       "collective": ("peer-store" if peer else "nccl") if sw > 1 else None,
                        "bytes_per_step": total_bytes},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_s / e2e_steps * 1e3,
-                    "api": "pg_matmul_quantized_host (pinned host x in, host y out, blocking)" if world == 1 else
+                    "api": "pg_matmul_quantized_host (pinned host x in, host y out, blocking)" if sw == 1 else
                            "pinned H2D + pg_matmul_quantized + all-gather + D2H of the full result"},
             "gpu_launches": launches_per_step * args.steps,
             "kernels_per_step": launches_per_step,
@@ -622,6 +628,8 @@ def main():
     ap.add_argument("--extra", action="store_true", help="also time the prefill GEMM and the GGUF products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama-8B-shape decode stack measurement (N = 1 only)")
+    ap.add_argument("--parallel", default="shard", choices=["shard", "replicas"],
+                    help="N > 1: column-sharded weights with an all-gather (strong scaling, default) or one full replica per GPU (weak)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: all-gather by peer stores recorded in the step graph (default) or eager NCCL")
     args = ap.parse_args()

@@ -251,6 +251,13 @@ PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const 
                                        float *d_work, float *d_out /* [B, Hq*hd] f32, nullable when the int8 form is taken */,
                                        int8_t *d_out_i8 /* nullable: the same rows through the activation quantiser */,
                                        float *d_out_scales /* [B], with d_out_i8 */);
+/* pg_rope_kv_append + pg_gqa_attention_decode in one launch (4 or 8 query heads per KV head): d_qkv is the raw
+   [B, (Hq + 2 Hkv) * hd] output of the fused Q|K|V projection; the newest token's rotated key and its value are written
+   at position *d_pos of the caches */
+PG_API int32_t pg_gqa_attention_decode_fused(pg_ctx *ctx, const float *d_qkv, const int32_t *d_pos, const float *d_cos,
+                                             const float *d_sin, float *d_kcache, float *d_vcache, int64_t B, int64_t Hq,
+                                             int64_t Hkv, int64_t hd, int64_t cap, float *d_work, float *d_out,
+                                             int8_t *d_out_i8, float *d_out_scales);
 /* embedding gather (src/nn.rs:217-227); greedy argmax, first maximum (examples/llama/main.rs:15-26) */
 PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim,
                             float *d_out);

@@ -97,6 +97,7 @@ SIGNATURES = {
     "pg_rope_kv_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
     "pg_gqa_decode_splits": (_i32, [_vp, _i64, _i64, _i64, _i64]),
     "pg_gqa_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "pg_gqa_attention_decode_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "pg_embedding": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "pg_argmax_advance": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "pg_matmul_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),

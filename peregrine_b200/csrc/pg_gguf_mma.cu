@@ -161,32 +161,48 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     // Issue side of the FIFO: walks (chunk, tile, row group, step) in the order the consumer does.  Each lane
     // copies its own 16 bytes of rows g and g+8; the first step of a row group also brings the block
     // scales of the warp's K slice for those rows (lanes t = 0, 1 copy them for g and g+8).
+    // State: the block index of the start of rows g and g+8 of the current row group (rb0, rb1; -1 past the
+    // edge of the matrix or of this CTA's work) and the first block of the current step inside the row (ib).
     int i_chunk = 0, i_tile = 0, i_step = 0, i_rg = 0, i_slot = 0;
+    int64_t rb0 = -1, rb1 = -1;
+    int ib = wblk;
+    auto place = [&]() {   // row starts for (i_tile, i_rg); called when either changes
+        const int64_t row = (blockIdx.x + (int64_t)i_tile * gridDim.x) * TROWS + i_rg * 16 + g;
+        const bool live = (i_chunk < nchunks) && (i_tile < my_tiles);
+        rb0 = (live && row < N) ? row * nblk_row : -1;
+        rb1 = (live && row + 8 < N) ? (row + 8) * nblk_row : -1;
+    };
+    place();
     auto issue = [&]() {
-        const int64_t tile = blockIdx.x + (int64_t)i_tile * gridDim.x;
-        const int b = i_chunk * G_CHUNK + wblk + i_step * BPS;   // first block of the step inside the row
-        const bool kok = (i_chunk < nchunks) && (i_tile < my_tiles) && (b < nblk_row);
         const uint32_t slot = wbase + (uint32_t)i_slot * G_SLOT_BYTES;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            int64_t row = tile * TROWS + i_rg * 16 + g + h * 8;
-            const bool ok = kok && (row < N);
-            row = ok ? row : 0;
-            const int64_t blk = row * nblk_row + (ok ? b : 0);
-            cp_async16(slot + (h * 32 + lane) * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
-            if (i_step == 0 && t == h) cp_async16(slot + G_QAREA + (h * 8 + g) * 16, dd + blk, ok ? 16u : 0u);
+        const bool kok = ib < nblk_row;
+        {
+            const bool ok = kok && rb0 >= 0;
+            const int64_t blk = ok ? rb0 + ib : 0;
+            cp_async16(slot + lane * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
+            if (i_step == 0 && t == 0) cp_async16(slot + G_QAREA + g * 16, dd + blk, ok ? 16u : 0u);
+        }
+        {
+            const bool ok = kok && rb1 >= 0;
+            const int64_t blk = ok ? rb1 + ib : 0;
+            cp_async16(slot + (32 + lane) * 16, qs + blk * QB + t * 16, ok ? 16u : 0u);
+            if (i_step == 0 && t == 1) cp_async16(slot + G_QAREA + (8 + g) * 16, dd + blk, ok ? 16u : 0u);
         }
         cp_commit();
         if (++i_slot == D) i_slot = 0;
+        ib += BPS;
         if (++i_step == STEPS) {
             i_step = 0;
+            ib -= STEPS * BPS;
             if (++i_rg == R) {
                 i_rg = 0;
                 if (++i_tile >= my_tiles) {
                     i_tile = 0;
                     ++i_chunk;
+                    ib += G_CHUNK;
                 }
             }
+            place();
         }
     };
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

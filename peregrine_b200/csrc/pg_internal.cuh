@@ -180,8 +180,9 @@ int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
 // pg_llama_attn.cu
 int pgk_gqa_stream_splits(const pg_ctx *ctx, int64_t B, int64_t Hkv, int64_t cap);
 bool pgk_gqa_stream_supports(int64_t G);
-int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, const int32_t *d_pos, int64_t B,
-                              int64_t Hq, int64_t Hkv, int64_t cap, int S, float scale, float *part_o, float *part_ml);
+int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, float *d_k, float *d_v, const int32_t *d_pos, const float *d_cos,
+                              const float *d_sin, int64_t B, int64_t Hq, int64_t Hkv, int64_t cap, int S, float scale, float *part_o,
+                              float *part_ml);
 // pg_gemm_tcgen05.cu
 bool pgk_gemm_i8_tcgen05_supports(int64_t m, int64_t k, int64_t n);
 int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, pg_qtensor *w,

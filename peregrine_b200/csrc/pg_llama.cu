@@ -566,9 +566,9 @@ PG_API int32_t pg_gqa_decode_splits(pg_ctx *ctx, int64_t B, int64_t Hq, int64_t 
     return cap <= 512 ? 1 : (cap <= 2048 ? 4 : 8);
 }
 
-PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
-                                       const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_work,
-                                       float *d_out, int8_t *d_out_i8, float *d_out_scales)
+static int32_t attention_decode(pg_ctx *ctx, const float *d_q_rot, float *d_kcache, float *d_vcache, const int32_t *d_pos,
+                                const float *d_cos, const float *d_sin, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
+                                float *d_work, float *d_out, int8_t *d_out_i8, float *d_out_scales)
 {
     PG_REQUIRE(ctx && d_q_rot && d_kcache && d_vcache && d_pos && d_work, "gqa_attention_decode: null pointer");
     PG_REQUIRE(d_out || d_out_i8, "gqa_attention_decode: no output");
@@ -584,8 +584,9 @@ PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const 
     float *part_ml = d_work + B * Hq * S * 128;
     int32_t rc;
     if (pgk_gqa_stream_supports(G)) {
-        rc = pgk_gqa_decode_stream(ctx, d_q_rot, d_kcache, d_vcache, d_pos, B, Hq, Hkv, cap, S, scale, part_o, part_ml);
+        rc = pgk_gqa_decode_stream(ctx, d_q_rot, d_kcache, d_vcache, d_pos, d_cos, d_sin, B, Hq, Hkv, cap, S, scale, part_o, part_ml);
     } else {
+        PG_REQUIRE(d_cos == nullptr, "gqa_attention_decode_fused: %lld query heads per KV head is not supported (4, 8)", (long long)G);
         const int chunk = (int)((cap + S - 1) / S);
         const size_t smem = ((size_t)chunk * G + 8 * G * 128) * sizeof(float);
         const dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
@@ -613,6 +614,26 @@ PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const 
                     (int)Hq, S, merged);
     if (rc || !d_out_i8) return rc;
     return pgk_quantize_activations(ctx, merged, B, Hq * 128, d_out_i8, d_out_scales);
+}
+
+
+PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
+                                       const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_work,
+                                       float *d_out, int8_t *d_out_i8, float *d_out_scales)
+{
+    // the caches are only read on this path
+    return attention_decode(ctx, d_q_rot, const_cast<float *>(d_kcache), const_cast<float *>(d_vcache), d_pos, nullptr, nullptr, B, Hq, Hkv, hd,
+                            cap, d_work, d_out, d_out_i8, d_out_scales);
+}
+
+// pg_rope_kv_append + pg_gqa_attention_decode in one launch: d_qkv is the raw [B, (Hq + 2 Hkv) * hd] output of the fused
+// Q|K|V projection; the newest token's rotated key and its value are written at position *d_pos of the caches.
+PG_API int32_t pg_gqa_attention_decode_fused(pg_ctx *ctx, const float *d_qkv, const int32_t *d_pos, const float *d_cos, const float *d_sin,
+                                             float *d_kcache, float *d_vcache, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
+                                             float *d_work, float *d_out, int8_t *d_out_i8, float *d_out_scales)
+{
+    PG_REQUIRE(d_cos && d_sin, "gqa_attention_decode_fused: null rotation tables");
+    return attention_decode(ctx, d_qkv, d_kcache, d_vcache, d_pos, d_cos, d_sin, B, Hq, Hkv, hd, cap, d_work, d_out, d_out_i8, d_out_scales);
 }
 
 PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim, float *d_out)

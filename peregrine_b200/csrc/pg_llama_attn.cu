@@ -18,6 +18,12 @@
 //     shared memory, then the weighted sum of V with the lane's four head-dim elements per head.
 //   * The unit writes its unnormalised output with (max, sum); a second small kernel merges the S
 //     partials of every (sequence, query head).
+//   * FUSED form: the kernel takes the raw output of the fused Q|K|V projection instead of rotated
+//     queries and an already appended cache.  Every warp rotates the query heads of its unit itself
+//     (RoPE, src/nn.rs:1322-1338: the halves of a head live 16 lanes apart, one shuffle each), and
+//     the warp whose slice holds the newest position rotates that token's key, writes key and value
+//     to the cache (KVCache::append, src/attention.rs:65-83) and into its ring slot, from where they
+//     are used like every other row.  One launch less per layer.
 //
 // The mbarrier waits are bounded (about a second): on expiry the warp records
 // PG_ERR_DEVICE_TIMEOUT in the context's status word and leaves.
@@ -93,12 +99,37 @@ __device__ __forceinline__ float4 at_lds128(uint32_t addr)
 // Slices of the context: `S` per (sequence, KV head), each a whole number of batches.
 __host__ __device__ inline int at_chunk(int len, int S, int P) { return (((len + S - 1) / S) + P - 1) / P * P; }
 
+// RoPE of the four elements this lane holds of one head (elements 4 * lane .. 4 * lane + 3): the partner half is 16 lanes away.
+// Same operations, in the same order, as rope_kv_append_kernel.
+__device__ __forceinline__ float4 at_rope(float4 mine, float4 cs, float4 sn, int lane)
+{
+    float4 other;
+    other.x = __shfl_xor_sync(0xffffffffu, mine.x, 16);
+    other.y = __shfl_xor_sync(0xffffffffu, mine.y, 16);
+    other.z = __shfl_xor_sync(0xffffffffu, mine.z, 16);
+    other.w = __shfl_xor_sync(0xffffffffu, mine.w, 16);
+    float4 r;
+    if (lane < 16) {   // first half: x0 * c - x1 * s
+        r.x = __fsub_rn(__fmul_rn(mine.x, cs.x), __fmul_rn(other.x, sn.x));
+        r.y = __fsub_rn(__fmul_rn(mine.y, cs.y), __fmul_rn(other.y, sn.y));
+        r.z = __fsub_rn(__fmul_rn(mine.z, cs.z), __fmul_rn(other.z, sn.z));
+        r.w = __fsub_rn(__fmul_rn(mine.w, cs.w), __fmul_rn(other.w, sn.w));
+    } else {           // second half: x0 * s + x1 * c
+        r.x = __fadd_rn(__fmul_rn(other.x, sn.x), __fmul_rn(mine.x, cs.x));
+        r.y = __fadd_rn(__fmul_rn(other.y, sn.y), __fmul_rn(mine.y, cs.y));
+        r.z = __fadd_rn(__fmul_rn(other.z, sn.z), __fmul_rn(mine.z, cs.z));
+        r.w = __fadd_rn(__fmul_rn(other.w, sn.w), __fmul_rn(mine.w, cs.w));
+    }
+    return r;
+}
+
 // G query heads per KV head.  part_o [B*Hq][S][128], part_ml [B*Hq][S][2].
-template <int G>
+// FUSED: q is the raw [B, (Hq + 2 Hkv) * 128] output of the Q|K|V projection, kc / vc are written at the newest position.
+template <int G, bool FUSED>
 __global__ void __launch_bounds__(AT_THREADS, 1)
-    gqa_decode_stream_kernel(const float *__restrict__ q, const float *__restrict__ kc, const float *__restrict__ vc,
-                             const int *__restrict__ pos_ptr, int B, int Hq, int Hkv, int cap, int S, float scale,
-                             float *__restrict__ part_o, float *__restrict__ part_ml, int32_t *status)
+    gqa_decode_stream_kernel(const float *__restrict__ q, float *__restrict__ kc, float *__restrict__ vc,
+                             const int *__restrict__ pos_ptr, const float *__restrict__ cos_t, const float *__restrict__ sin_t, int B, int Hq,
+                             int Hkv, int cap, int S, float scale, float *__restrict__ part_o, float *__restrict__ part_ml, int32_t *status)
 {
     constexpr int P = 32 / G;                 // positions per batch
     constexpr int SLOT = P * AT_HD * 4;       // bytes of K (or V) per batch
@@ -119,6 +150,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int len = pg_ld_fresh(pos_ptr) + 1;
+    float4 rope_c = make_float4(1.f, 1.f, 1.f, 1.f), rope_s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (FUSED) {       // the row of the cos / sin tables of the newest position, [max_pos, 64]
+        rope_c = __ldg(reinterpret_cast<const float4 *>(cos_t + (int64_t)(len - 1) * (AT_HD / 2)) + (lane & 15));
+        rope_s = __ldg(reinterpret_cast<const float4 *>(sin_t + (int64_t)(len - 1) * (AT_HD / 2)) + (lane & 15));
+    }
+    const int qkv_heads = Hq + 2 * Hkv;
     const int chunk = at_chunk(len, S, P);
     const int units = B * Hkv * S;
     const int my_p = lane / G;             // lane i holds pair (position i / G, head i % G) after the butterfly
@@ -157,7 +194,23 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
         float4 qv[G];
 #pragma unroll
         for (int h = 0; h < G; h++) {
-            qv[h] = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * Hq + kvh * G + h) * AT_HD) + lane);
+            if (FUSED) {
+                const float4 raw = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * qkv_heads + kvh * G + h) * AT_HD) + lane);
+                qv[h] = at_rope(raw, rope_c, rope_s, lane);
+            } else {
+                qv[h] = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * Hq + kvh * G + h) * AT_HD) + lane);
+            }
+        }
+        // FUSED: this unit appends the newest token's key and value if its slice holds position len - 1
+        const bool appends = FUSED && (t0 + n == len);
+        float4 k_new = make_float4(0.f, 0.f, 0.f, 0.f), v_new = k_new;
+        if (appends) {
+            const float4 kraw = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * qkv_heads + Hq + kvh) * AT_HD) + lane);
+            k_new = at_rope(kraw, rope_c, rope_s, lane);
+            v_new = pg_ld_fresh(reinterpret_cast<const float4 *>(q + ((int64_t)b * qkv_heads + Hq + Hkv + kvh) * AT_HD) + lane);
+            const int64_t at = (((int64_t)b * Hkv + kvh) * cap + (len - 1)) * AT_HD;
+            reinterpret_cast<float4 *>(kc + at)[lane] = k_new;
+            reinterpret_cast<float4 *>(vc + at)[lane] = v_new;
         }
         float m_run = -INFINITY, l_run = 0.0f;
         float4 acc[G];
@@ -168,6 +221,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
             const uint32_t slot = fills % AT_SLOTS;
             if (!at_mbar_wait(bars + slot * 8, (fills / AT_SLOTS) & 1u, status)) return;
             const int valid = min(P, n - bi * P);
+            if (appends && bi == nb - 1) {
+                // the bulk copy brought the cache's old bytes for the newest position: put the new row in its place
+                const uint32_t off = slot * SLOT + (uint32_t)(valid - 1) * (AT_HD * 4) + lane * 16;
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(kring + off), "f"(k_new.x), "f"(k_new.y), "f"(k_new.z), "f"(k_new.w) : "memory");
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(vring + off), "f"(v_new.x), "f"(v_new.y), "f"(v_new.z), "f"(v_new.w) : "memory");
+                __syncwarp();
+            }
             // partial dot products of this lane's four elements: v[p * G + h]
             float v[32];
 #pragma unroll
@@ -265,9 +325,12 @@ int pgk_gqa_stream_splits(const pg_ctx *ctx, int64_t B, int64_t Hkv, int64_t cap
 
 bool pgk_gqa_stream_supports(int64_t G) { return G == 4 || G == 8; }
 
-int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, const float *d_k, const float *d_v, const int32_t *d_pos, int64_t B,
-                              int64_t Hq, int64_t Hkv, int64_t cap, int S, float scale, float *part_o, float *part_ml)
+int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, float *d_k, float *d_v, const int32_t *d_pos, const float *d_cos,
+                              const float *d_sin, int64_t B, int64_t Hq, int64_t Hkv, int64_t cap, int S, float scale, float *part_o,
+                              float *part_ml)
 {
+    // d_cos != NULL: d_q is the raw Q|K|V projection; the kernel applies RoPE and appends the newest key and value
+    const bool fused = d_cos != nullptr;
     const int G = (int)(Hq / Hkv);
     const int64_t units = B * Hkv * S;
     PG_REQUIRE(units <= 0x7fffffff, "gqa_attention_decode: too many (sequence, head, slice) units");
@@ -281,17 +344,19 @@ int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, const float *d_k, c
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (G == 4) {
-        cfg.dynamicSmemBytes = at_smem_bytes<4>();
-        PG_CUDA(cudaFuncSetAttribute(gqa_decode_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<4>()));
-        PG_CUDA(cudaLaunchKernelEx(&cfg, gqa_decode_stream_kernel<4>, d_q, d_k, d_v, (const int *)d_pos, (int)B, (int)Hq, (int)Hkv, (int)cap, S,
-                                   scale, part_o, part_ml, ctx->d_status));
-    } else {
-        cfg.dynamicSmemBytes = at_smem_bytes<8>();
-        PG_CUDA(cudaFuncSetAttribute(gqa_decode_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<8>()));
-        PG_CUDA(cudaLaunchKernelEx(&cfg, gqa_decode_stream_kernel<8>, d_q, d_k, d_v, (const int *)d_pos, (int)B, (int)Hq, (int)Hkv, (int)cap, S,
-                                   scale, part_o, part_ml, ctx->d_status));
+#define PG_AT_CASE(GG, FF)                                                                                                              \
+    {                                                                                                                                   \
+        cfg.dynamicSmemBytes = at_smem_bytes<GG>();                                                                                     \
+        PG_CUDA(cudaFuncSetAttribute(gqa_decode_stream_kernel<GG, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<GG>())); \
+        PG_CUDA(cudaLaunchKernelEx(&cfg, gqa_decode_stream_kernel<GG, FF>, d_q, d_k, d_v, (const int *)d_pos, d_cos, d_sin, (int)B, (int)Hq, \
+                                   (int)Hkv, (int)cap, S, scale, part_o, part_ml, ctx->d_status));                                      \
     }
+    if (G == 4) {
+        if (fused) PG_AT_CASE(4, true) else PG_AT_CASE(4, false)
+    } else {
+        if (fused) PG_AT_CASE(8, true) else PG_AT_CASE(8, false)
+    }
+#undef PG_AT_CASE
     PG_LAUNCHED();
     return PG_OK;
 }

@@ -7,7 +7,7 @@ linears of every layer as device-resident `QuantizedTensor`s -- fused `[Q | K | 
 (src/models/llama/attention.rs:51-71), O, fused `[gate | up]` (src/models/llama/decoder.rs:49-67), down,
 and the output head -- and runs one decode step for a batch of independent sequences:
 
-    x -> [RMSNorm+quantise] -> QKV -> [RoPE, KV append] -> [GQA attention + quantise] -> O
+    x -> [RMSNorm+quantise] -> QKV -> [RoPE, KV append, GQA attention + quantise] -> O
       -> [residual+RMSNorm+quantise] -> gate|up -> [SwiGLU+quantise] -> down -> (residual into the next norm)
     final: [residual+RMSNorm+quantise] -> lm_head -> [argmax, position += 1] -> [embedding] -> x
 
@@ -119,6 +119,8 @@ class LlamaInt8Decoder:
         S = self.lib.pg_gqa_decode_splits(gpu.handle, B, c.n_q_heads, c.n_kv_heads, c.capacity)
         self.work = torch.zeros(B * c.n_q_heads * S * 130, dtype=f32, device=dev)
         self.graph = None
+        # RoPE and the KV append run inside the attention kernel when it has the streaming form (4 or 8 query heads per KV head)
+        self.fuse_rope = False  # set below once validated: (c.n_q_heads // c.n_kv_heads) in (4, 8)
         torch.cuda.synchronize()   # torch filled the buffers on its own stream; the kernels use the context's
 
     # ---- state --------------------------------------------------------------------------------
@@ -144,10 +146,15 @@ class LlamaInt8Decoder:
             _lib.check(lib.pg_add_rmsnorm_quantize(h, P(self.x), P(delta) if delta is not None else None, P(L["attn_norm"]), B, c.hidden,
                                                    c.eps, P(self.q8), P(self.q8s), None))
             _lib.check(lib.pg_gemm_i8(h, P(self.q8), P(self.q8s), B, c.hidden, L["qkv"], P(self.qkv), None, _lib.ALGO_AUTO))
-            _lib.check(lib.pg_rope_kv_append(h, P(self.qkv), P(self.pos), P(self.cos), P(self.sin), B, c.n_q_heads, c.n_kv_heads, c.head_dim,
-                                             c.capacity, P(self.q_rot), P(self.kcache[i]), P(self.vcache[i])))
-            _lib.check(lib.pg_gqa_attention_decode(h, P(self.q_rot), P(self.kcache[i]), P(self.vcache[i]), P(self.pos), B, c.n_q_heads,
-                                                   c.n_kv_heads, c.head_dim, c.capacity, P(self.work), None, P(self.q8), P(self.q8s)))
+            if self.fuse_rope:
+                _lib.check(lib.pg_gqa_attention_decode_fused(h, P(self.qkv), P(self.pos), P(self.cos), P(self.sin), P(self.kcache[i]),
+                                                             P(self.vcache[i]), B, c.n_q_heads, c.n_kv_heads, c.head_dim, c.capacity,
+                                                             P(self.work), None, P(self.q8), P(self.q8s)))
+            else:
+                _lib.check(lib.pg_rope_kv_append(h, P(self.qkv), P(self.pos), P(self.cos), P(self.sin), B, c.n_q_heads, c.n_kv_heads,
+                                                 c.head_dim, c.capacity, P(self.q_rot), P(self.kcache[i]), P(self.vcache[i])))
+                _lib.check(lib.pg_gqa_attention_decode(h, P(self.q_rot), P(self.kcache[i]), P(self.vcache[i]), P(self.pos), B, c.n_q_heads,
+                                                       c.n_kv_heads, c.head_dim, c.capacity, P(self.work), None, P(self.q8), P(self.q8s)))
             _lib.check(lib.pg_gemm_i8(h, P(self.q8), P(self.q8s), B, c.hidden, L["o"], P(self.o), None, _lib.ALGO_AUTO))
             _lib.check(lib.pg_add_rmsnorm_quantize(h, P(self.x), P(self.o), P(L["ffn_norm"]), B, c.hidden, c.eps, P(self.q8), P(self.q8s), None))
             _lib.check(lib.pg_gemm_i8(h, P(self.q8), P(self.q8s), B, c.hidden, L["gate_up"], P(self.gate_up), None, _lib.ALGO_AUTO))

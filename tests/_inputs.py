@@ -26,3 +26,13 @@ def bits_equal(a, b):
     a = np.ascontiguousarray(a)
     b = np.ascontiguousarray(b)
     return a.shape == b.shape and np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+def lcg(n, seed):
+    """The LCG stream of tests/huffman_parity.rs:9-21 (f32 arithmetic as in the reference)."""
+    out = np.empty(n, np.float32)
+    state = seed
+    for i in range(n):
+        state = (state * 1103515245 + 12345) & 0xFFFFFFFF
+        out[i] = np.float32(np.float32(state) / np.float32(0xFFFFFFFF)) * np.float32(2.0) - np.float32(1.0)
+    return out

@@ -148,6 +148,17 @@ def test_rope_append_attention_embedding_argmax(pg, gpu, oracle):
         # the fused quantiser: bit-exact with the oracle's quantiser applied to the f32 rows the kernel produced
         qo, so = oracle.quantize_activations(out.cpu().numpy(), B, Hq * hd)
         assert np.array_equal(o8.cpu().numpy(), qo) and np.array_equal(o8s.cpu().numpy(), so)
+        if Hq // Hkv in (4, 8):
+            # RoPE + append inside the attention kernel: the same cache bits, the same output to the last few ulps
+            fK, fV = _t(K), _t(V)
+            fout = torch.zeros(B, Hq * hd, device="cuda")
+            torch.cuda.synchronize()
+            _lib.check(lib.pg_gqa_attention_decode_fused(gpu.handle, tq.data_ptr(), tpos.data_ptr(), tc.data_ptr(), ts.data_ptr(), fK.data_ptr(),
+                                                         fV.data_ptr(), B, Hq, Hkv, hd, cap, work.data_ptr(), fout.data_ptr(), None, None))
+            gpu.sync()
+            assert np.array_equal(fK.cpu().numpy(), K2) and np.array_equal(fV.cpu().numpy(), V2)
+            assert np.abs(fout.cpu().numpy() - ref).max() <= 1e-5 * np.abs(ref).max()
+            assert gpu.device_status() == 0
     # embedding and argmax (first maximum; the position is advanced once)
     table = normal(g, (50, 64))
     tok = np.array([3, 49, 0], np.int32)
