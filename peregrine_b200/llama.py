@@ -120,7 +120,7 @@ class LlamaInt8Decoder:
         self.work = torch.zeros(B * c.n_q_heads * S * 130, dtype=f32, device=dev)
         self.graph = None
         # RoPE and the KV append run inside the attention kernel when it has the streaming form (4 or 8 query heads per KV head)
-        self.fuse_rope = False  # set below once validated: (c.n_q_heads // c.n_kv_heads) in (4, 8)
+        self.fuse_rope = (c.n_q_heads // c.n_kv_heads) in (4, 8)
         torch.cuda.synchronize()   # torch filled the buffers on its own stream; the kernels use the context's
 
     # ---- state --------------------------------------------------------------------------------
