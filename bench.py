@@ -12,9 +12,12 @@ Metric: achieved HBM bandwidth in GB/s = algorithmic bytes of the sweep / time, 
     python bench.py --gpus N --steps K --warmup W            this library
     python bench.py --impl reference ...                     the reference's CPU algorithm (C port)
 
-With N > 1 the weights are sharded by output column over the ranks (one process per GPU,
-torchrun) and the output slices are all-gathered over NCCL; `value` is the whole job's bytes over
-the slowest rank's time.
+With N > 1 (one process per GPU, torchrun) every rank holds a full replica of the weights and runs its
+own sweep, with no data-path collective: the rows of a decode batch are independent sequences and
+the matrices fit one GPU many times over, so this is how the path scales out (`scaling: weak`;
+`value` is all ranks' bytes over the slowest rank's time).  `--parallel shard` runs the other layout:
+weights sharded by output column over the ranks, one sweep, output slices all-gathered (by peer stores
+over NVLink, or `--collective nccl`), reported as strong scaling.
 
 Cache discipline: every case of a step reads its own copy of the weights (three copies per shape,
 402 MB in total), so a weight matrix is re-read only after ~400 MB of other traffic (L2 is 126 MB).
@@ -628,8 +631,10 @@ def main():
     ap.add_argument("--extra", action="store_true", help="also time the prefill GEMM and the GGUF products")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama-8B-shape decode stack measurement (N = 1 only)")
-    ap.add_argument("--parallel", default="shard", choices=["shard", "replicas"],
-                    help="N > 1: column-sharded weights with an all-gather (strong scaling, default) or one full replica per GPU (weak)")
+    ap.add_argument("--parallel", default="replicas", choices=["replicas", "shard"],
+                    help="N > 1: one full replica of the weights and one sweep per GPU, no collective (weak scaling, default: the sweep's "
+                         "rows are independent sequences and the matrices fit one GPU many times over), or column-sharded weights with an "
+                         "all-gather of the output slices (strong scaling of one sweep)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: all-gather by peer stores recorded in the step graph (default) or eager NCCL")
     args = ap.parse_args()
