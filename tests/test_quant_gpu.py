@@ -201,7 +201,7 @@ def test_decode_gemv_sweep(pg, gpu, oracle_mt, idx, m, k, n):
 
 @pytest.mark.parametrize("m,k,n", [
     (1, 64, 1), (2, 128, 9), (8, 192, 8), (9, 64, 17), (16, 576, 24), (16, 4096 + 64, 100), (5, 1088, 1000), (12, 2048, 130),
-    (3, 8192, 40), (8, 8192 + 128, 33), (16, 4160, 3000), (8, 14336, 100), (2, 65536 - 64, 20), (7, 512, 2369 * 8 + 3),
+    (3, 8192, 40), (8, 8192 + 128, 33), (16, 4160, 3000), (8, 14336, 100), (2, 65536 - 64, 20), (7, 512, 2369 * 16 + 3),
 ])
 def test_warp_stream_kernel_ragged_shapes(pg, gpu, oracle_mt, m, k, n):
     """Edges of the persistent decode kernel: N not a multiple of the 8-column tile, K not a multiple of the 512-byte
@@ -220,7 +220,7 @@ def test_warp_stream_k_split_over_a_cluster(pg, gpu, oracle_mt, kw, cs):
     gpu.lib.pg_tune_wstream_kw(kw)
     gpu.lib.pg_tune_wstream_cluster(cs)
     try:
-        for m, k, n in ((1, 4096, 520), (16, 4096, 8), (7, 4032, 33), (16, 4096, 3000), (9, 4096, 2369 * 8 + 5)):
+        for m, k, n in ((1, 4096, 520), (16, 4096, 8), (7, 4032, 33), (16, 4096, 3000), (9, 4096, 2369 * 16 + 5)):
             x, w = linear_inputs(m, k, n, 850 + kw + m)
             _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["wstream", "wstream"])
         gpu.lib.pg_tune_wstream_cluster(0)
