@@ -204,6 +204,10 @@ PG_API int32_t pg_matmul_gguf_host(pg_ctx *ctx, const float *x, int64_t m, const
  * dequantise -> quantize_weights(rows, cols), all on the device. */
 PG_API int32_t pg_qtensor_from_q8_0(pg_ctx *ctx, const uint8_t *raw, size_t raw_len, int64_t rows, int64_t cols,
                                     pg_qtensor **out);
+/* serial::read_quantized_tensor (src/serial.rs:161-222) keeps data_i8 [rows, cols] and scales [cols] in the file and
+   rebuilds data_i8_t on load: here the transposition runs on the device.  Host arrays in, resident tensor out. */
+PG_API int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scales, int64_t rows, int64_t cols,
+                                  pg_qtensor **out);
 
 /* ---- all-gather of output slices between the GPUs of one node; API precedent:
  *      Communicator::allgather (src/comm/communicator.rs:162-191, a CPU shared-memory ring) ----

@@ -770,6 +770,46 @@ int32_t pg_qtensor_from_q8_0(pg_ctx *ctx, const uint8_t *raw, size_t raw_len, in
     return rc;
 }
 
+// A quantised tensor as the serial format stores it (src/serial.rs:127-222: i8 [rows, cols] row-major + f32 scales
+// [cols]): uploaded once, the GEMM layout data_i8_t [cols, rows] rebuilt on the device.
+int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scales, int64_t rows, int64_t cols, pg_qtensor **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "qtensor_from_i8: out is null");
+    *out = nullptr;
+    PG_REQUIRE(rows >= 0 && cols >= 0, "qtensor_from_i8: negative shape");
+    PG_REQUIRE(rows * cols == 0 || data_i8, "qtensor_from_i8: data is null");
+    PG_REQUIRE(cols == 0 || scales, "qtensor_from_i8: scales are null");
+    pg_qtensor *t = new (std::nothrow) pg_qtensor();
+    if (!t) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    t->rows = rows;
+    t->cols = cols;
+    t->owned = true;
+    const size_t tb = (size_t)rows * cols;
+    void *d_q = nullptr, *d_t = nullptr, *d_s = nullptr;
+    cudaError_t e = cudaMalloc(&d_q, tb + 16);
+    if (e == cudaSuccess) e = cudaMalloc(&d_t, tb + 1024);   // 1 KiB of slack for tiled loads of the last rows
+    if (e == cudaSuccess) e = cudaMalloc(&d_s, (size_t)(cols ? cols : 1) * 4);
+    if (e == cudaSuccess && tb) e = cudaMemcpyAsync(d_q, data_i8, tb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess && cols) e = cudaMemcpyAsync(d_s, scales, (size_t)cols * 4, cudaMemcpyHostToDevice, ctx->stream);
+    int32_t rc = PG_OK;
+    if (e == cudaSuccess) rc = pgk_transpose_i8(ctx, (const int8_t *)d_q, rows, cols, (int8_t *)d_t);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // the host arrays may go away after the call
+    if (e != cudaSuccess || rc != PG_OK) {
+        cudaFree(d_q);
+        cudaFree(d_t);
+        cudaFree(d_s);
+        delete t;
+        if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "qtensor_from_i8: %s", cudaGetErrorString(e));
+        return rc;
+    }
+    t->d_data_i8 = (const int8_t *)d_q;
+    t->d_data_i8_t = (const int8_t *)d_t;
+    t->d_scales = (const float *)d_s;
+    *out = t;
+    return PG_OK;
+}
+
 int32_t pg_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n, float *d_out)
 {
     PG_ENTER(ctx);

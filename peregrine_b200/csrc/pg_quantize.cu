@@ -240,6 +240,33 @@ int32_t pgk_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_
     return PG_OK;
 }
 
+// [rows, cols] i8 -> [cols, rows] i8 through a 64 x 64 tile in shared memory (one byte of padding per row keeps the
+// column reads off a single bank): what read_quantized_tensor does on the host to rebuild data_i8_t (src/serial.rs:203-208).
+__global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t *__restrict__ in, int64_t rows, int64_t cols, int8_t *__restrict__ out)
+{
+    __shared__ int8_t tile[64][65];
+    const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int r = i >> 6, c = i & 63;
+        if (r0 + r < rows && c0 + c < cols) tile[r][c] = in[(r0 + r) * cols + c0 + c];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        const int c = i >> 6, r = i & 63;
+        if (r0 + r < rows && c0 + c < cols) out[(c0 + c) * rows + r0 + r] = tile[r][c];
+    }
+}
+
+int32_t pgk_transpose_i8(pg_ctx *ctx, const int8_t *d_in, int64_t rows, int64_t cols, int8_t *d_out)
+{
+    if (rows == 0 || cols == 0) return PG_OK;
+    const dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+    PG_REQUIRE(grid.y <= 65535, "transpose_i8: rows=%lld too large", (long long)rows);
+    transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(d_in, rows, cols, d_out);
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
 int32_t pgk_dequantize(pg_ctx *ctx, const int8_t *d_q, const float *d_scales, int64_t rows, int64_t cols, float *d_out)
 {
     const int64_t total = rows * cols;
