@@ -470,8 +470,29 @@ def run_ours(args):
         }
         if args.extra:
             line["also"] = extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks)
-        if world == 1 and not args.no_llama:
-            line.setdefault("also", {})["llama8b_int8_decode"] = llama_decode_measurement(gpu, torch, stream, dev, hbm_peak)
+    # The Llama-3-8B-shape decode stack: on one GPU, or (replicas) one full model and one batch of 16 sequences per GPU
+    if not args.no_llama and (world == 1 or replicas):
+        peak_l = 6532.9
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peak_l = float(json.load(f).get("hbm_gbs", peak_l))
+        except (OSError, ValueError):
+            pass
+        ll = llama_decode_measurement(gpu, torch, stream, dev, peak_l)
+        if world > 1:
+            # whole-job tokens per second: all replicas' tokens over the slowest replica's time
+            t = torch.tensor([ll["ms_per_step"]], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ll["ms_per_step"] = float(t.item())
+            ll["tok_s"] = world * ll["batch"] * 1e3 / ll["ms_per_step"]
+            ll["replicas"] = world
+            ll["hbm_gbs"] = world * ll["bytes_per_step"] / (ll["ms_per_step"] * 1e-3) / 1e9
+            ll["frac_of_measured_hbm"] = ll["hbm_gbs"] / (world * peak_l)
+            t = torch.tensor([ll["e2e_tok_s"]], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            ll["e2e_tok_s"] = float(t.item())
+        if rank == 0:
+            line.setdefault("also", {})["llama8b_int8_decode"] = ll
     if world > 1:
         dist.barrier()
         if exs:
