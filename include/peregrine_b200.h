@@ -209,6 +209,22 @@ PG_API int32_t pg_qtensor_from_q8_0(pg_ctx *ctx, const uint8_t *raw, size_t raw_
 PG_API int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scales, int64_t rows, int64_t cols,
                                   pg_qtensor **out);
 
+/* Huffman-coded int8 weights (src/huffman.rs).  One canonical code (256 bit lengths, the code book of
+ * HuffmanTable::to_bytes / from_bytes, src/huffman.rs:287-307) shared by `num_streams` bitstreams that lie back to
+ * back in `streams` (the layout of serial::write_huffman_tensor, src/serial.rs:320-365); stream s holds
+ * stream_symbols[s] code words in stream_bytes[s] bytes.
+ *   pg_huffman_decode_host   HuffmanTable::decode (src/huffman.rs:254-284) over every stream: host in, host out
+ *                            (sum of stream_symbols bytes), the decode itself on the device.
+ *   pg_qtensor_from_huffman  HuffmanTensor::decode_to_quantized + to_gpu (src/huffman.rs:374-437): the compressed
+ *                            bytes are uploaded, decoded and transposed on the device; the tensor comes back resident,
+ *                            ready for pg_matmul_quantized (what matmul_huffman does, src/huffman.rs:465-476).
+ * The symbols must add up to rows * cols (the reference asserts it), else PG_ERR_INVALID. */
+PG_API int32_t pg_huffman_decode_host(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
+                                      const uint64_t *stream_bytes, const uint8_t *streams, int8_t *out);
+PG_API int32_t pg_qtensor_from_huffman(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
+                                       const uint64_t *stream_bytes, const uint8_t *streams, const float *scales, int64_t rows,
+                                       int64_t cols, pg_qtensor **out);
+
 /* ---- all-gather of output slices between the GPUs of one node; API precedent:
  *      Communicator::allgather (src/comm/communicator.rs:162-191, a CPU shared-memory ring) ----
  * One process per GPU.  Every rank creates an exchange (a result buffer of y_bytes plus control words,

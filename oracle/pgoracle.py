@@ -1,4 +1,4 @@
-"""numpy front end of the CPU oracle (oracle/peregrine_oracle.c, oracle/gguf_encode.c).
+"""numpy front end of the CPU oracle (oracle/peregrine_oracle.c, oracle/gguf_encode.c, oracle/huffman_oracle.c).
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the
 benchmark's CPU-baseline leg.  The product package never imports it.
@@ -32,7 +32,7 @@ _sz = C.c_size_t
 def build(force: bool = False) -> None:
     """Compile both oracle libraries with oracle/Makefile (gcc only)."""
     libs = [os.path.join(_BUILD, n) for n in ("libpgoracle.so", "libpgoracle_mt.so")]
-    srcs = [os.path.join(_HERE, n) for n in ("peregrine_oracle.c", "gguf_encode.c", "Makefile")]
+    srcs = [os.path.join(_HERE, n) for n in ("peregrine_oracle.c", "gguf_encode.c", "huffman_oracle.c", "Makefile")]
     stale = force or any(
         not os.path.exists(l) or os.path.getmtime(l) < max(os.path.getmtime(s) for s in srcs) for l in libs
     )
@@ -78,6 +78,14 @@ class Oracle:
         lib.pgo_matmul_f32_wt.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _f32p]
         lib.pgo_matmul_f64acc_wt.argtypes = [_f32p, _f32p, _sz, _sz, _sz, _f64p]
         lib.pgo_matmul_dequant_w8a32.argtypes = [_f32p, _i8p, _f32p, _sz, _sz, _sz, _f32p]
+        _u32p = np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS")
+        _u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
+        lib.pgo_huffman_from_frequencies.argtypes = [_u64p, _u8p, _u32p]
+        lib.pgo_huffman_canonical_codes.argtypes = [_u8p, _u32p]
+        lib.pgo_huffman_build_lut.argtypes = [_u8p, _u32p, _u32p]
+        lib.pgo_huffman_encode.argtypes = [_u8p, _u32p, _i8p, _sz, _u8p]
+        lib.pgo_huffman_encode.restype = _sz
+        lib.pgo_huffman_decode.argtypes = [_u32p, _u8p, _sz, _sz, _i8p]
         for name in ("pgo_encode_q8_0", "pgo_encode_q4_0", "pgo_encode_q4_1"):
             getattr(lib, name).argtypes = [_f32p, _sz, _u8p]
 
@@ -203,3 +211,38 @@ class Oracle:
         out = np.empty(w.size // 32 * bs, np.uint8)
         getattr(self.lib, "pgo_encode_" + kind)(w, w.size, out)
         return out
+
+    # ---- Huffman-coded int8 weights (src/huffman.rs) ------------------------------------------
+    def huffman_from_frequencies(self, freqs):
+        """HuffmanTable::from_frequencies -> (bit_lengths[256] u8, codes[256] u32)."""
+        f = np.ascontiguousarray(freqs, np.uint64)
+        assert f.size == 256
+        bl, codes = np.zeros(256, np.uint8), np.zeros(256, np.uint32)
+        self.lib.pgo_huffman_from_frequencies(f, bl, codes)
+        return bl, codes
+
+    def huffman_canonical_codes(self, bit_lengths):
+        bl = np.ascontiguousarray(bit_lengths, np.uint8)
+        codes = np.zeros(256, np.uint32)
+        self.lib.pgo_huffman_canonical_codes(bl, codes)
+        return codes
+
+    def huffman_lut(self, bit_lengths, codes):
+        """The 4096-entry decode table in the packing of to_gpu_lut: (bit_length << 8) | (symbol + 128)."""
+        lut = np.zeros(4096, np.uint32)
+        self.lib.pgo_huffman_build_lut(np.ascontiguousarray(bit_lengths, np.uint8), np.ascontiguousarray(codes, np.uint32), lut)
+        return lut
+
+    def huffman_encode(self, bit_lengths, codes, data):
+        d = np.ascontiguousarray(data, np.int8).reshape(-1)
+        bl = np.ascontiguousarray(bit_lengths, np.uint8)
+        out = np.zeros(int(bl[(d.astype(np.int16) + 128)].astype(np.int64).sum() + 7) // 8 + 1, np.uint8)
+        n = self.lib.pgo_huffman_encode(bl, np.ascontiguousarray(codes, np.uint32), d, d.size, out)
+        return out[:n].copy()
+
+    def huffman_decode(self, lut, bitstream, num_symbols):
+        bs = np.ascontiguousarray(bitstream, np.uint8).reshape(-1)
+        out = np.zeros(num_symbols, np.int8)
+        self.lib.pgo_huffman_decode(np.ascontiguousarray(lut, np.uint32), bs if bs.size else np.zeros(1, np.uint8), bs.size, num_symbols, out)
+        return out
+

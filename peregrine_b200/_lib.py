@@ -86,6 +86,8 @@ SIGNATURES = {
     "pg_matmul_gguf_host": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "pg_qtensor_from_q8_0": (_i32, [_vp, _vp, _sz, _i64, _i64, C.POINTER(_vp)]),
     "pg_qtensor_from_i8": (_i32, [_vp, _vp, _vp, _i64, _i64, C.POINTER(_vp)]),
+    "pg_huffman_decode_host": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp]),
+    "pg_qtensor_from_huffman": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, C.POINTER(_vp)]),
     "pg_exchange_create": (_i32, [_vp, _i32, _i32, _sz, _vp, C.POINTER(_vp)]),
     "pg_exchange_connect": (_i32, [_vp, _vp, _vp]),
     "pg_exchange_result": (_vp, [_vp]),

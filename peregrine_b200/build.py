@@ -30,6 +30,7 @@ SOURCES = [
     "pg_noalloc.cu",
     "pg_peer.cu",
     "pg_llama.cu", "pg_llama_attn.cu",
+    "pg_huffman.cu",
 ]
 
 NVCC_FLAGS = [

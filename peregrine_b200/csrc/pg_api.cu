@@ -810,6 +810,94 @@ int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scal
     return PG_OK;
 }
 
+// Uploads the bitstreams (back to back, as the serial format holds them) and decodes them into d_out.
+static int32_t huffman_decode_to_device(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
+                                        const uint64_t *stream_bytes, const uint8_t *streams, uint64_t expect_symbols, int8_t *d_out)
+{
+    PG_REQUIRE(bit_lengths != nullptr, "huffman: the code book is null");
+    PG_REQUIRE(num_streams >= 0 && (num_streams == 0 || (stream_symbols && stream_bytes)), "huffman: stream tables are null");
+    uint64_t symbols = 0, bytes = 0;
+    for (int64_t s = 0; s < num_streams; s++) {
+        symbols += stream_symbols[s];
+        bytes += stream_bytes[s];
+    }
+    // decode_to_quantized asserts that the streams hold rows * cols symbols (src/huffman.rs:384)
+    PG_REQUIRE(symbols == expect_symbols, "huffman: the streams hold %llu symbols, %llu expected", (unsigned long long)symbols,
+               (unsigned long long)expect_symbols);
+    PG_REQUIRE(bytes == 0 || streams, "huffman: the bitstreams are null");
+    if (symbols == 0) return PG_OK;
+    uint8_t *d_bits = nullptr;
+    cudaError_t e = cudaMalloc((void **)&d_bits, bytes + 16);   // the decoder reads whole words: 8 bytes of slack
+    if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "huffman: %s", cudaGetErrorString(e));
+    if (bytes) e = cudaMemcpyAsync(d_bits, streams, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    int32_t rc = PG_OK;
+    if (e == cudaSuccess) rc = pgk_huffman_decode(ctx, bit_lengths, num_streams, stream_symbols, stream_bytes, d_bits, d_out);
+    const cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d_bits);
+    if (e != cudaSuccess || (rc == PG_OK && e2 != cudaSuccess)) PG_FAIL(PG_ERR_CUDA, "huffman: %s", cudaGetErrorString(e != cudaSuccess ? e : e2));
+    return rc;
+}
+
+int32_t pg_huffman_decode_host(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
+                               const uint64_t *stream_bytes, const uint8_t *streams, int8_t *out)
+{
+    PG_ENTER(ctx);
+    uint64_t symbols = 0;
+    for (int64_t s = 0; s < num_streams && stream_symbols; s++) symbols += stream_symbols[s];
+    if (symbols == 0 && num_streams >= 0) return PG_OK;
+    PG_REQUIRE(out != nullptr, "huffman_decode: out is null");
+    int8_t *d_out = nullptr;
+    cudaError_t e = cudaMalloc((void **)&d_out, symbols + 16);
+    if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "huffman_decode: %s", cudaGetErrorString(e));
+    int32_t rc = huffman_decode_to_device(ctx, bit_lengths, num_streams, stream_symbols, stream_bytes, streams, symbols, d_out);
+    if (rc == PG_OK) {
+        e = cudaMemcpyAsync(out, d_out, symbols, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    }
+    cudaFree(d_out);
+    if (rc == PG_OK && e != cudaSuccess) PG_FAIL(PG_ERR_CUDA, "huffman_decode: %s", cudaGetErrorString(e));
+    return rc;
+}
+
+int32_t pg_qtensor_from_huffman(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
+                                const uint64_t *stream_bytes, const uint8_t *streams, const float *scales, int64_t rows, int64_t cols,
+                                pg_qtensor **out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(out != nullptr, "qtensor_from_huffman: out is null");
+    *out = nullptr;
+    PG_REQUIRE(rows >= 0 && cols >= 0, "qtensor_from_huffman: negative shape");
+    PG_REQUIRE(cols == 0 || scales, "qtensor_from_huffman: scales are null");
+    pg_qtensor *t = new (std::nothrow) pg_qtensor();
+    if (!t) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
+    t->rows = rows;
+    t->cols = cols;
+    t->owned = true;
+    const size_t tb = (size_t)rows * cols;
+    void *d_q = nullptr, *d_t = nullptr, *d_s = nullptr;
+    cudaError_t e = cudaMalloc(&d_q, tb + 16);
+    if (e == cudaSuccess) e = cudaMalloc(&d_t, tb + 1024);   // 1 KiB of slack for tiled loads of the last rows
+    if (e == cudaSuccess) e = cudaMalloc(&d_s, (size_t)(cols ? cols : 1) * 4);
+    if (e == cudaSuccess && cols) e = cudaMemcpyAsync(d_s, scales, (size_t)cols * 4, cudaMemcpyHostToDevice, ctx->stream);
+    int32_t rc = PG_OK;
+    if (e == cudaSuccess) rc = huffman_decode_to_device(ctx, bit_lengths, num_streams, stream_symbols, stream_bytes, streams, tb, (int8_t *)d_q);
+    if (e == cudaSuccess && rc == PG_OK) rc = pgk_transpose_i8(ctx, (const int8_t *)d_q, rows, cols, (int8_t *)d_t);
+    if (e == cudaSuccess && rc == PG_OK) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess || rc != PG_OK) {
+        cudaFree(d_q);
+        cudaFree(d_t);
+        cudaFree(d_s);
+        delete t;
+        if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "qtensor_from_huffman: %s", cudaGetErrorString(e));
+        return rc;
+    }
+    t->d_data_i8 = (const int8_t *)d_q;
+    t->d_data_i8_t = (const int8_t *)d_t;
+    t->d_scales = (const float *)d_s;
+    *out = t;
+    return PG_OK;
+}
+
 int32_t pg_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n, float *d_out)
 {
     PG_ENTER(ctx);

@@ -1,5 +1,5 @@
-"""The quantised serial format: host-side mirror of `write_quantized_tensor` / `read_quantized_tensor`
-(src/serial.rs:124-222).
+"""The quantised serial formats: host-side mirror of `write_quantized_tensor` / `read_quantized_tensor`
+(src/serial.rs:124-222) and of `write_huffman_tensor` / `read_huffman_tensor` (src/serial.rs:315-443).
 
     [name_len: u32][name: utf-8][dtype = 1: u8][ndim = 2: u32][rows: u32][cols: u32]
     [data_i8: rows * cols bytes, row-major][scales: cols x f32]                      (all little-endian)
@@ -7,6 +7,13 @@
 Writing is byte bookkeeping.  Reading hands the int8 matrix to the GPU, where the GEMM layout
 `data_i8_t` [cols, rows] is rebuilt (the reference transposes on the host, src/serial.rs:203-208): the
 tensor comes back resident, with its host arrays filled in.
+
+A Huffman record keeps the int8 matrix as bitstreams:
+
+    [name_len: u32][name][dtype = 3: u8][ndim = 2: u32][rows: u32][cols: u32][code book: 256 bit lengths]
+    [num_streams: u32][symbols per stream: u32 each][bytes per stream: u32 each][bitstreams][scales: cols x f32]
+
+and is read back as a `HuffmanTensor`, whose `to_gpu` sends the compressed bytes to the device and decodes there.
 
 Where the reference returns `io::Error` (short reads, invalid UTF-8) this raises `ValueError`; where
 it asserts (`expected dtype=1`, `quantized tensors must be 2D`) this raises `SerialPanic`.
@@ -77,3 +84,48 @@ def read_quantized_tensor(file: BinaryIO, gpu: Optional[GpuContext] = None) -> T
         qt.from_gpu(gpu)
         assert np.array_equal(qt.data_i8, keep_q) and np.array_equal(qt.scales.view(np.uint32), keep_s.view(np.uint32))
     return name, qt
+
+
+def write_huffman_tensor(file: BinaryIO, name: str, ht) -> None:
+    """src/serial.rs:320-365"""
+    name_bytes = name.encode("utf-8")
+    scales = np.ascontiguousarray(ht.scales, np.float32).reshape(-1)
+    if len(ht.streams) != ht.num_streams or len(ht.stream_lengths) != ht.num_streams:
+        raise ValueError("write_huffman_tensor: one stream and one length per stream")
+    file.write(struct.pack("<I", len(name_bytes)))
+    file.write(name_bytes)
+    file.write(b"\x03")                                   # dtype tag: 3 = Huffman coded
+    file.write(struct.pack("<III", 2, ht.rows, ht.cols))
+    file.write(ht.table.to_bytes())
+    file.write(struct.pack("<I", ht.num_streams))
+    file.write(struct.pack(f"<{ht.num_streams}I", *ht.stream_lengths))
+    file.write(struct.pack(f"<{ht.num_streams}I", *[len(s) for s in ht.streams]))
+    for s in ht.streams:
+        file.write(bytes(s))
+    file.write(scales.astype("<f4", copy=False).tobytes())
+
+
+def read_huffman_tensor(file: BinaryIO):
+    """src/serial.rs:367-443 -> (name, HuffmanTensor)."""
+    from .huffman import HuffmanTable, HuffmanTensor
+
+    (name_len,) = struct.unpack("<I", _read_exact(file, 4))
+    try:
+        name = _read_exact(file, name_len).decode("utf-8")
+    except UnicodeDecodeError as e:
+        raise ValueError(f"invalid utf-8 sequence: {e}") from e
+    dtype = _read_exact(file, 1)[0]
+    if dtype != 3:
+        raise SerialPanic("expected dtype=3 (Huffman) for huffman tensor")
+    (ndim,) = struct.unpack("<I", _read_exact(file, 4))
+    if ndim != 2:
+        raise SerialPanic("huffman tensors must be 2D")
+    rows, cols = struct.unpack("<II", _read_exact(file, 8))
+    table = HuffmanTable.from_bytes(_read_exact(file, 256))
+    (num_streams,) = struct.unpack("<I", _read_exact(file, 4))
+    lengths = list(struct.unpack(f"<{num_streams}I", _read_exact(file, 4 * num_streams)))
+    sizes = struct.unpack(f"<{num_streams}I", _read_exact(file, 4 * num_streams))
+    streams = [_read_exact(file, n) for n in sizes]
+    scales = np.frombuffer(_read_exact(file, cols * 4), "<f4").astype(np.float32)
+    return name, HuffmanTensor(table, streams, lengths, scales, rows, cols, num_streams)
+
