@@ -810,7 +810,7 @@ int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scal
     return PG_OK;
 }
 
-// Uploads the bitstreams (back to back, as the serial format holds them) and decodes them into d_out.
+// Checks the stream tables and decodes the bitstreams (host memory, back to back as the serial format holds them) into d_out.
 static int32_t huffman_decode_to_device(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
                                         const uint64_t *stream_bytes, const uint8_t *streams, uint64_t expect_symbols, int8_t *d_out)
 {
@@ -826,16 +826,7 @@ static int32_t huffman_decode_to_device(pg_ctx *ctx, const uint8_t *bit_lengths,
                (unsigned long long)expect_symbols);
     PG_REQUIRE(bytes == 0 || streams, "huffman: the bitstreams are null");
     if (symbols == 0) return PG_OK;
-    uint8_t *d_bits = nullptr;
-    cudaError_t e = cudaMalloc((void **)&d_bits, bytes + 16);   // the decoder reads whole words: 8 bytes of slack
-    if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "huffman: %s", cudaGetErrorString(e));
-    if (bytes) e = cudaMemcpyAsync(d_bits, streams, bytes, cudaMemcpyHostToDevice, ctx->stream);
-    int32_t rc = PG_OK;
-    if (e == cudaSuccess) rc = pgk_huffman_decode(ctx, bit_lengths, num_streams, stream_symbols, stream_bytes, d_bits, d_out);
-    const cudaError_t e2 = cudaStreamSynchronize(ctx->stream);
-    cudaFree(d_bits);
-    if (e != cudaSuccess || (rc == PG_OK && e2 != cudaSuccess)) PG_FAIL(PG_ERR_CUDA, "huffman: %s", cudaGetErrorString(e != cudaSuccess ? e : e2));
-    return rc;
+    return pgk_huffman_decode(ctx, bit_lengths, num_streams, stream_symbols, stream_bytes, streams, d_out);
 }
 
 int32_t pg_huffman_decode_host(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,

@@ -165,9 +165,9 @@ int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales);
 int32_t pgk_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int8_t *d_q, int8_t *d_qt, float *d_scales);
 int32_t pgk_transpose_i8(pg_ctx *ctx, const int8_t *d_in, int64_t rows, int64_t cols, int8_t *d_out);
-// Huffman streams (back to back in d_data, which starts on a word and has 8 bytes of slack) -> int8 symbols back to back
+// Huffman streams (back to back in host memory) -> int8 symbols back to back on the device
 int32_t pgk_huffman_decode(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
-                           const uint64_t *stream_bytes, const uint8_t *d_data, int8_t *d_out);
+                           const uint64_t *stream_bytes, const uint8_t *h_data, int8_t *d_out);
 int32_t pgk_dequantize(pg_ctx *ctx, const int8_t *d_q, const float *d_scales, int64_t rows, int64_t cols, float *d_out);
 int32_t pgk_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t m, int64_t k, int64_t n, float *d_out);
 // pg_gemm_naive.cu

@@ -257,9 +257,48 @@ __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t *__restr
     }
 }
 
+// The same for shapes and pointers that allow 32-bit accesses: a 128 x 128 tile, rows read and written as whole
+// 128-byte lines.  The tile's row stride of 129 bytes puts the four bytes a thread gathers for one output word, and
+// the words of the 32 lanes, in different banks.
+__global__ void __launch_bounds__(256) transpose_i8_words_kernel(const int8_t *__restrict__ in, int64_t rows, int64_t cols, int8_t *__restrict__ out)
+{
+    __shared__ uint8_t tile[128 * 129];
+    const int64_t r0 = (int64_t)blockIdx.y * 128, c0 = (int64_t)blockIdx.x * 128;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t v[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int r = warp * 16 + i;
+        v[i] = (r0 + r < rows && c0 + 4 * lane < cols) ? __ldg((const uint32_t *)(in + (r0 + r) * cols + c0) + lane) : 0u;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        uint8_t *t = tile + (warp * 16 + i) * 129 + 4 * lane;
+        t[0] = (uint8_t)v[i];
+        t[1] = (uint8_t)(v[i] >> 8);
+        t[2] = (uint8_t)(v[i] >> 16);
+        t[3] = (uint8_t)(v[i] >> 24);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int c = warp * 16 + i;
+        if (c0 + c >= cols || r0 + 4 * lane >= rows) continue;
+        const uint8_t *t = tile + (4 * lane) * 129 + c;
+        const uint32_t w = (uint32_t)t[0] | ((uint32_t)t[129] << 8) | ((uint32_t)t[258] << 16) | ((uint32_t)t[387] << 24);
+        *((uint32_t *)(out + (c0 + c) * rows + r0) + lane) = w;
+    }
+}
+
 int32_t pgk_transpose_i8(pg_ctx *ctx, const int8_t *d_in, int64_t rows, int64_t cols, int8_t *d_out)
 {
     if (rows == 0 || cols == 0) return PG_OK;
+    if (rows % 4 == 0 && cols % 4 == 0 && (((uintptr_t)d_in | (uintptr_t)d_out) & 3) == 0 && (rows + 127) / 128 <= 65535) {
+        const dim3 grid((unsigned)((cols + 127) / 128), (unsigned)((rows + 127) / 128));
+        transpose_i8_words_kernel<<<grid, 256, 0, ctx->stream>>>(d_in, rows, cols, d_out);
+        PG_LAUNCHED();
+        return PG_OK;
+    }
     const dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
     PG_REQUIRE(grid.y <= 65535, "transpose_i8: rows=%lld too large", (long long)rows);
     transpose_i8_kernel<<<grid, 256, 0, ctx->stream>>>(d_in, rows, cols, d_out);

@@ -239,7 +239,11 @@ class HuffmanTensor:
         gpu = gpu or current_gpu()
         if sum(self.stream_lengths) != self.rows * self.cols:
             raise HuffmanPanic(f"assertion failed: the streams hold {sum(self.stream_lengths)} symbols, {self.rows * self.cols} expected")
-        packed, sizes, lens = _stream_tables(self.streams, self.stream_lengths)
+        # the streams back to back, as a file holds them; kept for the next call while the streams stay the same objects
+        key = (tuple(id(x) for x in self.streams), tuple(self.stream_lengths))
+        if getattr(self, "_packed_key", None) != key:
+            self._packed, self._packed_key = _stream_tables(self.streams, self.stream_lengths), key
+        packed, sizes, lens = self._packed
         h = C.c_void_p()
         _lib.check(gpu.lib.pg_qtensor_from_huffman(gpu.handle, _ptr(self.table.bit_lengths), len(lens), _ptr(lens), _ptr(sizes),
                                                    _ptr(packed), _ptr(self.scales), self.rows, self.cols, C.byref(h)))

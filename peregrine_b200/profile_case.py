@@ -5,6 +5,7 @@
     python -m peregrine_b200.profile_case --op gguf --kind q4_0 --m 1 --k 4096 --n 32768
     python -m peregrine_b200.profile_case --op quant --m 8192 --k 4096
     python -m peregrine_b200.profile_case --op llama --layers 2 --m 16 --context 2048 --reps 2
+    python -m peregrine_b200.profile_case --op huffman --k 4096 --n 14336 --streams 4 --reps 3
 
 Inputs are seeded random values generated on the host; weights for `w8a8` are random int8 (no
 quantisation pass), so start-up stays short.  Prints the mean time per call in microseconds
@@ -67,9 +68,52 @@ def llama_case(a) -> None:
         raise SystemExit(1)
 
 
+def huffman_case(a) -> None:
+    """Loads a Huffman-coded [k, n] int8 weight (N(0, 0.02) quantised per column, --sparsity of it zeroed first) with
+    pg_qtensor_from_huffman, beside the plain upload of the decoded bytes (pg_qtensor_from_i8).  Host clock around
+    the whole call: upload from pageable memory, decode, transposition."""
+    from . import quant
+    from .huffman import HuffmanTensor, _stream_tables
+    from .runtime import _ptr
+
+    gpu = GpuContext(0)
+    g = np.random.Generator(np.random.PCG64(1))
+    w = g.standard_normal((a.k, a.n), dtype=np.float32) * np.float32(0.02)
+    if a.sparsity > 0:
+        w[g.random((a.k, a.n)) < a.sparsity] = 0
+    qt = quant.quantize_weights(w, a.k, a.n, gpu)
+    ht = HuffmanTensor.from_quantized(qt, a.streams, limit_lengths=True)
+    packed, sizes, lens = _stream_tables(ht.streams, ht.stream_lengths)
+
+    def timed(fn):
+        best = 1e9
+        for _ in range(a.reps + 1):
+            h = C.c_void_p()
+            t0 = time.perf_counter()
+            _lib.check(fn(h))
+            best = min(best, time.perf_counter() - t0)
+            last = h
+            if _ < a.reps:
+                gpu.lib.pg_qtensor_free(gpu.handle, h)
+        return best * 1e3, last
+
+    ms_h, h = timed(lambda h: gpu.lib.pg_qtensor_from_huffman(gpu.handle, _ptr(ht.table.bit_lengths), len(lens), _ptr(lens), _ptr(sizes),
+                                                              _ptr(packed), _ptr(ht.scales), a.k, a.n, C.byref(h)))
+    back_t, back_s = np.empty((a.n, a.k), np.int8), np.empty(a.n, np.float32)
+    _lib.check(gpu.lib.pg_qtensor_download(gpu.handle, h, None, _ptr(back_t), _ptr(back_s)))
+    same = np.array_equal(back_t, qt.data_i8_t)
+    gpu.lib.pg_qtensor_free(gpu.handle, h)
+    ms_p, h = timed(lambda h: gpu.lib.pg_qtensor_from_i8(gpu.handle, _ptr(qt.data_i8), _ptr(qt.scales), a.k, a.n, C.byref(h)))
+    gpu.lib.pg_qtensor_free(gpu.handle, h)
+    print(f"op=huffman k={a.k} n={a.n} streams={a.streams} sparsity={a.sparsity}: {packed.size} compressed bytes for {a.k * a.n} "
+          f"(ratio {ht.compression_ratio():.3f}), from_huffman {ms_h:.2f} ms, from_i8 {ms_p:.2f} ms, identical={same}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["w8a8", "gguf", "quant", "llama"], default="w8a8")
+    ap.add_argument("--op", choices=["w8a8", "gguf", "quant", "llama", "huffman"], default="w8a8")
+    ap.add_argument("--streams", type=int, default=4, help="huffman: bitstreams per tensor")
+    ap.add_argument("--sparsity", type=float, default=0.0, help="huffman: share of the weights set to zero before quantisation")
     ap.add_argument("--algo", choices=list(ALGOS), default="auto")
     ap.add_argument("--kind", choices=list(TYPE_BY_NAME), default="q4_0")
     ap.add_argument("--m", type=int, default=16)
@@ -85,6 +129,8 @@ def main() -> None:
     a = ap.parse_args()
     if a.op == "llama":
         return llama_case(a)
+    if a.op == "huffman":
+        return huffman_case(a)
 
     gpu = GpuContext(0)
     lib = gpu.lib
