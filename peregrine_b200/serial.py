@@ -1,5 +1,7 @@
 """The quantised serial formats: host-side mirror of `write_quantized_tensor` / `read_quantized_tensor`
-(src/serial.rs:124-222) and of `write_huffman_tensor` / `read_huffman_tensor` (src/serial.rs:315-443).
+(src/serial.rs:124-222), of `write_huffman_tensor` / `read_huffman_tensor` (src/serial.rs:315-443), of
+`save_model` / `load_model` (src/serial.rs:10-86) and of the two converters the reference ships as scripts
+(scripts/convert_weights_int8.py, scripts/convert_huffman.py).
 
     [name_len: u32][name: utf-8][dtype = 1: u8][ndim = 2: u32][rows: u32][cols: u32]
     [data_i8: rows * cols bytes, row-major][scales: cols x f32]                      (all little-endian)
@@ -22,7 +24,7 @@ from __future__ import annotations
 
 import ctypes as C
 import struct
-from typing import BinaryIO, Optional, Tuple
+from typing import BinaryIO, List, Optional, Sequence, Tuple
 
 import numpy as np
 
@@ -57,16 +59,16 @@ def _read_exact(file: BinaryIO, n: int) -> bytes:
     return b
 
 
-def read_quantized_tensor(file: BinaryIO, gpu: Optional[GpuContext] = None) -> Tuple[str, QuantizedTensor]:
-    """src/serial.rs:159-222.  The returned tensor is already on the GPU (`on_gpu`)."""
+def _read_name(file: BinaryIO) -> str:
     (name_len,) = struct.unpack("<I", _read_exact(file, 4))
     try:
-        name = _read_exact(file, name_len).decode("utf-8")
+        return _read_exact(file, name_len).decode("utf-8")
     except UnicodeDecodeError as e:
         raise ValueError(f"invalid utf-8 sequence: {e}") from e
-    dtype = _read_exact(file, 1)[0]
-    if dtype != 1:
-        raise SerialPanic("expected dtype=1 (i8) for quantized tensor")
+
+
+def _read_i8_body(file: BinaryIO, gpu: Optional[GpuContext]) -> QuantizedTensor:
+    """What follows the dtype byte of an i8 record (src/serial.rs:188-222)."""
     (ndim,) = struct.unpack("<I", _read_exact(file, 4))
     if ndim != 2:
         raise SerialPanic("quantized tensors must be 2D")
@@ -83,7 +85,16 @@ def read_quantized_tensor(file: BinaryIO, gpu: Optional[GpuContext] = None) -> T
         keep_q, keep_s = qt.data_i8.copy(), qt.scales.copy()
         qt.from_gpu(gpu)
         assert np.array_equal(qt.data_i8, keep_q) and np.array_equal(qt.scales.view(np.uint32), keep_s.view(np.uint32))
-    return name, qt
+    return qt
+
+
+def read_quantized_tensor(file: BinaryIO, gpu: Optional[GpuContext] = None) -> Tuple[str, QuantizedTensor]:
+    """src/serial.rs:159-222.  The returned tensor is already on the GPU (`on_gpu`)."""
+    name = _read_name(file)
+    dtype = _read_exact(file, 1)[0]
+    if dtype != 1:
+        raise SerialPanic("expected dtype=1 (i8) for quantized tensor")
+    return name, _read_i8_body(file, gpu)
 
 
 def write_huffman_tensor(file: BinaryIO, name: str, ht) -> None:
@@ -105,18 +116,10 @@ def write_huffman_tensor(file: BinaryIO, name: str, ht) -> None:
     file.write(scales.astype("<f4", copy=False).tobytes())
 
 
-def read_huffman_tensor(file: BinaryIO):
-    """src/serial.rs:367-443 -> (name, HuffmanTensor)."""
+def _read_huffman_body(file: BinaryIO):
+    """What follows the dtype byte of a Huffman record (src/serial.rs:385-443)."""
     from .huffman import HuffmanTable, HuffmanTensor
 
-    (name_len,) = struct.unpack("<I", _read_exact(file, 4))
-    try:
-        name = _read_exact(file, name_len).decode("utf-8")
-    except UnicodeDecodeError as e:
-        raise ValueError(f"invalid utf-8 sequence: {e}") from e
-    dtype = _read_exact(file, 1)[0]
-    if dtype != 3:
-        raise SerialPanic("expected dtype=3 (Huffman) for huffman tensor")
     (ndim,) = struct.unpack("<I", _read_exact(file, 4))
     if ndim != 2:
         raise SerialPanic("huffman tensors must be 2D")
@@ -127,5 +130,122 @@ def read_huffman_tensor(file: BinaryIO):
     sizes = struct.unpack(f"<{num_streams}I", _read_exact(file, 4 * num_streams))
     streams = [_read_exact(file, n) for n in sizes]
     scales = np.frombuffer(_read_exact(file, cols * 4), "<f4").astype(np.float32)
-    return name, HuffmanTensor(table, streams, lengths, scales, rows, cols, num_streams)
+    return HuffmanTensor(table, streams, lengths, scales, rows, cols, num_streams)
 
+
+def read_huffman_tensor(file: BinaryIO):
+    """src/serial.rs:367-443 -> (name, HuffmanTensor)."""
+    name = _read_name(file)
+    dtype = _read_exact(file, 1)[0]
+    if dtype != 3:
+        raise SerialPanic("expected dtype=3 (Huffman) for huffman tensor")
+    return name, _read_huffman_body(file)
+
+
+# ---- whole model files ---------------------------------------------------------------------------------------------
+def load_model(path: str) -> List[Tuple[str, List[int], np.ndarray]]:
+    """serial::load_model (src/serial.rs:44-86): [num_tensors: u32] then [name][ndim: u32][shape: u32 each][f32 data] per
+    tensor -> (name, shape, flat f32 data) triples."""
+    out = []
+    with open(path, "rb") as f:
+        (count,) = struct.unpack("<I", _read_exact(f, 4))
+        for _ in range(count):
+            name = _read_name(f)
+            (ndim,) = struct.unpack("<I", _read_exact(f, 4))
+            shape = list(struct.unpack(f"<{ndim}I", _read_exact(f, 4 * ndim)))
+            n = int(np.prod(shape, dtype=np.int64)) if shape else 1
+            out.append((name, shape, np.frombuffer(_read_exact(f, 4 * n), "<f4").astype(np.float32)))
+    return out
+
+
+def save_model(params: Sequence[Tuple[str, Sequence[int], np.ndarray]], path: str) -> None:
+    """serial::save_model (src/serial.rs:10-41) for (name, shape, data) triples."""
+    with open(path, "wb") as f:
+        f.write(struct.pack("<I", len(params)))
+        for name, shape, data in params:
+            nb = name.encode("utf-8")
+            f.write(struct.pack("<I", len(nb)) + nb + struct.pack("<I", len(shape)) + struct.pack(f"<{len(shape)}I", *shape))
+            f.write(np.ascontiguousarray(data, np.float32).astype("<f4", copy=False).tobytes())
+
+
+def load_typed_model(path: str, gpu: Optional[GpuContext] = None) -> List[Tuple[str, object]]:
+    """A file of typed records, as scripts/convert_weights_int8.py:44-81 and scripts/convert_huffman.py:266-300 write them:
+    [num_tensors: u32] then per tensor [name][dtype: u8] and
+        dtype 0   [ndim][shape][f32 data]         -> (shape, flat f32 array)
+        dtype 1   an i8 record                    -> QuantizedTensor, resident on the GPU
+        dtype 3   a Huffman record                -> HuffmanTensor (`to_gpu` decodes it on the device)
+    The 2:4 sparse records (dtype 2, src/serial.rs:226-313) are not read."""
+    out: List[Tuple[str, object]] = []
+    with open(path, "rb") as f:
+        (count,) = struct.unpack("<I", _read_exact(f, 4))
+        for _ in range(count):
+            name = _read_name(f)
+            dtype = _read_exact(f, 1)[0]
+            if dtype == 0:
+                (ndim,) = struct.unpack("<I", _read_exact(f, 4))
+                shape = list(struct.unpack(f"<{ndim}I", _read_exact(f, 4 * ndim)))
+                n = int(np.prod(shape, dtype=np.int64)) if shape else 1
+                out.append((name, (shape, np.frombuffer(_read_exact(f, 4 * n), "<f4").astype(np.float32))))
+            elif dtype == 1:
+                out.append((name, _read_i8_body(f, gpu)))
+            elif dtype == 3:
+                out.append((name, _read_huffman_body(f)))
+            else:
+                raise SerialPanic(f"unsupported dtype {dtype} for tensor '{name}'")
+    return out
+
+
+def convert_weights_int8(input_path: str, output_path: str, gpu: Optional[GpuContext] = None) -> None:
+    """scripts/convert_weights_int8.py: an f32 model file -> a typed file in which every 2-D tensor whose name contains
+    ".weight" is an i8 record and everything else an f32 record.  The quantiser is `quantize_weights` on the GPU
+    (src/quant.rs:27-75: half away from zero; the script's numpy rounding is half to even, so a value that lies
+    exactly on a tie differs by one step, and nothing else does)."""
+    from .quant import quantize_weights
+
+    tensors = load_model(input_path)
+    with open(output_path, "wb") as f:
+        f.write(struct.pack("<I", len(tensors)))
+        for name, shape, data in tensors:
+            if len(shape) == 2 and ".weight" in name:
+                write_quantized_tensor(f, name, quantize_weights(data, shape[0], shape[1], gpu))
+            else:
+                nb = name.encode("utf-8")
+                f.write(struct.pack("<I", len(nb)) + nb + b"\x00" + struct.pack("<I", len(shape)) + struct.pack(f"<{len(shape)}I", *shape))
+                f.write(data.astype("<f4", copy=False).tobytes())
+
+
+def convert_huffman(input_path: str, output_path: str, num_streams: int = 4, limit_lengths: bool = False,
+                    gpu: Optional[GpuContext] = None) -> None:
+    """scripts/convert_huffman.py: a typed file (or a plain f32 model file) -> a file of Huffman records for its 2-D
+    tensors; f32 tensors are quantised first, tensors of other ranks are left out, as the script leaves them out.
+    The code is built by HuffmanTable.from_frequencies (the tie rules of src/huffman.rs, not those of the script's
+    heap): both are optimal prefix codes, the bytes may differ, the decoded tensors do not."""
+    from .huffman import HuffmanTensor
+    from .quant import quantize_weights
+
+    with open(input_path, "rb") as f:
+        head = f.read(16)
+    (count,) = struct.unpack("<I", head[:4])
+    (name_len,) = struct.unpack("<I", head[4:8]) if count else (0,)
+    with open(input_path, "rb") as f:
+        f.seek(8 + name_len)
+        tag = f.read(5)
+    # After the first name a plain f32 file holds the rank as a u32 (bytes r 0 0 0), a typed file the dtype byte and then
+    # the rank (bytes d r 0 0 0): the second byte is zero in the one and the rank in the other.  (The script looks at the
+    # first byte only and so takes the rank of a plain 2-D tensor for a dtype.)
+    typed = count > 0 and len(tag) == 5 and tag[1] != 0
+    records: List[Tuple[str, QuantizedTensor]] = []
+    if typed:
+        for name, item in load_typed_model(input_path, gpu):
+            if isinstance(item, QuantizedTensor):
+                records.append((name, item))
+            elif not isinstance(item, tuple):
+                raise ValueError(f"Unsupported dtype for conversion: tensor '{name}'")
+    else:
+        for name, shape, data in load_model(input_path):
+            if len(shape) == 2:
+                records.append((name, quantize_weights(data, shape[0], shape[1], gpu)))
+    with open(output_path, "wb") as f:
+        f.write(struct.pack("<I", len(records)))
+        for name, qt in records:
+            write_huffman_tensor(f, name, HuffmanTensor.from_quantized(qt, num_streams, limit_lengths))
