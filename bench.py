@@ -468,7 +468,7 @@ def run_ours(args):
             "roofline": roofline,
             "cpu_baseline": cpu,
         }
-        if args.extra:
+        if world == 1 and not args.no_extra:
             line["also"] = extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks)
     # The Llama-3-8B-shape decode stack: on one GPU, or (replicas) one full model and one batch of 16 sequences per GPU
     if not args.no_llama and (world == 1 or replicas):
@@ -504,7 +504,7 @@ def run_ours(args):
 
 
 def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
-    """Secondary figures of the same path: prefill GEMM TOPS and GGUF dequant-product GB/s."""
+    """Secondary figures of the same path: prefill GEMM TOPS, GGUF dequant-product GB/s, Huffman-coded weight load."""
     import peregrine_b200 as pg
     from peregrine_b200 import _lib
 
@@ -538,13 +538,12 @@ def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
                                                   "frac_of_4500_nominal": tops / 4500.0}
             lib.pg_qtensor_free(gpu.handle, h)
             del x, wq, y, q
-    from oracle.pgoracle import Oracle
-
-    orc = Oracle(mt=True)
     n, k = 14336, 4096
-    w = (g.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
     for kind, bs in (("q4_0", 18), ("q8_0", 34)):
-        raw = orc.encode(kind, w)
+        # random quants under one sane f16 scale per block: the product's speed does not depend on the values
+        blocks = g.integers(0, 256, (n * (k // 32), bs), dtype=np.uint8)
+        blocks[:, 0:2] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)
+        raw = blocks.reshape(-1)
         copies = [pg.gguf.GgufWeight(kind, raw, n, k, gpu) for _ in range(6 if kind == "q4_0" else 3)]
         for m in (1, 8):
             with torch.cuda.stream(stream):
@@ -570,7 +569,55 @@ def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
             out[f"gguf_{kind}_M{m}"] = {"us": us, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak}
         for c in copies:
             c.free()
+    out["huffman_load"] = huffman_load_measurement(gpu, g)
     return out
+
+
+def huffman_load_measurement(gpu, g, rows=4096, cols=4096, sparsity=0.5, reps=5):
+    """A Huffman-coded [rows, cols] int8 weight (N(0, 0.02), half of it zeroed, quantised per column) loaded with
+    pg_qtensor_from_huffman (compressed bytes up, parallel decode and transposition on the device) beside the plain load
+    of the decoded bytes (pg_qtensor_from_i8).  Host clock around the blocking calls, pinned host memory, best of `reps`."""
+    import torch
+
+    import peregrine_b200 as pg
+    from peregrine_b200 import _lib
+    from peregrine_b200.huffman import HuffmanTensor, _stream_tables
+    from peregrine_b200.runtime import _ptr
+
+    C = _lib.C
+    w = g.standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+    w[g.random((rows, cols)) < sparsity] = 0
+    qt = pg.quant.quantize_weights(w, rows, cols, gpu)
+    ht = HuffmanTensor.from_quantized(qt, 4, limit_lengths=True)
+    packed, sizes, lens = _stream_tables(ht.streams, ht.stream_lengths)
+    pinned_bits = torch.from_numpy(packed).pin_memory()
+    pinned_q = torch.from_numpy(np.ascontiguousarray(qt.data_i8)).pin_memory()
+
+    def best(fn):
+        t_best, keep = 1e9, None
+        for i in range(reps + 1):
+            h = C.c_void_p()
+            t0 = time.perf_counter()
+            _lib.check(fn(h))
+            dt = time.perf_counter() - t0
+            if i:
+                t_best = min(t_best, dt)
+            if keep is not None:
+                gpu.lib.pg_qtensor_free(gpu.handle, keep)
+            keep = h
+        return t_best * 1e3, keep
+
+    ms_h, h = best(lambda h: gpu.lib.pg_qtensor_from_huffman(gpu.handle, _ptr(ht.table.bit_lengths), len(lens), _ptr(lens), _ptr(sizes),
+                                                             pinned_bits.data_ptr(), _ptr(ht.scales), rows, cols, C.byref(h)))
+    back = np.empty((cols, rows), np.int8)
+    _lib.check(gpu.lib.pg_qtensor_download(gpu.handle, h, None, _ptr(back), None))
+    identical = bool(np.array_equal(back, qt.data_i8_t))
+    gpu.lib.pg_qtensor_free(gpu.handle, h)
+    ms_p, h = best(lambda h: gpu.lib.pg_qtensor_from_i8(gpu.handle, pinned_q.data_ptr(), _ptr(qt.scales), rows, cols, C.byref(h)))
+    gpu.lib.pg_qtensor_free(gpu.handle, h)
+    return {"tensor": f"{rows}x{cols} int8, {int(sparsity * 100)}% zeros, 4 streams", "compressed_bytes": int(packed.size),
+            "ratio": float(ht.compression_ratio()), "from_huffman_ms": ms_h, "from_i8_ms": ms_p, "sweeps": int(gpu.lib.pg_huffman_last_sweeps()),
+            "decoded_gb_s": rows * cols / (ms_h * 1e-3) / 1e9, "identical_to_source": identical, "host_memory": "pinned"}
 
 
 def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmup=8, layers=32):
@@ -649,7 +696,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5000)
     ap.add_argument("--warmup", type=int, default=100)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--extra", action="store_true", help="also time the prefill GEMM and the GGUF products")
+    ap.add_argument("--extra", action="store_true", help="(default at N=1; kept for old command lines)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the prefill GEMM, GGUF product and Huffman load figures")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama-8B-shape decode stack measurement (N = 1 only)")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "shard"],

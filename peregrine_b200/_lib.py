@@ -129,6 +129,8 @@ def load() -> C.CDLL:
     for name in ("pg_tune_stream_ng", "pg_tune_stream_depth", "pg_tune_stream_carveout", "pg_tune_stream_split", "pg_tune_wstream_kw", "pg_tune_wstream_cluster", "pg_tune_tcgen05_bn", "pg_tune_tcgen05_pair", "pg_tune_gguf_simple", "pg_tune_gguf_rows"):
         getattr(lib, name).argtypes = [C.c_int]
         getattr(lib, name).restype = None
+    lib.pg_tune_host_direct.argtypes = [C.c_int, C.c_int]
+    lib.pg_tune_host_direct.restype = None
     _lib = lib
     return lib
 

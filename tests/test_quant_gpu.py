@@ -415,3 +415,36 @@ def test_column_shard_equals_slice_of_full_result(pg, gpu, oracle):
         qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, 512, 96)
         qt.to_gpu(gpu, b, e)
         assert bits_equal(pg.quant.matmul_quantized(x, 16, 512, qt, gpu), full[:, b:e])
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (1, 1024, 320), (4, 4096, 512), (16, 4096, 4096), (16, 14336, 64), (3, 1000, 40)])
+def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n):
+    """pg_matmul_quantized_host lets the kernels address page-locked host buffers themselves where that is faster (x up
+    to 1 MiB, y up to 16 KiB) and copies otherwise: pageable, page-locked, misaligned page-locked and both directions
+    forced on or off all give the oracle's bits."""
+    import torch
+
+    from peregrine_b200 import _lib
+
+    x, w = linear_inputs(m, k, n, 700 + m + n)
+    ref = oracle_mt.quantize_weights(w, k, n)
+    want = oracle_mt.matmul_quantized(x, m, k, ref)
+    qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, k, n)
+    qt.to_gpu(gpu)
+    lib = gpu.lib
+    x_pin = torch.from_numpy(x.reshape(-1)).pin_memory()
+    x_off = torch.empty(m * k + 1).pin_memory()          # a view that starts 4 bytes into a page-locked block
+    x_off[1:].copy_(torch.from_numpy(x.reshape(-1)))
+    y_pin = torch.empty(m * n + 1).pin_memory()
+    try:
+        for x_bytes, y_bytes in ((-1, -1), (0, 0), (1 << 24, 1 << 24)):
+            lib.pg_tune_host_direct(x_bytes, y_bytes)
+            for xp, yp in ((x_pin.data_ptr(), y_pin.data_ptr()), (x_off.data_ptr() + 4, y_pin.data_ptr() + 4),
+                           (x.ctypes.data, y_pin.data_ptr())):
+                y_pin.fill_(float("nan"))
+                _lib.check(lib.pg_matmul_quantized_host(gpu.handle, xp, m, k, qt._gpu, yp))
+                off = 1 if yp != y_pin.data_ptr() else 0
+                assert bits_equal(y_pin.numpy()[off:off + m * n].reshape(m, n), want), (x_bytes, y_bytes)
+    finally:
+        lib.pg_tune_host_direct(-1, -1)
+        qt.free_gpu()
