@@ -131,6 +131,8 @@ def load() -> C.CDLL:
         getattr(lib, name).restype = None
     lib.pg_tune_host_direct.argtypes = [C.c_int, C.c_int]
     lib.pg_tune_host_direct.restype = None
+    lib.pg_tune_host_push.argtypes = [C.c_int]
+    lib.pg_tune_host_push.restype = None
     _lib = lib
     return lib
 

@@ -495,9 +495,13 @@ int32_t pg_qtensor_free(pg_ctx *ctx, pg_qtensor *t)
     PG_ENTER(ctx);
     if (t->owned) {
         PG_CUDA(cudaStreamSynchronize(ctx->stream));
-        cudaFree((void *)t->d_data_i8);
-        cudaFree((void *)t->d_data_i8_t);
-        cudaFree((void *)t->d_scales);
+        if (t->block) {
+            cudaFree(t->block);
+        } else {
+            cudaFree((void *)t->d_data_i8);
+            cudaFree((void *)t->d_data_i8_t);
+            cudaFree((void *)t->d_scales);
+        }
     }
     delete t;
     return PG_OK;
@@ -584,18 +588,22 @@ int32_t pg_matmul_quantized(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k,
 }
 
 // Host buffers the GPU can address (page-locked: cudaHostAlloc, cudaHostRegister) need no copy engine for small
-// payloads.  The quantiser reads x across PCIe itself (128-bit loads, one pass): measured over the nine decode cases of
-// the benchmark that takes 14 % off the blocking call (405 -> 347 us in sum; 87 -> 59 us for 16 x 14336 floats).  The
-// product writes y in 4-byte stores, which cross PCIe as tiny packets: writing y directly only pays up to 16 KiB
-// (30 -> 26 us at 1 x 4096; 46 -> 115 us already at 16 x 4096), so larger results keep the copy engine.
-// 0 switches a direction off, a negative value restores the default.
-constexpr size_t HOST_DIRECT_X = 1 << 20, HOST_DIRECT_Y = 16 << 10;
-static size_t g_host_direct_x = HOST_DIRECT_X, g_host_direct_y = HOST_DIRECT_Y;
+// payloads: a copy engine starts several microseconds after the kernel before it, a kernel does not.
+//   x  the quantiser reads it across PCIe itself (128-bit loads, one pass), up to 1 MiB;
+//   y  the product writes to device memory as always and a copy kernel behind it pushes the result to the host in
+//      16-byte stores, up to 1 MiB.  (Letting the product write y to the host directly is slower beyond a few KiB: its
+//      4-byte stores cross PCIe as tiny packets, 46 -> 115 us already at 16 x 4096 floats; kept behind the knob, off.)
+// Measured over the nine decode cases of the benchmark, blocking call, sum: 382 us with copies both ways, 354 us with
+// x read directly, 329 us with the push kernel as well.  Larger payloads and pageable memory keep the copy engines.
+// pg_tune_host_direct(x_bytes, y_bytes) / pg_tune_host_push(y_bytes): 0 switches a path off, negative restores the default.
+constexpr size_t HOST_DIRECT_X = 1 << 20, HOST_DIRECT_Y = 0, HOST_PUSH_Y = 1 << 20;
+static size_t g_host_direct_x = HOST_DIRECT_X, g_host_direct_y = HOST_DIRECT_Y, g_host_push_y = HOST_PUSH_Y;
 extern "C" PG_API void pg_tune_host_direct(int x_bytes, int y_bytes)
 {
     g_host_direct_x = x_bytes < 0 ? HOST_DIRECT_X : (size_t)x_bytes;
     g_host_direct_y = y_bytes < 0 ? HOST_DIRECT_Y : (size_t)y_bytes;
 }
+extern "C" PG_API void pg_tune_host_push(int y_bytes) { g_host_push_y = y_bytes < 0 ? HOST_PUSH_Y : (size_t)y_bytes; }
 
 // The device's address of a page-locked host buffer, or null for ordinary (pageable) memory.
 static void *device_view_of_host(const void *p)
@@ -628,13 +636,20 @@ int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t
     float *d_s = (float *)(base + nx + ny + nq);
     const size_t bx = (size_t)m * k * 4, by = (size_t)m * n * 4;
     const float *x_dev = (bx && bx <= g_host_direct_x && ((uintptr_t)x & 15) == 0) ? (const float *)device_view_of_host(x) : nullptr;
-    float *y_dev = (by <= g_host_direct_y && ((uintptr_t)y & 15) == 0) ? (float *)device_view_of_host(y) : nullptr;
+    float *y_view = (by <= std::max(g_host_direct_y, g_host_push_y) && ((uintptr_t)y & 15) == 0) ? (float *)device_view_of_host(y) : nullptr;
+    float *y_dev = by <= g_host_direct_y ? y_view : nullptr;
+    const bool push = !y_dev && y_view != nullptr;
     if (bx && !x_dev) PG_CUDA(cudaMemcpyAsync(d_x, x, bx, cudaMemcpyHostToDevice, ctx->stream));
     rc = pgk_quantize_activations(ctx, x_dev ? x_dev : d_x, m, k, d_q, d_s);
     if (rc) return rc;
     rc = gemm_dispatch(ctx, d_q, d_s, m, k, w, y_dev ? y_dev : d_y, nullptr, PG_ALGO_AUTO);
     if (rc) return rc;
-    if (!y_dev) PG_CUDA(cudaMemcpyAsync(y, d_y, by, cudaMemcpyDeviceToHost, ctx->stream));
+    if (push) {
+        rc = pgk_copy_words(ctx, d_y, y_view, by);
+        if (rc) return rc;
+    } else if (!y_dev) {
+        PG_CUDA(cudaMemcpyAsync(y, d_y, by, cudaMemcpyDeviceToHost, ctx->stream));
+    }
     PG_CUDA(cudaStreamSynchronize(ctx->stream));
     return PG_OK;
 }
@@ -814,19 +829,21 @@ int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scal
     t->cols = cols;
     t->owned = true;
     const size_t tb = (size_t)rows * cols;
+    // one allocation: data_i8 | data_i8_t (+ 1 KiB of slack for tiled loads of the last rows) | scales
     void *d_q = nullptr, *d_t = nullptr, *d_s = nullptr;
-    cudaError_t e = cudaMalloc(&d_q, tb + 16);
-    if (e == cudaSuccess) e = cudaMalloc(&d_t, tb + 1024);   // 1 KiB of slack for tiled loads of the last rows
-    if (e == cudaSuccess) e = cudaMalloc(&d_s, (size_t)(cols ? cols : 1) * 4);
+    const size_t o_t = align256(tb + 16), o_s = o_t + align256(tb + 1024);
+    cudaError_t e = cudaMalloc(&d_q, o_s + (size_t)(cols ? cols : 1) * 4);
+    if (e == cudaSuccess) {
+        d_t = (char *)d_q + o_t;
+        d_s = (char *)d_q + o_s;
+    }
     if (e == cudaSuccess && tb) e = cudaMemcpyAsync(d_q, data_i8, tb, cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess && cols) e = cudaMemcpyAsync(d_s, scales, (size_t)cols * 4, cudaMemcpyHostToDevice, ctx->stream);
     int32_t rc = PG_OK;
     if (e == cudaSuccess) rc = pgk_transpose_i8(ctx, (const int8_t *)d_q, rows, cols, (int8_t *)d_t);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // the host arrays may go away after the call
     if (e != cudaSuccess || rc != PG_OK) {
-        cudaFree(d_q);
-        cudaFree(d_t);
-        cudaFree(d_s);
+        cudaFree(d_q);   // the one block
         delete t;
         if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "qtensor_from_i8: %s", cudaGetErrorString(e));
         return rc;
@@ -834,6 +851,7 @@ int32_t pg_qtensor_from_i8(pg_ctx *ctx, const int8_t *data_i8, const float *scal
     t->d_data_i8 = (const int8_t *)d_q;
     t->d_data_i8_t = (const int8_t *)d_t;
     t->d_scales = (const float *)d_s;
+    t->block = d_q;
     *out = t;
     return PG_OK;
 }
@@ -893,19 +911,21 @@ int32_t pg_qtensor_from_huffman(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t
     t->cols = cols;
     t->owned = true;
     const size_t tb = (size_t)rows * cols;
+    // one allocation: data_i8 | data_i8_t (+ 1 KiB of slack for tiled loads of the last rows) | scales
     void *d_q = nullptr, *d_t = nullptr, *d_s = nullptr;
-    cudaError_t e = cudaMalloc(&d_q, tb + 16);
-    if (e == cudaSuccess) e = cudaMalloc(&d_t, tb + 1024);   // 1 KiB of slack for tiled loads of the last rows
-    if (e == cudaSuccess) e = cudaMalloc(&d_s, (size_t)(cols ? cols : 1) * 4);
+    const size_t o_t = align256(tb + 16), o_s = o_t + align256(tb + 1024);
+    cudaError_t e = cudaMalloc(&d_q, o_s + (size_t)(cols ? cols : 1) * 4);
+    if (e == cudaSuccess) {
+        d_t = (char *)d_q + o_t;
+        d_s = (char *)d_q + o_s;
+    }
     if (e == cudaSuccess && cols) e = cudaMemcpyAsync(d_s, scales, (size_t)cols * 4, cudaMemcpyHostToDevice, ctx->stream);
     int32_t rc = PG_OK;
     if (e == cudaSuccess) rc = huffman_decode_to_device(ctx, bit_lengths, num_streams, stream_symbols, stream_bytes, streams, tb, (int8_t *)d_q);
     if (e == cudaSuccess && rc == PG_OK) rc = pgk_transpose_i8(ctx, (const int8_t *)d_q, rows, cols, (int8_t *)d_t);
     if (e == cudaSuccess && rc == PG_OK) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess || rc != PG_OK) {
-        cudaFree(d_q);
-        cudaFree(d_t);
-        cudaFree(d_s);
+        cudaFree(d_q);   // the one block
         delete t;
         if (e != cudaSuccess) PG_FAIL(e == cudaErrorMemoryAllocation ? PG_ERR_NOMEM : PG_ERR_CUDA, "qtensor_from_huffman: %s", cudaGetErrorString(e));
         return rc;
@@ -913,6 +933,7 @@ int32_t pg_qtensor_from_huffman(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t
     t->d_data_i8 = (const int8_t *)d_q;
     t->d_data_i8_t = (const int8_t *)d_t;
     t->d_scales = (const float *)d_s;
+    t->block = d_q;
     *out = t;
     return PG_OK;
 }

@@ -137,6 +137,7 @@ struct pg_qtensor {
     int64_t rows = 0;                     // K
     int64_t cols = 0;                     // N held on this GPU
     bool owned = false;
+    void *block = nullptr;                // where the three arrays are parts of one allocation: that allocation
     // TMA descriptor of data_i8_t for the tcgen05 path, built on first use (128 B, opaque)
     alignas(64) unsigned char tmap_b[128];
     int tmap_b_box_rows = 0;
@@ -165,6 +166,8 @@ int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales);
 int32_t pgk_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int8_t *d_q, int8_t *d_qt, float *d_scales);
 int32_t pgk_transpose_i8(pg_ctx *ctx, const int8_t *d_in, int64_t rows, int64_t cols, int8_t *d_out);
+// device -> device-visible memory by a kernel, 16-byte words (both pointers 16-byte aligned)
+int32_t pgk_copy_words(pg_ctx *ctx, const void *d_src, void *dst, size_t bytes);
 // Huffman streams (back to back in host memory) -> int8 symbols back to back on the device
 int32_t pgk_huffman_decode(pg_ctx *ctx, const uint8_t *bit_lengths, int64_t num_streams, const uint64_t *stream_symbols,
                            const uint64_t *stream_bytes, const uint8_t *h_data, int8_t *d_out);

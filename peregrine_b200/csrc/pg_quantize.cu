@@ -324,3 +324,39 @@ int32_t pgk_matmul_f32(pg_ctx *ctx, const float *d_a, const float *d_b, int64_t 
     PG_LAUNCHED();
     return PG_OK;
 }
+
+// A plain copy of 16-byte words by the SMs (both pointers 16-byte aligned).  Used to push a small result into
+// page-locked host memory: a kernel behind the product in the stream starts sooner than a copy engine does.
+__global__ void __launch_bounds__(256) copy_words_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, size_t words, size_t tail_from,
+                                                         size_t bytes)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride) {
+        const uint4 v = pg_ld_fresh(src + i);
+        dst[i] = v;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < bytes - tail_from)
+        ((unsigned char *)dst)[tail_from + threadIdx.x] = pg_ld_fresh((const unsigned char *)src + tail_from + threadIdx.x);
+}
+
+int32_t pgk_copy_words(pg_ctx *ctx, const void *d_src, void *dst, size_t bytes)
+{
+    if (bytes == 0) return PG_OK;
+    const size_t words = bytes / 16;
+    const unsigned blocks = (unsigned)std::min<size_t>((words + 255) / 256 ? (words + 255) / 256 : 1, 2 * 148);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PG_CUDA(cudaLaunchKernelEx(&cfg, copy_words_kernel, (const uint4 *)d_src, (uint4 *)dst, words, words * 16, bytes));
+    PG_LAUNCHED();
+    return PG_OK;
+}
+

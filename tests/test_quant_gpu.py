@@ -419,9 +419,9 @@ def test_column_shard_equals_slice_of_full_result(pg, gpu, oracle):
 
 @pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (1, 1024, 320), (4, 4096, 512), (16, 4096, 4096), (16, 14336, 64), (3, 1000, 40)])
 def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n):
-    """pg_matmul_quantized_host lets the kernels address page-locked host buffers themselves where that is faster (x up
-    to 1 MiB, y up to 16 KiB) and copies otherwise: pageable, page-locked, misaligned page-locked and both directions
-    forced on or off all give the oracle's bits."""
+    """pg_matmul_quantized_host lets kernels address page-locked host buffers themselves where that is faster (the
+    quantiser reads x, a copy kernel pushes y) and uses the copy engines otherwise: pageable, page-locked, misaligned
+    page-locked buffers and every path forced on or off all give the oracle's bits."""
     import torch
 
     from peregrine_b200 import _lib
@@ -437,8 +437,9 @@ def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n
     x_off[1:].copy_(torch.from_numpy(x.reshape(-1)))
     y_pin = torch.empty(m * n + 1).pin_memory()
     try:
-        for x_bytes, y_bytes in ((-1, -1), (0, 0), (1 << 24, 1 << 24)):
+        for x_bytes, y_bytes, push in ((-1, -1, -1), (0, 0, 0), (1 << 24, 1 << 24, 0), (0, 0, 1 << 24), (1 << 24, 1024, 1 << 24)):
             lib.pg_tune_host_direct(x_bytes, y_bytes)
+            lib.pg_tune_host_push(push)
             for xp, yp in ((x_pin.data_ptr(), y_pin.data_ptr()), (x_off.data_ptr() + 4, y_pin.data_ptr() + 4),
                            (x.ctypes.data, y_pin.data_ptr())):
                 y_pin.fill_(float("nan"))
@@ -447,4 +448,5 @@ def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n
                 assert bits_equal(y_pin.numpy()[off:off + m * n].reshape(m, n), want), (x_bytes, y_bytes)
     finally:
         lib.pg_tune_host_direct(-1, -1)
+        lib.pg_tune_host_push(-1)
         qt.free_gpu()
