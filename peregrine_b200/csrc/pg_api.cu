@@ -536,7 +536,11 @@ static int32_t gemm_dispatch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, 
         case PG_ALGO_AUTO:
             if (aligned && pgk_gemm_i8_wstream_supports(m, k, n))
                 return pgk_gemm_i8_wstream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
-            if (aligned && pgk_gemm_i8_stream_supports(m, k, n))
+            // 17 <= M <= 64: the per-lane FIFO kernel's time grows with M (it is MMA-issue bound there: 25 / 33 / 56 us
+            // at M = 17 / 32 / 64 for K 4096, N 14336), the tcgen05 kernel's does not (23 us for any M <= 128), but it
+            // needs enough 64-column tiles to occupy the SMs (35 us at N = 4096, K = 14336, against 31 us at M <= 32).
+            if (aligned && pgk_gemm_i8_stream_supports(m, k, n) &&
+                !(pgk_gemm_i8_tcgen05_supports(m, k, n) && m > 16 && (m > 32 || n >= 40ll * ctx->sm_count)))
                 return pgk_gemm_i8_stream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
             if (aligned && pgk_gemm_i8_tcgen05_supports(m, k, n))
                 return pgk_gemm_i8_tcgen05(ctx, d_a, d_as, m, k, const_cast<pg_qtensor *>(w), d_y, d_acc);
