@@ -181,7 +181,9 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "w8a8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        # the host's throughput does not depend on how many sweeps it is given: the label follows the GPU arm's layout
+        "scaling": "weak" if (args.gpus > 1 and args.parallel == "replicas") else "strong", "vs_baseline": None, "dtype": "i8",
+        "data": "synthetic",
         "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": orc.threads, "kind": "port",
                          "sample": sample + "; OpenMP over independent outputs (the reference itself runs this path on one thread)"},
