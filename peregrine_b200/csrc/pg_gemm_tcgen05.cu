@@ -446,8 +446,16 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     int bn = 64;
     if (tiles_m * ((n + 127) / 128) >= ctx->sm_count) bn = 128;
     if (tiles_m * ((n + 255) / 256) >= ctx->sm_count) bn = 256;
+    // Narrow layers at small M (one row of tiles): 32-column tiles where they shorten the longest SM's share of the
+    // columns, e.g. N = 4096: 128 tiles of 32 instead of 64 tiles of 64 on 148 SMs.
+    if (bn == 64) {
+        const int64_t waves64 = (tiles_m * ((n + 63) / 64) + ctx->sm_count - 1) / ctx->sm_count;
+        const int64_t waves32 = (tiles_m * ((n + 31) / 32) + ctx->sm_count - 1) / ctx->sm_count;
+        if (waves32 * 32 < waves64 * 64) bn = 32;
+    }
     if (g_force_bn) bn = g_force_bn;
     if (bn == 256) return launch<256>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
     if (bn == 128) return launch<128>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
+    if (bn == 32) return launch<32>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
     return launch<64>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
 }

@@ -267,7 +267,7 @@ def test_tcgen05_kernel_ragged_shapes(pg, gpu, oracle_mt, m, k, n):
     _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive", "tcgen05"])
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
 def test_tcgen05_every_tile_width(pg, gpu, oracle_mt, bn):
     x, w = linear_inputs(384, 1024, 1280, 500 + bn)
     gpu.lib.pg_tune_tcgen05_bn(bn)
