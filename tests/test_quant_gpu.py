@@ -446,6 +446,13 @@ def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n
                 _lib.check(lib.pg_matmul_quantized_host(gpu.handle, xp, m, k, qt._gpu, yp))
                 off = 1 if yp != y_pin.data_ptr() else 0
                 assert bits_equal(y_pin.numpy()[off:off + m * n].reshape(m, n), want), (x_bytes, y_bytes)
+        # new contents in the same page-locked buffer are what the next call computes with: -x gives exactly -y
+        lib.pg_tune_host_direct(-1, -1)
+        lib.pg_tune_host_push(-1)
+        for sign in (-1.0, 1.0, -1.0):
+            x_pin.copy_(torch.from_numpy(x.reshape(-1)) * sign)
+            _lib.check(lib.pg_matmul_quantized_host(gpu.handle, x_pin.data_ptr(), m, k, qt._gpu, y_pin.data_ptr()))
+            assert np.array_equal(y_pin.numpy()[:m * n].reshape(m, n), want * np.float32(sign))
     finally:
         lib.pg_tune_host_direct(-1, -1)
         lib.pg_tune_host_push(-1)
