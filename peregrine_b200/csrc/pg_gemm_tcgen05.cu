@@ -439,19 +439,30 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     // CTA pairs (256 x 256 tiles) as soon as those tiles can occupy half of the SM pairs: measured
     // faster than one CTA per tile from M = 512 upwards (2896 vs 2658 TOPS at M 8192, N 14336)
     const int64_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && !g_force_bn && pair_tiles >= ctx->sm_count / 4);
+    // (not for a single row of tiles: at M <= 128 the ring's latency decides, see below: 23.0 us for pairs against
+    // 18.5 us for one CTA per 128-column tile at M 64, N 14336)
+    const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && !g_force_bn && m > BM && pair_tiles >= ctx->sm_count / 4);
     if (pair) return pgk_gemm_i8_tcgen05_2cta(ctx, d_a, d_as, m, k, w, d_y, d_acc);
     // Largest N tile that still gives every SM a tile.
     const int64_t tiles_m = (m + BM - 1) / BM;
     int bn = 64;
     if (tiles_m * ((n + 127) / 128) >= ctx->sm_count) bn = 128;
     if (tiles_m * ((n + 255) / 256) >= ctx->sm_count) bn = 256;
-    // Narrow layers at small M (one row of tiles): 32-column tiles where they shorten the longest SM's share of the
-    // columns, e.g. N = 4096: 128 tiles of 32 instead of 64 tiles of 64 on 148 SMs.
-    if (bn == 64) {
-        const int64_t waves64 = (tiles_m * ((n + 63) / 64) + ctx->sm_count - 1) / ctx->sm_count;
-        const int64_t waves32 = (tiles_m * ((n + 31) / 32) + ctx->sm_count - 1) / ctx->sm_count;
-        if (waves32 * 32 < waves64 * 64) bn = 32;
+    // One row of tiles (M <= 128): the kernel is then bound by the latency of its shared-memory ring, not by the MMAs.
+    // Measured at M = 64 a k-block of 128 bytes per column takes a CTA about 230 ns + 1.8 ns per column of the tile
+    // (280 / 325 / 480 / 680 ns at 32 / 64 / 128 / 256 columns), whatever K and N are: take the tile width with the
+    // smallest waves x time-per-k-block (N 14336: one wave of 128-column tiles, 18.5 us, against 23.8 us for two waves
+    // of 64-column tiles; N 4096: 32-column tiles; N 6144: 64-column tiles).
+    if (tiles_m == 1) {
+        double best = 0.0;
+        for (int cand = 32; cand <= 256; cand *= 2) {
+            const int64_t waves = ((n + cand - 1) / cand + ctx->sm_count - 1) / ctx->sm_count;
+            const double cost = (double)waves * (230.0 + 1.8 * cand);
+            if (best == 0.0 || cost < best) {
+                best = cost;
+                bn = cand;
+            }
+        }
     }
     if (g_force_bn) bn = g_force_bn;
     if (bn == 256) return launch<256>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
