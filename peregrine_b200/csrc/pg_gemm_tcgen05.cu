@@ -166,23 +166,35 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n)
     return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <int BN>
+// AR: rows of A one copy brings (32 or 64 where M is that small, else 128).  The MMA always reads a 128-row A tile; with
+// AR < 128 the rows behind the copied ones are whatever follows in shared memory (the stage's B tile, the next stage):
+// they only feed accumulator rows >= M, which the epilogue never stores.  What the smaller A tile buys is a deeper ring
+// in the same shared memory, and the ring's depth is what bounds this kernel at small M.
+__host__ __device__ constexpr int ring_stages(int bn, int ar)
+{
+    const int stage = ar * BK + bn * BK;
+    const int room = 232448 - (1024 + 256 + 4 * PG_EPI_WARP_BYTES);
+    const int fit = room / stage;
+    return fit > 12 ? 12 : fit;   // the barrier block holds 2 * 12 + 4 barriers
+}
+
+template <int BN, int AR>
 struct Cfg {
-    static constexpr int STAGE_A = BM * BK;
+    static constexpr int STAGE_A = AR * BK;
     static constexpr int STAGE_B = BN * BK;
     static constexpr int STAGE = STAGE_A + STAGE_B;
-    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int STAGES = ring_stages(BN, AR);
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two >= 32
     static constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * PG_EPI_WARP_BYTES;
 };
 
-template <int BN>
+template <int BN, int AR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                            const float *__restrict__ a_scales, const float *__restrict__ w_scales, int M, int N, int K,
                            float *__restrict__ y, int32_t *__restrict__ acc_out, int32_t *status)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, AR>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -393,20 +405,20 @@ int32_t encode_kmajor(CUtensorMap *map, const void *ptr, int64_t rows, int64_t k
     return PG_OK;
 }
 
-template <int BN>
+template <int BN, int AR>
 int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, pg_qtensor *w, float *d_y, int32_t *d_acc)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, AR>;
     const int N = (int)w->cols;
     CUtensorMap ta;
-    int32_t rc = encode_kmajor(&ta, d_a, M, K, BM);
+    int32_t rc = encode_kmajor(&ta, d_a, M, K, AR);
     if (rc) return rc;
     if (w->tmap_b_box_rows != BN) {
         rc = encode_kmajor(reinterpret_cast<CUtensorMap *>(w->tmap_b), w->d_data_i8_t, N, K, BN);
         if (rc) return rc;
         w->tmap_b_box_rows = BN;
     }
-    auto kern = gemm_i8_tcgen05_kernel<BN>;
+    auto kern = gemm_i8_tcgen05_kernel<BN, AR>;
     PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
@@ -448,16 +460,18 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     int bn = 64;
     if (tiles_m * ((n + 127) / 128) >= ctx->sm_count) bn = 128;
     if (tiles_m * ((n + 255) / 256) >= ctx->sm_count) bn = 256;
-    // One row of tiles (M <= 128): the kernel is then bound by the latency of its shared-memory ring, not by the MMAs.
-    // Measured at M = 64 a k-block of 128 bytes per column takes a CTA about 230 ns + 1.8 ns per column of the tile
-    // (280 / 325 / 480 / 680 ns at 32 / 64 / 128 / 256 columns), whatever K and N are: take the tile width with the
-    // smallest waves x time-per-k-block (N 14336: one wave of 128-column tiles, 18.5 us, against 23.8 us for two waves
-    // of 64-column tiles; N 4096: 32-column tiles; N 6144: 64-column tiles).
+    // One row of tiles (M <= 128): the MMAs are not what bounds the kernel then.  Measured at M = 64, a k-block (128
+    // bytes per column) takes a CTA 280 / 325 / 480 / 680 ns at 32 / 64 / 128 / 256 columns, whatever K and N are:
+    // about 1.8 ns x (128 + columns).  Take the tile width with the smallest waves x time-per-k-block (N 14336: one
+    // wave of 128-column tiles, 18.5 us, against 23.8 us for two waves of 64-column tiles; N 4096: 32-column tiles;
+    // N 6144: 64-column tiles), and the smallest A tile that holds M rows (a deeper ring: 102 -> 92 us at N 128256,
+    // 22.7 -> 18.6 us at M 17, N 14336; no change at M 64, N 14336).
+    const int ar = m <= 32 ? 32 : (m <= 64 ? 64 : BM);
     if (tiles_m == 1) {
         double best = 0.0;
         for (int cand = 32; cand <= 256; cand *= 2) {
             const int64_t waves = ((n + cand - 1) / cand + ctx->sm_count - 1) / ctx->sm_count;
-            const double cost = (double)waves * (230.0 + 1.8 * cand);
+            const double cost = (double)waves * 1.8 * (128 + cand);
             if (best == 0.0 || cost < best) {
                 best = cost;
                 bn = cand;
@@ -465,8 +479,17 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
         }
     }
     if (g_force_bn) bn = g_force_bn;
-    if (bn == 256) return launch<256>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
-    if (bn == 128) return launch<128>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
-    if (bn == 32) return launch<32>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
-    return launch<64>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc);
+#define PG_TC_LAUNCH(BN_, AR_) return launch<BN_, AR_>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc)
+#define PG_TC_ROWS(BN_)                \
+    do {                               \
+        if (ar == 32) PG_TC_LAUNCH(BN_, 32); \
+        if (ar == 64) PG_TC_LAUNCH(BN_, 64); \
+        PG_TC_LAUNCH(BN_, 128);        \
+    } while (0)
+    if (bn == 256) PG_TC_ROWS(256);
+    if (bn == 128) PG_TC_ROWS(128);
+    if (bn == 32) PG_TC_ROWS(32);
+    PG_TC_ROWS(64);
+#undef PG_TC_ROWS
+#undef PG_TC_LAUNCH
 }
