@@ -6,6 +6,7 @@
     python -m peregrine_b200.profile_case --op quant --m 8192 --k 4096
     python -m peregrine_b200.profile_case --op llama --layers 2 --m 16 --context 2048 --reps 2
     python -m peregrine_b200.profile_case --op huffman --k 4096 --n 14336 --streams 4 --reps 3
+    python -m peregrine_b200.profile_case --op host --reps 1500
 
 Inputs are seeded random values generated on the host; weights for `w8a8` are random int8 (no
 quantisation pass), so start-up stays short.  Prints the mean time per call in microseconds
@@ -109,9 +110,51 @@ def huffman_case(a) -> None:
           f"(ratio {ht.compression_ratio():.3f}), from_huffman {ms_h:.2f} ms, from_i8 {ms_p:.2f} ms, identical={same}")
 
 
+def host_case(a) -> None:
+    """pg_matmul_quantized_host (host x in, host y out, blocking) over the nine decode cases of the benchmark, with
+    page-locked buffers and each way of moving x and y: copy engines only, x read by the quantiser, y pushed by a copy
+    kernel, y written by the product itself.  Microseconds per call, host clock."""
+    import torch
+
+    gpu = GpuContext(0)
+    lib = gpu.lib
+    g = np.random.Generator(np.random.PCG64(1))
+    modes = [("copies", (0, 0, 0)), ("x direct", (1 << 20, 0, 0)), ("x direct + y pushed (default)", (-1, -1, -1)),
+             ("x direct + y written by the product", (1 << 20, 1 << 20, 0))]
+    total = {name: 0.0 for name, _ in modes}
+    for k, n in ((4096, 4096), (4096, 14336), (14336, 4096)):
+        wt = g.integers(-127, 128, n * k, dtype=np.int8)
+        d_w = gpu.alloc(n * k + 1024, np.int8)
+        _lib.check(lib.pg_mem_upload(gpu.handle, d_w.ptr, wt.ctypes.data, n * k))
+        gpu.sync()
+        d_ws = gpu.upload(np.full(n, 1e-3, np.float32))
+        h = C.c_void_p()
+        _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, d_w.ptr, d_ws.ptr, k, n, C.byref(h)))
+        for m in (1, 4, 16):
+            x = torch.randn(m, k).pin_memory()
+            y = torch.empty(m, n).pin_memory()
+            line = []
+            for name, (bx, by, bp) in modes:
+                lib.pg_tune_host_direct(bx, by)
+                lib.pg_tune_host_push(bp)
+                for _ in range(300):
+                    lib.pg_matmul_quantized_host(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr())
+                t0 = time.perf_counter()
+                for _ in range(a.reps):
+                    _lib.check(lib.pg_matmul_quantized_host(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr()))
+                us = (time.perf_counter() - t0) / a.reps * 1e6
+                total[name] += us
+                line.append(f"{name} {us:.1f}")
+            print(f"op=host m={m} k={k} n={n}: " + " | ".join(line), flush=True)
+        lib.pg_qtensor_free(gpu.handle, h)
+    lib.pg_tune_host_direct(-1, -1)
+    lib.pg_tune_host_push(-1)
+    print("sum over the nine cases, us: " + " | ".join(f"{k} {v:.1f}" for k, v in total.items()))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["w8a8", "gguf", "quant", "llama", "huffman"], default="w8a8")
+    ap.add_argument("--op", choices=["w8a8", "gguf", "quant", "llama", "huffman", "host"], default="w8a8")
     ap.add_argument("--streams", type=int, default=4, help="huffman: bitstreams per tensor")
     ap.add_argument("--sparsity", type=float, default=0.0, help="huffman: share of the weights set to zero before quantisation")
     ap.add_argument("--algo", choices=list(ALGOS), default="auto")
@@ -131,6 +174,8 @@ def main() -> None:
         return llama_case(a)
     if a.op == "huffman":
         return huffman_case(a)
+    if a.op == "host":
+        return host_case(a)
 
     gpu = GpuContext(0)
     lib = gpu.lib
