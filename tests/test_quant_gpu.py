@@ -277,6 +277,27 @@ def test_tcgen05_every_tile_width(pg, gpu, oracle_mt, bn):
         gpu.lib.pg_tune_tcgen05_bn(0)
 
 
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+@pytest.mark.parametrize("m", [1, 17, 32, 33, 64, 65, 128])
+def test_tcgen05_small_row_counts(pg, gpu, oracle_mt, m, bn):
+    """One row of tiles: the A tile is copied with 32, 64 or 128 rows (the MMA reads 128 either way; what lies behind the
+    copied rows must not reach the output), every tile width, ragged K and N, and K shorter than the ring."""
+    gpu.lib.pg_tune_tcgen05_bn(bn)
+    try:
+        for k, n in ((1040, 520), (144, 257), (4096, 96)):
+            x, w = linear_inputs(m, k, n, 900 + m + bn + n)
+            _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["tcgen05"])
+    finally:
+        gpu.lib.pg_tune_tcgen05_bn(0)
+
+
+@pytest.mark.parametrize("m,k,n", [(17, 4096, 14336), (48, 4096, 6144), (64, 14336, 4096), (100, 4096, 4096), (24, 1040, 12000)])
+def test_mid_batch_dispatch(pg, gpu, oracle_mt, m, k, n):
+    """17 <= M <= 128 with the automatic kernel choice (tcgen05 with the modelled tile width, or the FIFO kernel)."""
+    x, w = linear_inputs(m, k, n, 40 + m)
+    _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive"])
+
+
 @pytest.mark.parametrize("m,k,n", [(256, 128, 256), (512, 1024, 768), (300, 1040, 520), (1000, 4096, 1000), (129, 144, 257)])
 def test_tcgen05_cta_pairs(pg, gpu, oracle_mt, m, k, n):
     """cta_group::2: two CTAs share one 256 x 256 tile; full and ragged tiles in M, N and K."""
