@@ -160,3 +160,34 @@ def test_symbol_count_is_checked(pg, gpu):
     rc = gpu.lib.pg_qtensor_from_huffman(gpu.handle, ht.table.bit_lengths.ctypes.data, 2, lens.ctypes.data, sizes.ctypes.data,
                                          packed.ctypes.data, ht.scales.ctypes.data, 4, 4, C.byref(h))
     assert rc == _lib.PG_ERR_INVALID and not h.value
+
+
+def test_random_tensors_and_damaged_streams(pg, gpu, oracle):
+    """80 seeded random tensors (five symbol distributions, 1 to 300 streams): the decode gives the source back, and a
+    damaged, shortened copy of the first stream decodes to what the oracle's sequential loop makes of it."""
+    g = rng(77)
+    for _ in range(80):
+        rows, cols = int(g.choice([1, 3, 16, 100, 333, 1024])), int(g.choice([1, 5, 32, 77, 256, 1000]))
+        kind = int(g.integers(0, 5))
+        if kind == 0:
+            q = (g.standard_normal((rows, cols)) * g.choice([0.5, 3, 12, 40])).clip(-127, 127).astype(np.int8)
+        elif kind == 1:
+            q = g.integers(-128, 128, (rows, cols)).astype(np.int8)
+        elif kind == 2:
+            q = g.integers(0, int(g.choice([1, 2, 3, 5, 17])), (rows, cols)).astype(np.int8)
+        elif kind == 3:
+            q = np.where(g.random((rows, cols)) < 0.95, 7, g.integers(-128, 128, (rows, cols))).astype(np.int8)
+        else:
+            q = (g.geometric(0.3, (rows, cols)) % 120).astype(np.int8)
+        qt = pg.quant.QuantizedTensor(q, np.ascontiguousarray(q.T), g.random(cols, dtype=np.float32), rows, cols)
+        ht = pg.huffman.HuffmanTensor.from_quantized(qt, int(g.choice([1, 2, 4, 7, 64, 300])), limit_lengths=True)
+        back = ht.decode_to_quantized(gpu)
+        assert np.array_equal(back.data_i8, q) and np.array_equal(back.data_i8_t, q.T), (rows, cols, kind)
+        back.free_gpu()
+        if len(ht.streams[0]) > 4:
+            bad = bytearray(ht.streams[0])
+            for _ in range(3):
+                bad[int(g.integers(0, len(bad)))] ^= int(g.integers(1, 256))
+            bad = bytes(bad[:max(1, len(bad) - int(g.integers(0, 3)))])
+            n0 = ht.stream_lengths[0]
+            assert np.array_equal(ht.table.decode(bad, n0, gpu), oracle_decode(oracle, ht.table, bad, n0)), (rows, cols, kind)

@@ -478,3 +478,42 @@ def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n
         lib.pg_tune_host_direct(-1, -1)
         lib.pg_tune_host_push(-1)
         qt.free_gpu()
+
+
+def test_random_shapes_every_kernel_agrees(pg, gpu):
+    """150 seeded random (M, K, N) around every switch point of the automatic kernel choice: the chosen kernel, the
+    one-thread-per-output checker and the blocking host call give the same accumulators and the same f32 bits."""
+    import ctypes as C
+
+    from peregrine_b200 import _lib
+
+    lib = gpu.lib
+    g = rng(2024)
+    ms = [1, 2, 3, 4, 7, 8, 15, 16, 17, 24, 31, 32, 33, 48, 63, 64, 65, 100, 127, 128, 129, 200, 300]
+    ks = [16, 32, 48, 64, 128, 144, 256, 512, 992, 1040, 2048, 4096, 4112]
+    ns = [1, 7, 8, 16, 31, 40, 64, 96, 127, 128, 257, 520, 1000, 2048, 4100, 6144]
+    for _ in range(150):
+        m, k, n = int(g.choice(ms)), int(g.choice(ks)), int(g.choice(ns))
+        wt = g.integers(-127, 128, (n, k), dtype=np.int8)
+        ws = (g.random(n, dtype=np.float32) * np.float32(1e-2) + np.float32(1e-4)).astype(np.float32)
+        x = normal(g, (m, k))
+        d_w = gpu.alloc(n * k + 1024, np.int8)
+        _lib.check(lib.pg_mem_upload(gpu.handle, d_w.ptr, wt.ctypes.data, n * k))
+        gpu.sync()
+        d_ws, d_x = gpu.upload(ws), gpu.upload(x.reshape(-1))
+        h = C.c_void_p()
+        _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, d_w.ptr, d_ws.ptr, k, n, C.byref(h)))
+        d_q, d_s = gpu.alloc(m * k + 16, np.int8), gpu.alloc(m, np.float32)
+        _lib.check(lib.pg_quantize_activations(gpu.handle, d_x.ptr, m, k, d_q.ptr, d_s.ptr))
+        outs = []
+        for algo in (_lib.ALGO_NAIVE, _lib.ALGO_AUTO):
+            d_y, d_a = gpu.alloc(m * n, np.float32), gpu.alloc(m * n, np.int32)
+            _lib.check(lib.pg_gemm_i8(gpu.handle, d_q.ptr, d_s.ptr, m, k, h, d_y.ptr, d_a.ptr, algo))
+            gpu.sync()
+            outs.append((d_y.read(), d_a.read()))
+        y_host = np.empty((m, n), np.float32)
+        _lib.check(lib.pg_matmul_quantized_host(gpu.handle, x.ctypes.data, m, k, h, y_host.ctypes.data))
+        assert np.array_equal(outs[0][1], outs[1][1]), (m, k, n)
+        assert bits_equal(outs[0][0], outs[1][0]) and bits_equal(y_host.reshape(-1), outs[0][0]), (m, k, n)
+        assert gpu.device_status() == 0
+        lib.pg_qtensor_free(gpu.handle, h)
