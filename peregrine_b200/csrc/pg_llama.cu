@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
     constexpr int HD = 128;
     extern __shared__ float sm[];  // sc[chunk][G], then red[8][G][HD]
     float *sc = sm;
-    float *red = sm + (size_t)chunk * G;
+    float *red = sm + (((size_t)chunk * G + 3) & ~(size_t)3);   // written as float4: starts on a 16-byte boundary
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int split = blockIdx.x, S = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -588,7 +588,7 @@ static int32_t attention_decode(pg_ctx *ctx, const float *d_q_rot, float *d_kcac
     } else {
         PG_REQUIRE(d_cos == nullptr, "gqa_attention_decode_fused: %lld query heads per KV head is not supported (4, 8)", (long long)G);
         const int chunk = (int)((cap + S - 1) / S);
-        const size_t smem = ((size_t)chunk * G + 8 * G * 128) * sizeof(float);
+        const size_t smem = ((((size_t)chunk * G + 3) & ~(size_t)3) + 8 * G * 128) * sizeof(float);
         const dim3 grid((unsigned)S, (unsigned)Hkv, (unsigned)B);
 #define PG_ATT(GG)                                                                                                              \
     {                                                                                                                           \

@@ -117,7 +117,9 @@ def test_rope_append_attention_embedding_argmax(pg, gpu, oracle):
     # 4 and 8 query heads per KV head take the streaming kernel, 1 and 2 the chunked one; first position, ragged slices,
     # more (sequence, head, slice) units than the GPU has warps
     for B, Hq, Hkv, cap, pos in ((3, 8, 2, 300, 7), (3, 8, 2, 1100, 1099), (3, 8, 2, 2200, 2047), (2, 16, 2, 700, 0), (2, 16, 2, 700, 650),
-                                 (1, 4, 2, 600, 333), (2, 2, 2, 300, 299), (40, 32, 8, 200, 130), (16, 32, 8, 2176, 2048)):
+                                 (1, 4, 2, 600, 333), (2, 2, 2, 300, 299), (40, 32, 8, 200, 130), (16, 32, 8, 2176, 2048),
+                                 # capacities whose slices are not multiples of four positions (chunked kernel: 513 per slice)
+                                 (2, 2, 1, 4100, 0), (2, 2, 2, 4100, 901), (3, 2, 1, 2178, 2158), (1, 8, 8, 66, 10), (5, 8, 1, 301, 86)):
         cos, sin = rope_tables(hd, cap, 500000.0)
         qkv = normal(g, (B, (Hq + 2 * Hkv) * hd))
         K = normal(g, (B, Hkv, cap, hd))
