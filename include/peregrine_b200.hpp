@@ -259,4 +259,61 @@ private:
 };
 
 }  // namespace gguf
+
+namespace huffman {
+
+using metal::GpuContext;
+
+// src/huffman.rs:311-325, decoding side: the code book as HuffmanTable::to_bytes gives it (256 bit lengths), the
+// bitstreams, the symbols per stream, the per-column scales.  (Building a code and encoding stay with the caller.)
+struct HuffmanTensor {
+    std::vector<uint8_t> bit_lengths;            // 256
+    std::vector<std::vector<uint8_t>> streams;
+    std::vector<size_t> stream_lengths;
+    std::vector<float> scales;
+    size_t rows = 0, cols = 0;
+
+    // src/huffman.rs:430-437, with the decode on the device: the resident tensor
+    quant::QuantizedTensor to_gpu(const GpuContext &g) const
+    {
+        if (bit_lengths.size() < 256) throw Panic(PG_ERR_INVALID, "codebook too short");
+        if (streams.size() != stream_lengths.size()) throw Panic(PG_ERR_INVALID, "one length per stream");
+        std::vector<uint8_t> packed;
+        std::vector<uint64_t> sizes, lens;
+        for (size_t i = 0; i < streams.size(); i++) {
+            packed.insert(packed.end(), streams[i].begin(), streams[i].end());
+            sizes.push_back(streams[i].size());
+            lens.push_back(stream_lengths[i]);
+        }
+        pg_qtensor *h = nullptr;
+        check(pg_qtensor_from_huffman(g.raw(), bit_lengths.data(), (int64_t)streams.size(), lens.data(), sizes.data(),
+                                      packed.empty() ? nullptr : packed.data(), scales.data(), (int64_t)rows, (int64_t)cols, &h));
+        quant::QuantizedTensor qt;
+        qt.rows = rows;
+        qt.cols = cols;
+        qt.scales = scales;
+        pg_ctx *ctx = g.raw();
+        qt.gpu = std::shared_ptr<pg_qtensor>(h, [ctx](pg_qtensor *p) { pg_qtensor_free(ctx, p); });
+        return qt;
+    }
+    // src/huffman.rs:374-404: all host fields filled in
+    quant::QuantizedTensor decode_to_quantized(const GpuContext &g) const
+    {
+        quant::QuantizedTensor qt = to_gpu(g);
+        qt.data_i8.resize(rows * cols);
+        qt.data_i8_t.resize(rows * cols);
+        if (rows * cols) qt.from_gpu(g);
+        return qt;
+    }
+};
+
+// src/huffman.rs:465-476
+inline std::vector<float> matmul_huffman(const GpuContext &g, const std::vector<float> &a_data, size_t m, size_t k, const HuffmanTensor &ht)
+{
+    if (ht.rows != k) throw Panic(PG_ERR_INVALID, "matmul_huffman: ht.rows != k");
+    quant::QuantizedTensor qt = ht.to_gpu(g);
+    return quant::matmul_quantized(g, a_data, m, k, qt);
+}
+
+}  // namespace huffman
 }  // namespace peregrine

@@ -146,6 +146,30 @@ int main()
         }
         EXPECT(threw, "w.rows != k must be rejected");
     }
+    {   // Huffman-coded weights (src/huffman.rs): bit lengths 3, 3, 2, 1 for the values -118, -108, -98, -88 give the canonical
+        // codes 110, 111, 10, 0; the 2 x 2 matrix [-88, -98; -118, -108] is the stream 0 10 110 111 = 0x5B 0x80
+        huffman::HuffmanTensor ht;
+        ht.bit_lengths.assign(256, 0);
+        ht.bit_lengths[10] = 3; ht.bit_lengths[20] = 3; ht.bit_lengths[30] = 2; ht.bit_lengths[40] = 1;
+        ht.streams = {{0x5B, 0x80}};
+        ht.stream_lengths = {4};
+        ht.scales = {0.5f, 0.25f};
+        ht.rows = 2; ht.cols = 2;
+        auto qt = ht.decode_to_quantized(g);
+        const int8_t want[4] = {-88, -98, -118, -108}, want_t[4] = {-88, -118, -98, -108};
+        for (int i = 0; i < 4; i++) EXPECT(qt.data_i8[i] == want[i] && qt.data_i8_t[i] == want_t[i], "huffman decode idx %d", i);
+        // y = x . (q * scale): x = [1, 0] picks the first row
+        auto y = huffman::matmul_huffman(g, {1.0f, 0.0f}, 1, 2, ht);
+        EXPECT(std::fabs(y[0] - (-88.0f * 0.5f)) < 0.5f && std::fabs(y[1] - (-98.0f * 0.25f)) < 0.25f, "matmul_huffman: %g %g", y[0], y[1]);
+        bool threw = false;
+        ht.stream_lengths = {3};
+        try {
+            ht.to_gpu(g);
+        } catch (const Panic &) {
+            threw = true;
+        }
+        EXPECT(threw, "streams that do not hold rows * cols symbols must be rejected");
+    }
     std::printf(failures ? "%d FAILURES\n" : "all reference tests passed\n", failures);
     return failures ? 1 : 0;
 }
