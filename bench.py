@@ -12,12 +12,13 @@ Metric: achieved HBM bandwidth in GB/s = algorithmic bytes of the sweep / time, 
     python bench.py --gpus N --steps K --warmup W            this library
     python bench.py --impl reference ...                     the reference's CPU algorithm (C port)
 
-With N > 1 (one process per GPU, torchrun) every rank holds a full replica of the weights and runs its
-own sweep, with no data-path collective: the rows of a decode batch are independent sequences and
-the matrices fit one GPU many times over, so this is how the path scales out (`scaling: weak`;
-`value` is all ranks' bytes over the slowest rank's time).  `--parallel shard` runs the other layout:
-weights sharded by output column over the ranks, one sweep, output slices all-gathered (by peer stores
-over NVLink, or `--collective nccl`), reported as strong scaling.
+With N > 1 (one process per GPU, torchrun) the weights are sharded by output column over the ranks: one
+sweep, every rank quantises the (replicated) activations and computes its columns, and the products' own
+epilogues store the slices into every rank's result buffer over NVLink (`--collective nccl`: eager NCCL
+all-gathers instead); `scaling: strong`, `value` is the sweep's bytes over the slowest rank's time.  The
+same line carries the column-sharded Llama-3-8B-shape decode stack (`also.llama8b_int8_decode`).
+`--parallel replicas` runs the other layout, labelled as what it is: a full copy of the weights and an
+own sweep per GPU, no collective (`scaling: weak`).
 
 Cache discipline: every case of a step reads its own copy of the weights (three copies per shape,
 402 MB in total), so a weight matrix is re-read only after ~400 MB of other traffic (L2 is 126 MB).
@@ -64,6 +65,9 @@ def make_inputs(case_idx, m, k):
     ch = g.choice(k, size=int(np.ceil(0.01 * k)), replace=False)
     x[:, ch] *= np.float32(20.0)
     return x
+
+
+WORKLOAD = {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9}
 
 
 def make_weight(shape_idx, k, n):
@@ -184,7 +188,7 @@ def run_reference(args):
         # the host's throughput does not depend on how many sweeps it is given: the label follows the GPU arm's layout
         "scaling": "weak" if (args.gpus > 1 and args.parallel == "replicas") else "strong", "vs_baseline": None, "dtype": "i8",
         "data": "synthetic",
-        "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9},
+        "config": dict(WORKLOAD),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": orc.threads, "kind": "port",
                          "sample": sample + "; OpenMP over independent outputs (the reference itself runs this path on one thread)"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -259,15 +263,21 @@ def run_ours(args):
 
     peer = sw > 1 and args.collective == "peer"
     exs = [PeerExchange(gpu, rank, world, MS[mi], SHAPES[si][1]) for mi, si in CASES] if peer else None
+    qs = [torch.empty(MS[mi] * SHAPES[si][0] + 64, dtype=torch.int8, device=dev) for mi, si in CASES] if peer else None
+    qss = [torch.empty(MS[mi], dtype=torch.float32, device=dev) for mi, si in CASES] if peer else None
 
     def enqueue_products():
         for ci, (mi, si) in enumerate(CASES):
-            k, _ = SHAPES[si]
+            k, n = SHAPES[si]
             h = pool[si][mi][0]
-            _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
             if peer:
-                # this rank's slice goes straight into every rank's [M, N] buffer over NVLink
-                exs[ci].store(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
+                # the product's own epilogue stores this rank's columns into every rank's [M, N] buffer over NVLink and
+                # publishes the exchange: no all-gather launch
+                _lib.check(lib.pg_quantize_activations(gpu.handle, xs[ci].data_ptr(), MS[mi], k, qs[ci].data_ptr(), qss[ci].data_ptr()))
+                _lib.check(lib.pg_gemm_i8_exchange(gpu.handle, qs[ci].data_ptr(), qss[ci].data_ptr(), MS[mi], k, h, exs[ci].handle, n,
+                                                   shard[si][0], ys[ci].data_ptr()))
+            else:
+                _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
         if peer:
             # the nine products of the sweep are independent, so the (bounded) waits for the other ranks'
             # slices come after the last product: the step ends when every rank holds all nine full results
@@ -275,17 +285,14 @@ def run_ours(args):
                 ex.wait()
 
     def step_eager():
+        if peer:
+            return enqueue_products()
         for ci, (mi, si) in enumerate(CASES):
             k, _ = SHAPES[si]
             h = pool[si][mi][0]
             _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
-            if peer:
-                exs[ci].store(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
-            elif sw > 1:
+            if sw > 1:
                 dist.all_gather_into_tensor(ys_full[ci], ys[ci])
-        if peer:
-            for ex in exs:
-                ex.wait()
 
     n0 = lib.pg_launch_count()
     with torch.cuda.stream(stream):
@@ -355,7 +362,10 @@ def run_ours(args):
                 xs[ci].copy_(xs_host[ci], non_blocking=True)
                 _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
                 if peer:
-                    exs[ci].allgather(ys[ci].data_ptr(), MS[mi], shard[si][1] - shard[si][0], shard[si][0])
+                    _lib.check(lib.pg_quantize_activations(gpu.handle, xs[ci].data_ptr(), MS[mi], k, qs[ci].data_ptr(), qss[ci].data_ptr()))
+                    _lib.check(lib.pg_gemm_i8_exchange(gpu.handle, qs[ci].data_ptr(), qss[ci].data_ptr(), MS[mi], k, h, exs[ci].handle, n,
+                                                       shard[si][0], ys[ci].data_ptr()))
+                    exs[ci].wait()
                     _lib.check(lib.pg_mem_download(gpu.handle, ys_host[ci].data_ptr(), exs[ci].result_ptr, MS[mi] * n * 4))
                 else:
                     dist.all_gather_into_tensor(ys_full[ci], ys[ci])
@@ -452,14 +462,15 @@ def run_ours(args):
             "metric": "w8a8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak" if replicas else "strong",
             "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-            "config": {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9,
-                       "parallelism": (f"{world} replicas, one sweep each, no collective" if replicas else
-                                       f"column-sharded x{world}" + ((", peer-store all-gather over NVLink (own kernel, bounded flag wait)" if peer
-                                                                      else ", NCCL all-gather of output slices") if world > 1 else "")),
-                       "l2": "inputs larger than L2: each case reads its own copy of the weights (3 copies per shape, 402 MB per step)",
-                       "submission": "one CUDA graph per step" if graph is not None else "eager launches + NCCL",
-                       "collective": ("peer-store" if peer else "nccl") if sw > 1 else None,
-                       "bytes_per_step": total_bytes},
+            "config": dict(WORKLOAD),
+            "config_detail": {
+                "parallelism": (f"{world} replicas, one sweep each, no collective" if replicas else
+                                f"column-sharded x{world}" + ((", slices stored into every rank by the product's epilogue over NVLink, bounded flag waits"
+                                                               if peer else ", NCCL all-gather of output slices") if world > 1 else "")),
+                "l2": "inputs larger than L2: each case reads its own copy of the weights (3 copies per shape, 402 MB per step)",
+                "submission": "one CUDA graph per step" if graph is not None else "eager launches + NCCL",
+                "collective": ("peer-store (fused)" if peer else "nccl") if sw > 1 else None,
+                "bytes_per_step": total_bytes},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_s / e2e_steps * 1e3,
@@ -472,16 +483,31 @@ def run_ours(args):
         }
         if world == 1 and not args.no_extra:
             line["also"] = extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks)
-    # The Llama-3-8B-shape decode stack: on one GPU, or (replicas) one full model and one batch of 16 sequences per GPU
-    if not args.no_llama and (world == 1 or replicas):
+    # The Llama-3-8B-shape decode stack: on one GPU; column-sharded over the ranks (one model, one batch of 16 sequences);
+    # or (replicas) one full model and one batch per GPU
+    if not args.no_llama:
         peak_l = 6532.9
         try:
             with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
                 peak_l = float(json.load(f).get("hbm_gbs", peak_l))
         except (OSError, ValueError):
             pass
-        ll = llama_decode_measurement(gpu, torch, stream, dev, peak_l)
-        if world > 1:
+        if world > 1 and not replicas:
+            ll = llama_decode_measurement(gpu, torch, stream, dev, peak_l, rank=rank, world=world)
+            t = torch.tensor([ll["ms_per_step"], ll["e2e_ms_per_step"]], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ll["ms_per_step"], ll["e2e_ms_per_step"] = float(t[0].item()), float(t[1].item())
+            ll["tok_s"] = ll["batch"] * 1e3 / ll["ms_per_step"]
+            ll["e2e_tok_s"] = ll["batch"] * 1e3 / ll["e2e_ms_per_step"]
+            # bytes of one step over all ranks (every rank reads its shard of the weights and of the KV cache)
+            ll["bytes_per_step"] *= world
+            ll["hbm_gbs"] = ll["bytes_per_step"] / (ll["ms_per_step"] * 1e-3) / 1e9
+            ll["frac_of_measured_hbm"] = ll["hbm_gbs"] / (world * peak_l)
+            ll["parallelism"] = (f"column-sharded x{world}: heads / gate-up channels / O, down and vocabulary columns per rank, four exchanges per "
+                                 "layer stored by the producing kernels, awaited by the consuming ones")
+        else:
+            ll = llama_decode_measurement(gpu, torch, stream, dev, peak_l)
+        if world > 1 and replicas:
             # whole-job tokens per second: all replicas' tokens over the slowest replica's time
             t = torch.tensor([ll["ms_per_step"]], dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -515,7 +541,48 @@ def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
     g = np.random.Generator(np.random.PCG64(2002))
     bf16 = float(peaks.get("bf16_tflops", 1590.0))
     with torch.cuda.stream(stream):
-        for (m, k, n) in ((2048, 4096, 4096), (8192, 4096, 4096), (8192, 4096, 14336)):
+        # the single linear of the first benchmark config: M 32, K = N = 4096, seed 0, quantiser + product; eight copies of the
+        # weights (134 MB) walked in one graph so that no copy is found in L2
+        m, k, n = 32, 4096, 4096
+        g0 = np.random.Generator(np.random.PCG64(0))
+        x = torch.from_numpy(g0.standard_normal((m, k), dtype=np.float32)).to(dev)
+        w0 = (g0.standard_normal((k, n), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        qt0 = pg.quant.quantize_weights(w0, k, n, gpu)
+        t_w = torch.from_numpy(qt0.data_i8_t).to(dev)
+        t_s = torch.from_numpy(qt0.scales).to(dev)
+        copies = []
+        for _ in range(8):
+            buf = torch.empty(t_w.numel() + 1024, dtype=torch.int8, device=dev)
+            buf[: t_w.numel()].copy_(t_w.view(-1))
+            h = _lib.C.c_void_p()
+            _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, buf.data_ptr(), t_s.data_ptr(), k, n, _lib.C.byref(h)))
+            copies.append((h, buf))
+        y = torch.empty(m, n, dtype=torch.float32, device=dev)
+        torch.cuda.synchronize()
+        for h, _ in copies:
+            _lib.check(lib.pg_matmul_quantized(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr()))
+        with gpu.record() as gg:
+            for h, _ in copies:
+                _lib.check(lib.pg_matmul_quantized(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr()))
+        gg.launch()
+        reps = 50
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            gg.launch()
+        e1.record(stream)
+        stream.synchronize()
+        gg.free()
+        us = e0.elapsed_time(e1) / (reps * len(copies)) * 1e3
+        gbs = bytes_w8a8(m, k, n) / (us * 1e-6) / 1e9
+        out["w8a8_linear_M32_K4096_N4096_seed0"] = {"us": us, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak,
+                                                    "tops": 2.0 * m * n * k / (us * 1e-6) / 1e12}
+        for h, _ in copies:
+            lib.pg_qtensor_free(gpu.handle, h)
+        del copies, x, y, t_w
+        # the six prefill shapes, with the kernel the library chooses by itself
+        for (m, k, n) in ((512, 4096, 4096), (512, 4096, 14336), (2048, 4096, 4096), (2048, 4096, 14336), (8192, 4096, 4096),
+                          (8192, 4096, 14336)):
             x = torch.from_numpy(g.standard_normal((m, k), dtype=np.float32)).to(dev)
             wq = torch.randint(-127, 128, (n * k + 1024,), dtype=torch.int8, device=dev)
             sc = torch.rand(n, dtype=torch.float32, device=dev) * 1e-3
@@ -526,12 +593,12 @@ def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
             s = torch.empty(m, dtype=torch.float32, device=dev)
             _lib.check(lib.pg_quantize_activations(gpu.handle, x.data_ptr(), m, k, q.data_ptr(), s.data_ptr()))
             for _ in range(3):
-                _lib.check(lib.pg_gemm_i8(gpu.handle, q.data_ptr(), s.data_ptr(), m, k, h, y.data_ptr(), None, _lib.ALGO_TCGEN05))
+                _lib.check(lib.pg_gemm_i8(gpu.handle, q.data_ptr(), s.data_ptr(), m, k, h, y.data_ptr(), None, _lib.ALGO_AUTO))
             reps = 20
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             for _ in range(reps):
-                _lib.check(lib.pg_gemm_i8(gpu.handle, q.data_ptr(), s.data_ptr(), m, k, h, y.data_ptr(), None, _lib.ALGO_TCGEN05))
+                _lib.check(lib.pg_gemm_i8(gpu.handle, q.data_ptr(), s.data_ptr(), m, k, h, y.data_ptr(), None, _lib.ALGO_AUTO))
             e1.record(stream)
             stream.synchronize()
             us = e0.elapsed_time(e1) / reps * 1e3
@@ -622,7 +689,7 @@ def huffman_load_measurement(gpu, g, rows=4096, cols=4096, sparsity=0.5, reps=5)
             "decoded_gb_s": rows * cols / (ms_h * 1e-3) / 1e9, "identical_to_source": identical, "host_memory": "pinned"}
 
 
-def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmup=8, layers=32):
+def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmup=8, layers=32, rank=0, world=1):
     """Llama-3-8B-shape int8 decode stack: 32 layers, hidden 4096, GQA 32/8 heads of 128, SwiGLU 14336,
     vocab 128256, all linears ~N(0,0.02) quantised per column, batch 16, KV cache pre-filled with N(0,1)
     to context 2048, greedy decode of `steps` tokens from one recorded graph."""
@@ -644,8 +711,13 @@ def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmu
                      "gate_up": (cfg.hidden, 2 * cfg.ffn), "down": (cfg.ffn, cfg.hidden)}[k.split(".")[-1]]
             return torch.randn(*shape, generator=gen, device=dev) * 0.02
 
+        def columns(self, name, cols):
+            """only this rank's columns of a linear are ever drawn (values differ from the single-GPU run's; timing does not care)"""
+            rows = {"lm_head": cfg.hidden, "qkv": cfg.hidden, "o": cfg.n_q_heads * cfg.head_dim, "gate_up": cfg.hidden, "down": cfg.ffn}[name.split(".")[-1]]
+            return torch.randn(rows, len(cols), generator=gen, device=dev) * 0.02
+
     with torch.cuda.stream(stream):
-        model = LlamaInt8Decoder(cfg, gpu, Lazy(), device_index=dev.index)
+        model = LlamaInt8Decoder(cfg, gpu, Lazy(), device_index=dev.index, rank=rank, world=world)
         ctx0 = 2048
         for i in range(cfg.layers):
             model.kcache[i, :, :, :ctx0].normal_(generator=gen)
@@ -678,13 +750,18 @@ def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmu
             host_tok.copy_(model.tokens, non_blocking=True)
             stream.synchronize()
         e2e_s = time.perf_counter() - t0
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
     mean_len = ctx0 + (steps + 1) / 2.0
     bytes_per_step = model.weight_bytes() + model.kv_bytes(int(mean_len))
     out = {"tok_s": cfg.batch * steps / (ms * 1e-3), "ms_per_step": ms / steps, "steps": steps, "batch": cfg.batch, "context": ctx0,
            "layers": cfg.layers, "kernels_per_step": graph.kernels,
            "bytes_per_step": bytes_per_step, "weight_bytes": model.weight_bytes(), "kv_bytes_mean": model.kv_bytes(int(mean_len)),
            "hbm_gbs": bytes_per_step / (ms / steps * 1e-3) / 1e9, "frac_of_measured_hbm": bytes_per_step / (ms / steps * 1e-3) / 1e9 / hbm_peak,
-           "e2e_tok_s": cfg.batch * steps / e2e_s}
+           "e2e_tok_s": cfg.batch * steps / e2e_s, "e2e_ms_per_step": e2e_s / steps * 1e3,
+           "attention_slices": int(model.splits)}
     graph.free()
     model.free()
     del model
@@ -702,12 +779,13 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill GEMM, GGUF product and Huffman load figures")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-llama", action="store_true", help="skip the Llama-8B-shape decode stack measurement (N = 1 only)")
-    ap.add_argument("--parallel", default="replicas", choices=["replicas", "shard"],
-                    help="N > 1: one full replica of the weights and one sweep per GPU, no collective (weak scaling, default: the sweep's "
-                         "rows are independent sequences and the matrices fit one GPU many times over), or column-sharded weights with an "
-                         "all-gather of the output slices (strong scaling of one sweep)")
+    ap.add_argument("--parallel", default="shard", choices=["shard", "replicas"],
+                    help="N > 1: weights sharded by output column over the GPUs, output slices gathered (strong scaling of one sweep and "
+                         "of the Llama decode stack; default), or one full replica of the weights and one sweep per GPU with no collective "
+                         "(weak scaling)")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: all-gather by peer stores recorded in the step graph (default) or eager NCCL")
+                    help="N > 1, sharded: slices stored into every rank by the products' own epilogues, recorded in the step graph "
+                         "(default), or eager NCCL all-gathers")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -64,12 +64,15 @@ typedef enum pg_gguf_type { PG_GGUF_Q4_0 = 2, PG_GGUF_Q4_1 = 3, PG_GGUF_Q8_0 = 8
 
 /* Kernel selection for pg_gemm_i8 / pg_matmul_quantized_algo. */
 typedef enum pg_gemm_algo {
-    PG_ALGO_AUTO = 0,      /* M <= 16: warp-stream kernel; M <= 64: streaming kernel; otherwise tcgen05 */
+    PG_ALGO_AUTO = 0,      /* M <= 16 and K % 64 == 0: warp-stream kernel; 17 <= M <= 32 on narrow layers (and M <= 64
+                              where K % 64 != 0): per-lane streaming kernel; otherwise tcgen05; shapes none of them
+                              takes (K % 16 != 0, unaligned operands): the naive kernel */
     PG_ALGO_NAIVE = 1,     /* one thread per output, dp4a; the on-device checker */
-    PG_ALGO_STREAM = 2,    /* bandwidth-bound decode kernel (128-bit loads + int8 MMA), M <= 64 */
+    PG_ALGO_STREAM = 2,    /* bandwidth-bound decode kernel (per-lane cp.async FIFO + int8 mma.sync), M <= 64 */
     PG_ALGO_TCGEN05 = 3,   /* tcgen05.mma kind::i8, TMEM accumulators, TMA-fed */
     PG_ALGO_WSTREAM = 4    /* persistent decode kernel, M <= 16, K % 64 == 0: bulk copies into per-warp rings, activations
-                              resident in shared memory, split-K through an int32 workspace */
+                              resident in shared memory, K split inside the CTA (and over a cluster when the
+                              activations do not fit beside the rings), sums added in shared memory */
 } pg_gemm_algo;
 
 PG_API const char *pg_last_error(void);
@@ -86,13 +89,24 @@ PG_API int32_t pg_ctx_sync(pg_ctx *ctx);
 PG_API void *pg_ctx_stream(pg_ctx *ctx);
 /* Status word written by kernels whose waits are bounded; 0 if none gave up. Clears it. */
 PG_API int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out);
+/* How long a bounded wait inside a kernel (an mbarrier of a copy ring, another GPU's flag) may last before the kernel
+ * gives up with PG_ERR_DEVICE_TIMEOUT in the status word.  Default one second; at least a microsecond.  Applies to
+ * launches made after the call (recorded graphs keep the value they were recorded with).  The reference has no
+ * counterpart: its ring collectives spin without a limit (src/comm/signal.rs:61-63, 84-86). */
+PG_API int32_t pg_ctx_set_wait_limit_ns(pg_ctx *ctx, uint64_t ns);
+/* Device memory the context has allocated so far for its own intermediates (scratch, staging of *_host calls,
+ * split-K workspace): grows on demand, never shrinks before pg_ctx_destroy.  0 for a context that has only served
+ * calls which bring their own buffers (pg_gemm_i8, pg_matmul_quantized_ex with both buffers, pg_matmul_quantized_static). */
+PG_API uint64_t pg_ctx_scratch_bytes(const pg_ctx *ctx);
 
 /* ---- batched submission, replaces the pending command buffer of GpuContext
  *      (src/metal/context.rs:188-204: commands accumulate and are submitted together) ----
  * Everything enqueued on the context between begin and end is recorded into a CUDA graph
  * instead of running; pg_graph_launch then submits the whole batch with one call.  Run the same
  * calls once before recording: a call that has to grow the context's scratch memory cannot
- * be recorded.  *_host calls (they block) cannot be recorded. */
+ * be recorded.  *_host calls (they block) cannot be recorded.  A graph keeps the scratch addresses it was
+ * recorded with: when a later, larger call makes the context's scratch grow while graphs are alive, the old
+ * block stays allocated until the context's last graph is freed, so older graphs stay valid to launch. */
 PG_API int32_t pg_graph_begin(pg_ctx *ctx);
 PG_API int32_t pg_graph_end(pg_ctx *ctx, pg_graph **out);
 PG_API int32_t pg_graph_launch(pg_ctx *ctx, pg_graph *graph);
@@ -248,6 +262,24 @@ PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_sl
                                  int64_t n_total, int64_t col0);
 PG_API int32_t pg_exchange_wait(pg_ctx *ctx, pg_exchange *ex);
 PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex);
+/* Ranks that live in ONE process (several contexts of one process, one per GPU, or a test that plays all ranks on one
+ * GPU): `all` holds the `world` exchange objects in rank order; no IPC handle is opened. */
+PG_API int32_t pg_exchange_connect_local(pg_ctx *ctx, pg_exchange *ex, pg_exchange *const *all);
+/* The column-sharded integer GEMM with its all-gather inside: this rank's columns `w` ([K, n_local]) of the product
+ * land in columns [col0, col0 + n_local) of EVERY rank's [M, n_total] exchange buffer, stored by the product kernel's
+ * own epilogue (M <= 16, K % 64 == 0; plain stores over NVLink, all loads local), whose last CTA publishes the
+ * exchange.  Other shapes run pg_gemm_i8 into d_slice_tmp ([M, n_local] floats, may be NULL for decode shapes) followed
+ * by pg_exchange_store.  Wait with pg_exchange_wait or a consumer below.  Integer sums and the per-column epilogue
+ * make the gathered matrix bit-identical to the unsharded product. */
+PG_API int32_t pg_gemm_i8_exchange(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k,
+                                   const pg_qtensor *w, pg_exchange *ex, int64_t n_total, int64_t col0, float *d_slice_tmp);
+/* Consumers that begin with the (bounded) wait for every rank's flags, so an exchange costs no launch of its own:
+ * the quantiser of src/quant.rs:97-109 over the gathered [rows, cols] matrix, and pg_add_rmsnorm_quantize with the
+ * gathered matrix as the residual delta. */
+PG_API int32_t pg_quantize_activations_exchange(pg_ctx *ctx, pg_exchange *ex, int64_t rows, int64_t cols, int8_t *d_q,
+                                                float *d_scales);
+PG_API int32_t pg_add_rmsnorm_quantize_exchange(pg_ctx *ctx, float *d_x, pg_exchange *ex_delta, const float *d_w, int64_t rows,
+                                                int64_t dim, float eps, int8_t *d_q, float *d_scales, float *d_normed);
 
 /* ---- the glue of one Llama decode step between the quantised linears (what the reference runs on the
  *      host in f32: src/models/llama/decoder.rs:69-155, src/models/llama/attention.rs:73-195,
@@ -278,11 +310,37 @@ PG_API int32_t pg_gqa_attention_decode_fused(pg_ctx *ctx, const float *d_qkv, co
                                              const float *d_sin, float *d_kcache, float *d_vcache, int64_t B, int64_t Hq,
                                              int64_t Hkv, int64_t hd, int64_t cap, float *d_work, float *d_out,
                                              int8_t *d_out_i8, float *d_out_scales);
-/* embedding gather (src/nn.rs:217-227); greedy argmax, first maximum (examples/llama/main.rs:15-26) */
+/* embedding gather (src/nn.rs:217-227); greedy argmax, first maximum (examples/llama/main.rs:15-26).  *d_pos is
+   advanced by one but never beyond pos_limit (pass the KV capacity; 0 = no limit).  The kernels that read *d_pos
+   (pg_rope_kv_append, the attention entry points) touch neither the caches nor the rotation tables when it lies outside
+   [0, cap): they record PG_ERR_INVALID in the context's status word (pg_ctx_device_status) instead. */
 PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim,
                             float *d_out);
 PG_API int32_t pg_argmax_advance(pg_ctx *ctx, const float *d_logits, int64_t B, int64_t V, int32_t *d_tokens,
-                                 int32_t *d_pos);
+                                 int32_t *d_pos, int64_t pos_limit);
+/* ---- the same step with every linear sharded by output column over the ranks of a node (one process per GPU):
+ *      whole KV heads with their query heads per rank (fuse_qkv's column order, src/models/llama/attention.rs:51-71,
+ *      regrouped per rank), the same channel range of gate and up per rank (src/models/llama/decoder.rs:49-67), the
+ *      vocabulary by column range.  Four exchanges per layer (attention rows, O, SwiGLU rows, down), each stored by the
+ *      kernel that produces the slice and awaited by the kernel that consumes the rows. ----
+ * attention on this rank's heads (see pg_gqa_attention_decode_fused); merged f32 rows -> columns [col0, col0 + Hq*hd)
+ * of every rank's [B, n_total] buffer.  splits: context slices per (sequence, KV head); the unsharded shape's
+ * pg_gqa_decode_splits value reproduces the single-GPU sums bit for bit, 0 = this rank's own choice. */
+PG_API int32_t pg_gqa_attention_decode_fused_exchange(pg_ctx *ctx, const float *d_qkv, const int32_t *d_pos, const float *d_cos,
+                                                      const float *d_sin, float *d_kcache, float *d_vcache, int64_t B,
+                                                      int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_work,
+                                                      int32_t splits, pg_exchange *ex, int64_t n_total, int64_t col0);
+/* silu(gate) * up on this rank's [rows, 2 F_local] = [gate columns | up columns]; f32 rows -> columns
+ * [col0, col0 + F_local) of every rank's [rows, F_total] buffer */
+PG_API int32_t pg_swiglu_exchange(pg_ctx *ctx, const float *d_gate_up_local, int64_t rows, int64_t F_local, pg_exchange *ex,
+                                  int64_t F_total, int64_t col0);
+/* greedy choice over a vocabulary sharded by column: this rank's (maximum, index) pair per sequence goes to every
+ * rank (exchange buffer of B * world * 8 bytes); pg_pick_embed waits, takes the first maximum, advances *d_pos and
+ * gathers the chosen tokens' embedding rows (d_table nullable) */
+PG_API int32_t pg_argmax_exchange(pg_ctx *ctx, const float *d_logits_local, int64_t B, int64_t V_local, int64_t v0,
+                                  pg_exchange *ex);
+PG_API int32_t pg_pick_embed(pg_ctx *ctx, pg_exchange *ex, int64_t B, int32_t *d_tokens, int32_t *d_pos, int64_t pos_limit,
+                             const float *d_table, int64_t dim, float *d_out);
 
 /* ---- Tensor::matmul, naive branch (src/tensor.rs:1342-1354): [M,K] x [K,N] f32,
  *      ascending-p accumulation with separately rounded multiply and add ---- */

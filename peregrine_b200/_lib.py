@@ -47,6 +47,8 @@ SIGNATURES = {
     "pg_ctx_sync": (_i32, [_vp]),
     "pg_ctx_stream": (_vp, [_vp]),
     "pg_ctx_device_status": (_i32, [_vp, C.POINTER(_i32)]),
+    "pg_ctx_set_wait_limit_ns": (_i32, [_vp, C.c_uint64]),
+    "pg_ctx_scratch_bytes": (C.c_uint64, [_vp]),
     "pg_graph_begin": (_i32, [_vp]),
     "pg_graph_end": (_i32, [_vp, C.POINTER(_vp)]),
     "pg_graph_launch": (_i32, [_vp, _vp]),
@@ -95,6 +97,14 @@ SIGNATURES = {
     "pg_exchange_store": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64]),
     "pg_exchange_wait": (_i32, [_vp, _vp]),
     "pg_exchange_destroy": (_i32, [_vp, _vp]),
+    "pg_exchange_connect_local": (_i32, [_vp, _vp, C.POINTER(_vp)]),
+    "pg_gemm_i8_exchange": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
+    "pg_quantize_activations_exchange": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "pg_add_rmsnorm_quantize_exchange": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _vp, _vp, _vp]),
+    "pg_gqa_attention_decode_fused_exchange": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _i32, _vp, _i64, _i64]),
+    "pg_swiglu_exchange": (_i32, [_vp, _vp, _i64, _i64, _vp, _i64, _i64]),
+    "pg_argmax_exchange": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp]),
+    "pg_pick_embed": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _i64, _vp]),
     "pg_add_rmsnorm_quantize": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, C.c_float, _vp, _vp, _vp]),
     "pg_swiglu_quantize": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "pg_rope_kv_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp]),
@@ -102,8 +112,26 @@ SIGNATURES = {
     "pg_gqa_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "pg_gqa_attention_decode_fused": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "pg_embedding": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
-    "pg_argmax_advance": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "pg_argmax_advance": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _i64]),
     "pg_matmul_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+}
+
+# the knobs of include/peregrine_b200_tune.h (tests and profiling runs; process-wide, not thread-safe)
+_int = C.c_int
+TUNE_SIGNATURES = {
+    "pg_tune_stream_ng": (None, [_int]),
+    "pg_tune_stream_depth": (None, [_int]),
+    "pg_tune_stream_carveout": (None, [_int]),
+    "pg_tune_stream_split": (None, [_int]),
+    "pg_tune_wstream_kw": (None, [_int]),
+    "pg_tune_wstream_cluster": (None, [_int]),
+    "pg_tune_tcgen05_bn": (None, [_int]),
+    "pg_tune_tcgen05_pair": (None, [_int]),
+    "pg_tune_gguf_simple": (None, [_int]),
+    "pg_tune_gguf_rows": (None, [_int]),
+    "pg_tune_host_direct": (None, [_int, _int]),
+    "pg_tune_host_push": (None, [_int]),
+    "pg_huffman_last_sweeps": (_int, []),
 }
 
 _lib = None
@@ -126,13 +154,10 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    for name in ("pg_tune_stream_ng", "pg_tune_stream_depth", "pg_tune_stream_carveout", "pg_tune_stream_split", "pg_tune_wstream_kw", "pg_tune_wstream_cluster", "pg_tune_tcgen05_bn", "pg_tune_tcgen05_pair", "pg_tune_gguf_simple", "pg_tune_gguf_rows"):
-        getattr(lib, name).argtypes = [C.c_int]
-        getattr(lib, name).restype = None
-    lib.pg_tune_host_direct.argtypes = [C.c_int, C.c_int]
-    lib.pg_tune_host_direct.restype = None
-    lib.pg_tune_host_push.argtypes = [C.c_int]
-    lib.pg_tune_host_push.restype = None
+    for name, (res, args) in TUNE_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
     _lib = lib
     return lib
 

@@ -19,52 +19,34 @@ void pg_set_error(const char *fmt, ...)
     va_end(ap);
 }
 
-int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes)
+// Grows one of the context's device blocks.  Work already enqueued may still use the old block, so the stream is
+// drained first; a recorded graph may use it for as long as it lives, so with graphs alive the old block is parked
+// (pg_ctx::retired) instead of freed.
+static int32_t grow_block(pg_ctx *ctx, void **block, size_t *have, size_t bytes, const char *what, bool zeroed)
 {
-    if (bytes <= ctx->scratch_bytes) return PG_OK;
-    if (ctx->capturing) PG_FAIL(PG_ERR_INVALID, "scratch memory would have to grow while a graph is being recorded; run the call once before recording");
-    // Work already enqueued may still use the old block: drain before replacing it.
+    if (bytes <= *have) return PG_OK;
+    if (ctx->capturing)
+        PG_FAIL(PG_ERR_INVALID, "%s memory would have to grow while a graph is being recorded; run the call once before recording", what);
     PG_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (ctx->scratch) PG_CUDA(cudaFree(ctx->scratch));
-    ctx->scratch = nullptr;
-    ctx->scratch_bytes = 0;
+    if (*block) {
+        if (ctx->live_graphs > 0)
+            ctx->retired.push_back(*block);
+        else
+            PG_CUDA(cudaFree(*block));
+    }
+    *block = nullptr;
+    *have = 0;
     size_t want = bytes + (bytes >> 2);
     want = (want + 255) & ~(size_t)255;
-    PG_CUDA(cudaMalloc(&ctx->scratch, want));
-    ctx->scratch_bytes = want;
+    PG_CUDA(cudaMalloc(block, want));
+    if (zeroed) PG_CUDA(cudaMemsetAsync(*block, 0, want, ctx->stream));
+    *have = want;
     return PG_OK;
 }
 
-int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes)
-{
-    if (bytes <= ctx->staging_bytes) return PG_OK;
-    if (ctx->capturing) PG_FAIL(PG_ERR_INVALID, "staging memory would have to grow while a graph is being recorded");
-    PG_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (ctx->staging) PG_CUDA(cudaFree(ctx->staging));
-    ctx->staging = nullptr;
-    ctx->staging_bytes = 0;
-    size_t want = bytes + (bytes >> 2);
-    want = (want + 255) & ~(size_t)255;
-    PG_CUDA(cudaMalloc(&ctx->staging, want));
-    ctx->staging_bytes = want;
-    return PG_OK;
-}
-
-int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes)
-{
-    if (bytes <= ctx->splitk_bytes) return PG_OK;
-    if (ctx->capturing) PG_FAIL(PG_ERR_INVALID, "split-K workspace would have to grow while a graph is being recorded; run the call once before recording");
-    PG_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (ctx->splitk) PG_CUDA(cudaFree(ctx->splitk));
-    ctx->splitk = nullptr;
-    ctx->splitk_bytes = 0;
-    size_t want = bytes + (bytes >> 2);
-    want = (want + 255) & ~(size_t)255;
-    PG_CUDA(cudaMalloc(&ctx->splitk, want));
-    PG_CUDA(cudaMemsetAsync(ctx->splitk, 0, want, ctx->stream));
-    ctx->splitk_bytes = want;
-    return PG_OK;
-}
+int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes) { return grow_block(ctx, &ctx->scratch, &ctx->scratch_bytes, bytes, "scratch", false); }
+int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes) { return grow_block(ctx, &ctx->staging, &ctx->staging_bytes, bytes, "staging", false); }
+int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes) { return grow_block(ctx, &ctx->splitk, &ctx->splitk_bytes, bytes, "split-K workspace", true); }
 
 int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes)
 {
@@ -80,26 +62,6 @@ int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes)
 }
 
 namespace {
-
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = true;
-    explicit DeviceGuard(int dev)
-    {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
-    }
-    ~DeviceGuard()
-    {
-        int cur = -1;
-        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
-    }
-};
-
-#define PG_ENTER(ctx)                                                   \
-    PG_REQUIRE((ctx) != nullptr, "null context");                       \
-    DeviceGuard _guard((ctx)->device);                                  \
-    if (!_guard.ok) PG_FAIL(PG_ERR_CUDA, "cudaSetDevice(%d) failed", (ctx)->device)
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -160,6 +122,8 @@ int32_t pg_ctx_destroy(pg_ctx *ctx)
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->staging) cudaFree(ctx->staging);
     if (ctx->splitk) cudaFree(ctx->splitk);
+    for (void *p : ctx->retired) cudaFree(p);
+    if (ctx->h_done) cudaFreeHost((void *)ctx->h_done);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -187,6 +151,16 @@ int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out)
     return PG_OK;
 }
 
+int32_t pg_ctx_set_wait_limit_ns(pg_ctx *ctx, uint64_t ns)
+{
+    PG_REQUIRE(ctx != nullptr, "null context");
+    PG_REQUIRE(ns >= 1000, "pg_ctx_set_wait_limit_ns: a limit below a microsecond would end waits that are about to succeed");
+    ctx->wait_limit_ns = ns;
+    return PG_OK;
+}
+
+uint64_t pg_ctx_scratch_bytes(const pg_ctx *ctx) { return ctx ? (uint64_t)(ctx->scratch_bytes + ctx->staging_bytes + ctx->splitk_bytes) : 0; }
+
 int32_t pg_graph_begin(pg_ctx *ctx)
 {
     PG_ENTER(ctx);
@@ -204,7 +178,13 @@ int32_t pg_graph_end(pg_ctx *ctx, pg_graph **out)
     PG_REQUIRE(ctx->capturing, "pg_graph_end: not recording");
     ctx->capturing = false;
     cudaGraph_t g = nullptr;
-    PG_CUDA(cudaStreamEndCapture(ctx->stream, &g));
+    // cudaStreamEndCapture ends the capture even when a recorded call had failed and invalidated it
+    const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &g);
+    if (ce != cudaSuccess || !g) {
+        cudaGetLastError();
+        if (g) cudaGraphDestroy(g);
+        PG_FAIL(PG_ERR_CUDA, "pg_graph_end: the recording was invalidated (%s); nothing was recorded", cudaGetErrorString(ce));
+    }
     cudaGraphExec_t exec = nullptr;
     cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
     cudaGraphDestroy(g);
@@ -215,6 +195,7 @@ int32_t pg_graph_end(pg_ctx *ctx, pg_graph **out)
         PG_FAIL(PG_ERR_NOMEM, "out of host memory");
     }
     pgg->exec = exec;
+    ctx->live_graphs++;
     *out = pgg;
     return PG_OK;
 }
@@ -234,6 +215,10 @@ int32_t pg_graph_free(pg_ctx *ctx, pg_graph *graph)
     PG_CUDA(cudaStreamSynchronize(ctx->stream));
     if (graph->exec) cudaGraphExecDestroy(graph->exec);
     delete graph;
+    if (ctx->live_graphs > 0 && --ctx->live_graphs == 0) {
+        for (void *p : ctx->retired) cudaFree(p);
+        ctx->retired.clear();
+    }
     return PG_OK;
 }
 

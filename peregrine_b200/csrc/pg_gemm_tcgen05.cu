@@ -419,7 +419,8 @@ int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, 
         w->tmap_b_box_rows = BN;
     }
     auto kern = gemm_i8_tcgen05_kernel<BN, AR>;
-    PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    static std::atomic<uint64_t> smem_set{0};
+    PG_CUDA(pg_max_smem_once(kern, (int)C::SMEM, ctx->device, smem_set));
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     kern<<<grid, NUM_THREADS, C::SMEM, ctx->stream>>>(ta, *reinterpret_cast<CUtensorMap *>(w->tmap_b), d_as, w->d_scales, M, N, K,

@@ -381,7 +381,8 @@ int32_t pgk_gemm_i8_tcgen05_2cta(pg_ctx *ctx, const int8_t *d_a, const float *d_
         if (rc) return rc;
         w->tmap_b_box_rows = TNH;
     }
-    PG_CUDA(cudaFuncSetAttribute(gemm_i8_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    static std::atomic<uint64_t> smem_set{0};
+    PG_CUDA(pg_max_smem_once(gemm_i8_tcgen05_2cta_kernel, (int)SMEM_BYTES, ctx->device, smem_set));
     const int tiles = ((M + 2 * TM - 1) / (2 * TM)) * ((N + TN - 1) / TN);
     const int max_pairs = ctx->sm_count / 2;
     const int pairs = tiles < max_pairs ? tiles : max_pairs;

@@ -238,7 +238,8 @@ int32_t launch(pg_ctx *ctx, const int8_t *a, const float *as, int M, int K, cons
     constexpr size_t red_bytes = (size_t)WARPS * MB * 16 * NT * sizeof(int32_t);
     constexpr size_t smem = (fifo_bytes > red_bytes ? fifo_bytes : red_bytes) + (size_t)(S - 1) * MB * 16 * NT * sizeof(int32_t);
     auto kern = gemv_w8a8_kernel<MB, NG, WARPS, D, HI, S>;
-    if (smem > 48 * 1024) PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static std::atomic<uint64_t> smem_set{0};
+    if (smem > 48 * 1024) PG_CUDA(pg_max_smem_once(kern, (int)smem, ctx->device, smem_set));
     if (g_carveout_pct >= 0) PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, g_carveout_pct));
     const int64_t blocks = ((N + NT - 1) / NT) * S;
     PG_REQUIRE(blocks <= 0x7fffffff, "gemm_i8 stream: N too large");

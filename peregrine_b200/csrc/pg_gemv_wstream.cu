@@ -34,7 +34,6 @@ constexpr int WS_WARPS = 16;
 constexpr int WS_THREADS = WS_WARPS * 32;
 constexpr int WS_SLOTS = 2;
 constexpr int WS_SMEM_MAX = 227 * 1024;
-constexpr unsigned long long WS_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
 // SEG: bytes of one weight row per ring slot.  512 keeps 128 KB in flight per SM; 256 leaves room
 // for activations of up to 146 KB.
@@ -73,7 +72,8 @@ __device__ __forceinline__ bool ws_mbar_try(uint32_t bar, uint32_t parity)
         : "memory");
     return done != 0;
 }
-__device__ __forceinline__ bool ws_mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status)
+__device__ __forceinline__ bool ws_mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int32_t *status,
+                                             unsigned long long limit_ns)
 {
     unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
@@ -83,7 +83,7 @@ __device__ __forceinline__ bool ws_mbar_wait(uint32_t bar, uint32_t parity, vola
             const unsigned long long now = ws_globaltimer();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > WS_WAIT_LIMIT_NS) {
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicExch(status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
                 return false;
@@ -127,11 +127,15 @@ __device__ __forceinline__ uint32_t ws_mapa(uint32_t local_addr, uint32_t cta)
 // Warp w: tile slot w / kw, K part w % kw (KW bytes each) of the CTA's K range.
 // CTA b (unit u = b / cs; U = number of clusters or CTAs): tiles  u + U * (slot + (16 / kw) * j).
 // Shared memory: activations (a_bytes, row stride a_stride) | rings | mbarriers | CL: exchange cells [2][16 / kw][512 B].
-template <bool HI, int SEG, bool CL>
+// PEER: the kernel is one rank's part of a column-sharded product.  Its outputs go straight into every rank's [M, ld]
+// result buffer (plain stores to peer pointers over NVLink, columns col0 + n) and the kernel itself publishes the
+// exchange when its last CTA is done: no separate all-gather launch.  Only stores cross NVLink; every load, bulk
+// copies included, reads this GPU's own memory.
+template <bool HI, int SEG, bool CL, bool PEER>
 __global__ void __launch_bounds__(WS_THREADS, 1)
     gemv_wstream_kernel(const int8_t *__restrict__ a, const float *__restrict__ a_scales, int M, int K, const int8_t *__restrict__ bt,
                         const float *__restrict__ w_scales, int64_t N, float *__restrict__ y, int32_t *__restrict__ acc_out, int kw,
-                        int KW, int a_stride, int a_bytes, int KH, int32_t *status)
+                        int KW, int a_stride, int a_bytes, int KH, int32_t *status, unsigned long long limit_ns, const PgPeerOut po)
 {
     using C = WsCfg<SEG>;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -198,7 +202,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     __syncthreads();
     if ((int)threadIdx.x < M)
         ws_bulk_load(a_base + threadIdx.x * (uint32_t)a_stride, a + (int64_t)threadIdx.x * K + ka0, (uint32_t)kalen, a_bar);
-    bool ok = ws_mbar_wait(a_bar, 0, abort_flag, status);   // also keeps the shared memory alive until the copy has landed
+    bool ok = ws_mbar_wait(a_bar, 0, abort_flag, status, limit_ns);   // also keeps the shared memory alive until the copy has landed
     if (CL) {
         // the cells start from zero, and nobody adds into them before that
         if (my_rank == 0)
@@ -223,7 +227,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         if (j < my_tiles) {
             for (int sc = 0; sc < nsub; sc++, q++) {
                 const uint32_t slot = fifo + (uint32_t)(q % WS_SLOTS) * C::SLOT_BYTES;
-                ok = ok && ws_mbar_wait(my_bar + (uint32_t)(q % WS_SLOTS) * 8, (uint32_t)(q / WS_SLOTS) & 1u, abort_flag, status);
+                ok = ok && ws_mbar_wait(my_bar + (uint32_t)(q % WS_SLOTS) * 8, (uint32_t)(q / WS_SLOTS) & 1u, abort_flag, status, limit_ns);
                 if (ok) {
                     const int steps = min(SEG, klen - sc * SEG) >> 6;
                     const uint32_t ak = (uint32_t)sc * SEG;
@@ -286,12 +290,28 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
             for (int h = 0; h < (HI ? 2 : 1); h++) {
                 const int m = r + 8 * h;
                 if (m < M) {
+                    if (PEER) {
+                        // two adjacent columns per lane: one 8-byte store per rank where the pair exists and is aligned
+                        const float as = h ? as_hi : as_lo;
+                        const float v0 = (n < N) ? __fmul_rn(__fmul_rn(__int2float_rn(acc[2 * h]), as), __ldg(w_scales + n)) : 0.0f;
+                        const float v1 = (n + 1 < N) ? __fmul_rn(__fmul_rn(__int2float_rn(acc[2 * h + 1]), as), __ldg(w_scales + n + 1)) : 0.0f;
+                        const int64_t at = (int64_t)m * po.ld + po.col0 + n;
+                        if (n + 1 < N && ((po.ld | po.col0) & 1) == 0) {
+                            for (int p = 0; p < po.world; p++) *reinterpret_cast<float2 *>(po.y[p] + at) = make_float2(v0, v1);
+                        } else {
+                            if (n < N)
+                                for (int p = 0; p < po.world; p++) po.y[p][at] = v0;
+                            if (n + 1 < N)
+                                for (int p = 0; p < po.world; p++) po.y[p][at + 1] = v1;
+                        }
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        if (n + c < N) {
-                            const int32_t sum = acc[2 * h + c];
-                            if (acc_out) acc_out[(int64_t)m * N + n + c] = sum;
-                            if (y) y[(int64_t)m * N + n + c] = __fmul_rn(__fmul_rn(__int2float_rn(sum), h ? as_hi : as_lo), __ldg(w_scales + n + c));
+                        for (int c = 0; c < 2; c++) {
+                            if (n + c < N) {
+                                const int32_t sum = acc[2 * h + c];
+                                if (acc_out) acc_out[(int64_t)m * N + n + c] = sum;
+                                if (y) y[(int64_t)m * N + n + c] = __fmul_rn(__fmul_rn(__int2float_rn(sum), h ? as_hi : as_lo), __ldg(w_scales + n + c));
+                            }
                         }
                     }
                 }
@@ -299,19 +319,21 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         }
         acc[0] = acc[1] = acc[2] = acc[3] = 0;
     }
+    if (PEER) pg_peer_publish(po, threadIdx.x);
 }
 
 int g_force_kw = 0;    // tuning override, 0 = heuristic
 int g_force_cs = 0;    // 0 = heuristic, else the cluster size (1, 2, 4) over which K is split
 
-template <bool HI, int SEG, bool CL>
+template <bool HI, int SEG, bool CL, bool PEER>
 int32_t ws_launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, const int8_t *d_bt, const float *d_ws, int64_t n,
-                  float *d_y, int32_t *d_acc, int kw, int KW, int a_stride, int a_bytes, int KH, int grid, int cs)
+                  float *d_y, int32_t *d_acc, int kw, int KW, int a_stride, int a_bytes, int KH, int grid, int cs, const PgPeerOut &po)
 {
     using C = WsCfg<SEG>;
-    auto kern = gemv_wstream_kernel<HI, SEG, CL>;
+    auto kern = gemv_wstream_kernel<HI, SEG, CL, PEER>;
     const int smem = a_bytes + C::RING_BYTES + C::BAR_BYTES + (CL ? 2 * (WS_WARPS / kw) * 512 : 0);
-    PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM_MAX));
+    static std::atomic<uint64_t> smem_set{0};
+    PG_CUDA(pg_max_smem_once(kern, WS_SMEM_MAX, ctx->device, smem_set));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(WS_THREADS);
@@ -326,7 +348,8 @@ int32_t ws_launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int 
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = CL ? 2 : 1;
-    PG_CUDA(cudaLaunchKernelEx(&cfg, kern, d_a, d_as, M, K, d_bt, d_ws, n, d_y, d_acc, kw, KW, a_stride, a_bytes, KH, ctx->d_status));
+    PG_CUDA(cudaLaunchKernelEx(&cfg, kern, d_a, d_as, M, K, d_bt, d_ws, n, d_y, d_acc, kw, KW, a_stride, a_bytes, KH, ctx->d_status,
+                               ctx->wait_limit_ns, po));
     PG_LAUNCHED();
     return PG_OK;
 }
@@ -358,8 +381,8 @@ bool pgk_gemm_i8_wstream_supports(int64_t m, int64_t k, int64_t n)
     return ws_cluster_for<512>(m, k) != 0 || ws_cluster_for<256>(m, k) != 0;
 }
 
-int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
-                            const float *d_ws, int64_t n, float *d_y, int32_t *d_acc)
+static int32_t ws_dispatch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                           const float *d_ws, int64_t n, float *d_y, int32_t *d_acc, const PgPeerOut *peer)
 {
     if (!pgk_gemm_i8_wstream_supports(m, k, n) || ((uintptr_t)d_a & 15) || ((uintptr_t)d_bt & 15))
         PG_FAIL(PG_ERR_UNSUPPORTED,
@@ -393,8 +416,12 @@ int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     const int cells = cs > 1 ? 2 * groups * 512 : 0;
     const bool big_ring = a_bytes + cells <= WsCfg<512>::A_MAX;
     PG_REQUIRE(a_bytes + cells <= WsCfg<256>::A_MAX, "gemm_i8 warp-stream: activations do not fit in shared memory");
-#define PG_WS_CASE(HI, SEG, CL) \
-    return ws_launch<HI, SEG, CL>(ctx, d_a, d_as, M, K, d_bt, d_ws, n, d_y, d_acc, kw, KW, a_stride, a_bytes, KH, grid, cs)
+    static const PgPeerOut no_peer = {};
+#define PG_WS_CASE(HI, SEG, CL)                                                                                                      \
+    return peer ? ws_launch<HI, SEG, CL, true>(ctx, d_a, d_as, M, K, d_bt, d_ws, n, d_y, d_acc, kw, KW, a_stride, a_bytes, KH, grid, \
+                                               cs, *peer)                                                                            \
+                : ws_launch<HI, SEG, CL, false>(ctx, d_a, d_as, M, K, d_bt, d_ws, n, d_y, d_acc, kw, KW, a_stride, a_bytes, KH,      \
+                                                grid, cs, no_peer)
     if (cs > 1) {
         if (hi) {
             if (big_ring) PG_WS_CASE(true, 512, true);
@@ -410,4 +437,16 @@ int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     if (big_ring) PG_WS_CASE(false, 512, false);
     PG_WS_CASE(false, 256, false);
 #undef PG_WS_CASE
+}
+
+int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                            const float *d_ws, int64_t n, float *d_y, int32_t *d_acc)
+{
+    return ws_dispatch(ctx, d_a, d_as, m, k, d_bt, d_ws, n, d_y, d_acc, nullptr);
+}
+
+int32_t pgk_gemm_i8_wstream_peer(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                                 const float *d_ws, int64_t n, const PgPeerOut &out)
+{
+    return ws_dispatch(ctx, d_a, d_as, m, k, d_bt, d_ws, n, nullptr, nullptr, &out);
 }

@@ -332,7 +332,8 @@ int32_t run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, f
     const int K = (int)w->k, nblk = K / 32, M = (int)m;
     const size_t smem = (size_t)D * G_SLOT_BYTES + 2 * G_WARPS * R * 128 * sizeof(float);
     auto kern = gguf_mma_kernel<TYPE, R, D>;
-    PG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static std::atomic<uint64_t> smem_set{0};
+    PG_CUDA(pg_max_smem_once(kern, (int)smem, ctx->device, smem_set));
     const int64_t tiles = (w->n + 16 * R - 1) / (16 * R);
     const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
     cudaLaunchAttribute attr[1];

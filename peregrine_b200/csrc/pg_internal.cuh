@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include <atomic>
+#include <vector>
 
 #include "peregrine_b200.h"
 
@@ -39,6 +40,19 @@ extern std::atomic<uint64_t> g_pg_launches;
         g_pg_launches.fetch_add(1);         \
         PG_CUDA(cudaGetLastError());        \
     } while (0)
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) sticks to a kernel for the life of the process (per device): set it
+// once per kernel instantiation and device instead of on every launch.  `mask` is a static of the calling launcher
+// (one per instantiation); bit d = done on device d.
+template <typename K>
+inline cudaError_t pg_max_smem_once(K kern, int bytes, int device, std::atomic<uint64_t> &mask)
+{
+    const uint64_t bit = 1ull << (device & 63);
+    if (mask.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) mask.fetch_or(bit, std::memory_order_release);
+    return e;
+}
 
 // ------------------------------------------------- loads across kernels ----
 // The kernels of this library are launched with programmatic stream serialisation and signal
@@ -124,6 +138,27 @@ struct pg_ctx {
     void *h_pinned = nullptr;     // pinned staging for *_host calls
     size_t h_pinned_bytes = 0;
     bool capturing = false;       // between pg_graph_begin and pg_graph_end
+    // Bounded waits inside kernels (mbarrier waits, flag waits on other GPUs) give up after this long and record
+    // PG_ERR_DEVICE_TIMEOUT in d_status; a kernel argument, so a caller (or a test) can shorten it per context.
+    unsigned long long wait_limit_ns = 1000ull * 1000ull * 1000ull;
+    // A recorded graph keeps the scratch / staging / split-K addresses it was recorded with.  While graphs of this
+    // context are alive, a block that has to grow is not freed but parked here, and freed when the last graph goes
+    // (or with the context), so that replaying an older graph never touches freed memory.
+    int live_graphs = 0;
+    std::vector<void *> retired;
+    // page-locked host buffers seen by the *_host calls: host pointer -> device view (cudaPointerGetAttributes costs
+    // microseconds per call; a buffer's registration does not change while the caller keeps using it)
+    struct HostView {
+        const void *host = nullptr;
+        void *dev = nullptr;
+    };
+    HostView host_views[8];
+    int host_view_next = 0;
+    // completion word of the *_host calls: a word of mapped page-locked memory that the last kernel of a call writes
+    // and the host polls, instead of a stream synchronisation
+    volatile uint32_t *h_done = nullptr;
+    uint32_t *d_done = nullptr;   // the device's view of h_done
+    uint32_t done_seq = 0;
 };
 
 struct pg_graph {
@@ -156,14 +191,135 @@ struct pg_gguf_weight {
     int interleaved = 0;        // quants stored in the tensor-core kernel's chunk order (see repack_kernel)
 };
 
+// ---- exchange between the GPUs of a node (csrc/pg_peer.cu) ----------------------------------------------------
+// One symmetric block per rank: a result buffer followed by control words.  Producers store their slice of a result
+// into EVERY rank's buffer with plain stores (peer pointers from CUDA IPC) and then raise flag[producer rank] in every
+// rank's control block to the number of the exchange; consumers spin, bounded, on the flags of their OWN block.
+constexpr int PG_MAX_PEERS = 8;
+enum { PG_CTL_FLAG0 = 0, PG_CTL_SENT = 8, PG_CTL_WAITED = 9, PG_CTL_DONE = 10, PG_CTL_WORDS = 64 };
+
+// what a producing kernel gets (by value, in its arguments)
+struct PgPeerOut {
+    float *y[PG_MAX_PEERS];          // result buffer of each rank (own included)
+    uint32_t *ctl[PG_MAX_PEERS];     // control block of each rank
+    int32_t world, rank;
+    int64_t ld, col0;                // row stride of the result (total columns) and this rank's first column
+};
+// what a consuming kernel gets: its own control block; ctl == nullptr means "nothing to wait for"
+struct PgPeerWait {
+    const uint32_t *ctl;
+    int32_t world;
+    int32_t *status;
+    unsigned long long limit_ns;
+};
+
+struct pg_exchange {
+    int world = 0, rank = 0;
+    float *y_local = nullptr;       // own result buffer (start of the symmetric block)
+    uint32_t *ctl_local = nullptr;  // own control block (behind the result buffer)
+    void *base_local = nullptr;
+    size_t bytes = 0, y_bytes = 0;
+    void *peer_base[PG_MAX_PEERS] = {};
+    float *y[PG_MAX_PEERS] = {};
+    uint32_t *ctl[PG_MAX_PEERS] = {};
+    bool connected = false;
+};
+PgPeerOut pg_peer_out(const pg_exchange *ex, int64_t ld, int64_t col0);
+PgPeerWait pg_peer_wait_of(const pg_ctx *ctx, const pg_exchange *ex);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ unsigned long long pg_globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Consumer side, called by every thread of the CTA (tid = linear thread index) after griddepcontrol.wait: threads
+// 0..world-1 wait until rank `tid` has delivered the exchange this rank's own producer kernel (earlier in the stream)
+// counted last.  Bounded: on expiry PG_ERR_DEVICE_TIMEOUT goes to the status word and the kernel carries on with
+// whatever the buffer holds.  Data behind the flags must be read through L2 (pg_ld_fresh / bulk copies).
+__device__ __forceinline__ void pg_peer_wait(const PgPeerWait &w, int tid)
+{
+    if (w.ctl == nullptr) return;
+    if (tid < w.world) {
+        const uint32_t want = __ldcg(w.ctl + PG_CTL_SENT);
+        const unsigned long long t0 = pg_globaltimer_ns();
+        for (uint32_t it = 0;; ++it) {
+            uint32_t got;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(w.ctl + PG_CTL_FLAG0 + tid) : "memory");
+            if ((int32_t)(got - want) >= 0) break;
+            if ((it & 63) == 63 && pg_globaltimer_ns() - t0 > w.limit_ns) {
+                atomicExch(w.status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+}
+// Producer side, called once by every thread of EVERY CTA of the grid after its last store into the peers' buffers.
+// The CTA barrier orders the CTA's stores before thread 0's system-scope fence (fences are cumulative); the last CTA
+// to be counted numbers the exchange and raises this rank's flag on every rank.
+__device__ __forceinline__ void pg_peer_publish(const PgPeerOut &o, int tid)
+{
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence_system();
+        uint32_t *ctl = o.ctl[o.rank];
+        const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(&ctl[PG_CTL_DONE], 1u) == ctas - 1) {
+            ctl[PG_CTL_DONE] = 0;
+            const uint32_t seq = __ldcg(ctl + PG_CTL_SENT) + 1;
+            __stcg(ctl + PG_CTL_SENT, seq);
+            __threadfence_system();
+            for (int p = 0; p < o.world; p++)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(o.ctl[p] + PG_CTL_FLAG0 + o.rank), "r"(seq) : "memory");
+        }
+    }
+}
+// one value to column `col` (local numbering) of row `m` of every rank's buffer
+__device__ __forceinline__ void pg_peer_store(const PgPeerOut &o, int64_t m, int64_t col, float v)
+{
+    const int64_t at = m * o.ld + o.col0 + col;
+    for (int p = 0; p < o.world; p++) o.y[p][at] = v;
+}
+__device__ __forceinline__ void pg_peer_store4(const PgPeerOut &o, int64_t m, int64_t col, float4 v)   // 16-byte aligned
+{
+    const int64_t at = m * o.ld + o.col0 + col;
+    for (int p = 0; p < o.world; p++) *reinterpret_cast<float4 *>(o.y[p] + at) = v;
+}
+#endif
+
 int32_t pg_scratch_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pg_pinned_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pg_staging_reserve(pg_ctx *ctx, size_t bytes);
 int32_t pg_splitk_reserve(pg_ctx *ctx, size_t bytes);
 
+// Makes the context's device current for the duration of an entry point and restores the caller's afterwards.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev)
+    {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+    }
+    ~DeviceGuard()
+    {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+#define PG_ENTER(ctx)                                                   \
+    PG_REQUIRE((ctx) != nullptr, "null context");                       \
+    DeviceGuard _guard((ctx)->device);                                  \
+    if (!_guard.ok) PG_FAIL(PG_ERR_CUDA, "cudaSetDevice(%d) failed", (ctx)->device)
+
 // ------------------------------------------------------- kernel launchers ----
 // pg_quantize.cu
 int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales);
+int32_t pgk_quantize_activations_wait(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales,
+                                      const PgPeerWait *wait);
 int32_t pgk_quantize_weights(pg_ctx *ctx, const float *d_w, int64_t rows, int64_t cols, int8_t *d_q, int8_t *d_qt, float *d_scales);
 int32_t pgk_transpose_i8(pg_ctx *ctx, const int8_t *d_in, int64_t rows, int64_t cols, int8_t *d_out);
 // device -> device-visible memory by a kernel, 16-byte words (both pointers 16-byte aligned)
@@ -184,6 +340,9 @@ int32_t pgk_gemm_i8_stream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, in
 bool pgk_gemm_i8_wstream_supports(int64_t m, int64_t k, int64_t n);
 int32_t pgk_gemm_i8_wstream(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
                             const float *d_ws, int64_t n, float *d_y, int32_t *d_acc);
+// the same product with its outputs stored into every rank's exchange buffer and the exchange published by the kernel
+int32_t pgk_gemm_i8_wstream_peer(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int64_t m, int64_t k, const int8_t *d_bt,
+                                 const float *d_ws, int64_t n, const PgPeerOut &out);
 // pg_llama_attn.cu
 int pgk_gqa_stream_splits(const pg_ctx *ctx, int64_t B, int64_t Hkv, int64_t cap);
 bool pgk_gqa_stream_supports(int64_t G);

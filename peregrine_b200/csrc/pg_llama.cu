@@ -62,12 +62,13 @@ template <int VPT>
 __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict__ x, const float *__restrict__ delta,
                                                                 const float *__restrict__ w, int dim, float eps,
                                                                 int8_t *__restrict__ q, float *__restrict__ scales,
-                                                                float *__restrict__ normed)
+                                                                float *__restrict__ normed, const PgPeerWait wt)
 {
     __shared__ float red[32];
     __shared__ float xs[8], xm[8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    pg_peer_wait(wt, threadIdx.x);   // delta may be an exchange buffer that other GPUs fill
     const uint32_t cs = cl_size(), rank = cl_rank();
     const int64_t row = blockIdx.x / cs;
     const int nseg = (dim >> 2) / (int)cs;       // float4 per segment
@@ -161,12 +162,16 @@ __global__ void __launch_bounds__(LT) swiglu_quant_kernel(const float *__restric
 // grid (Hq + 2*Hkv, B), hd/2 threads.  qkv row = [Q heads | K heads | V heads].
 __global__ void rope_kv_append_kernel(const float *__restrict__ qkv, const int *__restrict__ pos_ptr, const float *__restrict__ cos_t,
                                       const float *__restrict__ sin_t, int Hq, int Hkv, int hd, int cap,
-                                      float *__restrict__ q_rot, float *__restrict__ kc, float *__restrict__ vc)
+                                      float *__restrict__ q_rot, float *__restrict__ kc, float *__restrict__ vc, int32_t *status)
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x, half = hd >> 1;
     const int pos = pg_ld_fresh(pos_ptr);
+    if ((unsigned)pos >= (unsigned)cap) {   // the cache and the rotation tables end at cap: record it, touch nothing
+        if (i == 0) atomicExch(status, (int32_t)PG_ERR_INVALID);
+        return;
+    }
     const float *src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + head) * hd;
     if (head < Hq + Hkv) {
         const float x0 = pg_ld_fresh(src + i), x1 = pg_ld_fresh(src + half + i);
@@ -193,7 +198,7 @@ template <int G>
 __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__restrict__ q, const float *__restrict__ kc,
                                                                   const float *__restrict__ vc, const int *__restrict__ pos_ptr, int Hq,
                                                                   int Hkv, int cap, int chunk, float scale, float *__restrict__ part_o,
-                                                                  float *__restrict__ part_ml)
+                                                                  float *__restrict__ part_ml, int32_t *status)
 {
     constexpr int HD = 128;
     extern __shared__ float sm[];  // sc[chunk][G], then red[8][G][HD]
@@ -203,7 +208,11 @@ __global__ void __launch_bounds__(256) gqa_decode_partial_kernel(const float *__
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int split = blockIdx.x, S = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int len = pg_ld_fresh(pos_ptr) + 1;
+    int len = pg_ld_fresh(pos_ptr) + 1;
+    if ((unsigned)(len - 1) >= (unsigned)cap) {   // position outside the cache: record it, read nothing (empty slices)
+        if (threadIdx.x == 0) atomicExch(status, (int32_t)PG_ERR_INVALID);
+        len = 0;
+    }
     const int t0 = split * chunk, t1 = min(len, t0 + chunk);
     const int n = t1 - t0;
     float *po = part_o + (((int64_t)b * Hq + kvh * G) * S + split) * HD;   // + h * S * HD
@@ -338,7 +347,11 @@ __global__ void embedding_kernel(const float *__restrict__ table, const int *__r
 
 // a cluster of cs CTAs per row, each scanning V / cs logits; the first maximum wins (examples/llama/main.rs:15-26).
 // The first CTA of row 0 also advances the position.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ tokens, int *pos_ptr)
+// PEER (po.world > 0): `logits` holds this rank's V columns of a vocabulary sharded by column; the row's local
+// (maximum, index + v0) pair goes to slot [b][rank] of every rank's exchange buffer instead of tokens[b], and
+// pick_embed_kernel chooses among the ranks' pairs.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int V, int *__restrict__ tokens, int *pos_ptr,
+                                                       int pos_limit, int v0, const PgPeerOut po)
 {
     __shared__ float bv[32];
     __shared__ int bi[32];
@@ -392,9 +405,79 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
                 best = xv[c];
                 idx = xi[c];
             }
-        tokens[b] = (idx == 0x7fffffff) ? 0 : idx;   // all-NaN row: the reference keeps index 0
-        if (b == 0 && pos_ptr) *pos_ptr = pg_ld_fresh(pos_ptr) + 1;
+        if (po.world > 0) {
+            // an all-NaN (or empty) slice never wins: -inf with the slice's first index
+            pg_peer_store(po, b, 0, (idx == 0x7fffffff) ? -INFINITY : best);
+            pg_peer_store(po, b, 1, __int_as_float((idx == 0x7fffffff) ? v0 : idx + v0));
+        } else {
+            tokens[b] = (idx == 0x7fffffff) ? 0 : idx;   // all-NaN row: the reference keeps index 0
+            if (b == 0 && pos_ptr) {
+                const int p = pg_ld_fresh(pos_ptr);
+                if (pos_limit <= 0 || p < pos_limit) *pos_ptr = p + 1;   // never past the end of the cache
+            }
+        }
     }
+    if (po.world > 0) pg_peer_publish(po, threadIdx.x);
+}
+
+// One CTA per sequence: waits for every rank's (maximum, index) pair of the sharded vocabulary, takes the first
+// maximum in index order (ranks own ascending column ranges, so rank order is index order; strict '>' as in
+// examples/llama/main.rs:15-26), stores the token, advances the position (CTA 0) and gathers the token's embedding
+// row (src/nn.rs:217-227) for the next step.  pairs: [B][world][2].
+__global__ void __launch_bounds__(256) pick_embed_kernel(const float *pairs, int world, int *__restrict__ tokens, int *pos_ptr, int pos_limit,
+                                                         const float *__restrict__ table, int dim, float *__restrict__ out,
+                                                         const PgPeerWait wt)
+{
+    __shared__ int s_tok;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pg_peer_wait(wt, threadIdx.x);
+    const int b = blockIdx.x;
+    if (threadIdx.x == 0) {
+        float best = -INFINITY;
+        int idx = 0;
+        bool any = false;
+        for (int r = 0; r < world; r++) {
+            const float v = pg_ld_fresh(pairs + ((int64_t)b * world + r) * 2);
+            const int i = __float_as_int(pg_ld_fresh(pairs + ((int64_t)b * world + r) * 2 + 1));
+            if (v > best) {
+                best = v;
+                idx = i;
+                any = true;
+            }
+        }
+        if (!any) idx = 0;   // every slice all-NaN or -inf: the reference's loop keeps index 0
+        tokens[b] = idx;
+        s_tok = idx;
+        if (b == 0 && pos_ptr) {
+            const int p = pg_ld_fresh(pos_ptr);
+            if (pos_limit <= 0 || p < pos_limit) *pos_ptr = p + 1;
+        }
+    }
+    __syncthreads();
+    if (table) {
+        const float4 *src = reinterpret_cast<const float4 *>(table + (int64_t)s_tok * dim);
+        float4 *dst = reinterpret_cast<float4 *>(out + (int64_t)b * dim);
+        for (int i = threadIdx.x; i < (dim >> 2); i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+}
+
+// silu(gate) * up on one rank's columns of a column-sharded [gate | up] product: gu [rows, 2 Fl] holds this rank's Fl
+// gate columns followed by its Fl up columns; the f32 results go to columns [col0, col0 + Fl) of every rank's [rows, F]
+// exchange buffer (the quantiser of the down projection needs the whole row, so it runs after the exchange).
+__global__ void __launch_bounds__(256) swiglu_peer_kernel(const float *__restrict__ gu, int rows, int Fl, const PgPeerOut po)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    auto silu_mul = [](float g, float u) { return __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u); };
+    const int nv = Fl >> 2;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)rows * nv; i += (int64_t)gridDim.x * 256) {
+        const int64_t row = i / nv, c = i - row * nv;
+        const float4 g = pg_ld_fresh(reinterpret_cast<const float4 *>(gu + row * 2 * Fl) + c);
+        const float4 u = pg_ld_fresh(reinterpret_cast<const float4 *>(gu + row * 2 * Fl + Fl) + c);
+        pg_peer_store4(po, row, c * 4, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
+    }
+    pg_peer_publish(po, threadIdx.x);
 }
 
 // Merge of the S partial attention outputs of every (sequence, query head), optionally followed by the per-row int8
@@ -402,7 +485,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
 // A cluster of cs CTAs per sequence, each with Hq / cs heads: blockDim = (128, Hq / cs).
 __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, int Hq,
                                                                   int S, float *__restrict__ out, int8_t *__restrict__ q8,
-                                                                  float *__restrict__ q8_scales)
+                                                                  float *__restrict__ q8_scales, const PgPeerOut peer)
 {
     constexpr int MAXS = 64;                      // slices per (sequence, KV head) never exceed this (checked on the host)
     __shared__ float red[32];
@@ -443,6 +526,12 @@ __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__
     const float o = (denom > 0.0f) ? __fdiv_rn(acc, denom) : 0.0f;
     const int64_t at = ((int64_t)b * Hq + qh) * 128 + d;
     if (out) out[at] = o;
+    if (peer.world > 0) {
+        // column-sharded heads: this rank's Hq heads are columns [col0, col0 + Hq * 128) of every rank's attention row
+        pg_peer_store(peer, b, (int64_t)qh * 128 + d, o);
+        pg_peer_publish(peer, threadIdx.y * 128 + threadIdx.x);
+        return;                                   // the quantiser needs the whole row: it runs after the exchange
+    }
     if (!q8) return;                              // uniform over the cluster: nobody waits at the barrier below
     float amax = fabsf(o);
 #pragma unroll
@@ -515,27 +604,61 @@ int32_t launch_pdl(pg_ctx *ctx, K kern, dim3 grid, dim3 block, size_t smem, Args
 
 }  // namespace
 
-extern "C" {
+static const PgPeerOut NO_PEER_OUT = {};
 
 // x [rows, dim] (updated in place to x + delta when delta != NULL) -> q [rows, dim] i8 + scales [rows] of
-// RMSNorm(x) * w; `normed` (nullable) receives the f32 normalised rows.
-PG_API int32_t pg_add_rmsnorm_quantize(pg_ctx *ctx, float *d_x, const float *d_delta, const float *d_w, int64_t rows, int64_t dim,
-                                       float eps, int8_t *d_q, float *d_scales, float *d_normed)
+// RMSNorm(x) * w; `normed` (nullable) receives the f32 normalised rows.  wait.ctl != NULL: delta is an exchange buffer.
+static int32_t add_rmsnorm_quantize(pg_ctx *ctx, float *d_x, const float *d_delta, const float *d_w, int64_t rows, int64_t dim, float eps,
+                                    int8_t *d_q, float *d_scales, float *d_normed, const PgPeerWait &wt)
 {
     PG_REQUIRE(ctx && d_x && d_w && d_q && d_scales, "add_rmsnorm_quantize: null pointer");
     PG_REQUIRE(rows >= 0 && dim > 0 && dim % 4 == 0 && dim <= LT * 4 * 16, "add_rmsnorm_quantize: dim must be a multiple of 4, at most %d", LT * 64);
     if (rows == 0) return PG_OK;
     const int cs = row_cluster(ctx, rows, dim / 4, 128);
     const dim3 g((unsigned)(rows * cs)), b(LT);
-    if (dim / cs <= LT * 4) return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<1>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
-    if (dim / cs <= LT * 16) return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<4>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
-    return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<16>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed);
+    if (dim / cs <= LT * 4) return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<1>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed, wt);
+    if (dim / cs <= LT * 16) return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<4>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed, wt);
+    return launch_pdl_cluster(ctx, add_rmsnorm_quant_kernel<16>, g, b, 0, cs, d_x, d_delta, d_w, (int)dim, eps, d_q, d_scales, d_normed, wt);
+}
+
+extern "C" {
+
+PG_API int32_t pg_add_rmsnorm_quantize(pg_ctx *ctx, float *d_x, const float *d_delta, const float *d_w, int64_t rows, int64_t dim,
+                                       float eps, int8_t *d_q, float *d_scales, float *d_normed)
+{
+    PG_ENTER(ctx);
+    PgPeerWait none = {};
+    return add_rmsnorm_quantize(ctx, d_x, d_delta, d_w, rows, dim, eps, d_q, d_scales, d_normed, none);
+}
+
+// The same with the residual delta taken from an exchange: the kernel waits (bounded) until every rank has delivered
+// its columns of the [rows, dim] result that `ex` gathers, then adds it to x.
+PG_API int32_t pg_add_rmsnorm_quantize_exchange(pg_ctx *ctx, float *d_x, pg_exchange *ex_delta, const float *d_w, int64_t rows,
+                                                int64_t dim, float eps, int8_t *d_q, float *d_scales, float *d_normed)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex_delta && ex_delta->connected, "add_rmsnorm_quantize_exchange: the exchange is not connected");
+    PG_REQUIRE((size_t)rows * (size_t)dim * sizeof(float) <= ex_delta->y_bytes, "add_rmsnorm_quantize_exchange: rows do not fit the exchange buffer");
+    return add_rmsnorm_quantize(ctx, d_x, ex_delta->y_local, d_w, rows, dim, eps, d_q, d_scales, d_normed, pg_peer_wait_of(ctx, ex_delta));
+}
+
+// quant::quantize_activations (src/quant.rs:97-109) on the [rows, cols] matrix an exchange gathers: waits (bounded) for
+// every rank's columns first.
+PG_API int32_t pg_quantize_activations_exchange(pg_ctx *ctx, pg_exchange *ex, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex && ex->connected && d_q && d_scales, "quantize_activations_exchange: null argument or unconnected exchange");
+    PG_REQUIRE(rows >= 0 && cols > 0 && (size_t)rows * (size_t)cols * sizeof(float) <= ex->y_bytes,
+               "quantize_activations_exchange: rows do not fit the exchange buffer");
+    const PgPeerWait wt = pg_peer_wait_of(ctx, ex);
+    return pgk_quantize_activations_wait(ctx, ex->y_local, rows, cols, d_q, d_scales, &wt);
 }
 
 // gate_up [rows, 2F] -> q [rows, F] i8 + scales [rows] of silu(gate) * up; `act` (nullable) receives the f32 rows.
 PG_API int32_t pg_swiglu_quantize(pg_ctx *ctx, const float *d_gate_up, int64_t rows, int64_t F, int8_t *d_q, float *d_scales, float *d_act)
 {
-    PG_REQUIRE(ctx && d_gate_up && d_q && d_scales, "swiglu_quantize: null pointer");
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_gate_up && d_q && d_scales, "swiglu_quantize: null pointer");
     PG_REQUIRE(rows >= 0 && F > 0 && F % 4 == 0 && F <= LT * 4 * 16, "swiglu_quantize: F must be a multiple of 4, at most %d", LT * 64);
     if (rows == 0) return PG_OK;
     const int cs = row_cluster(ctx, rows, F / 4, 128);
@@ -545,17 +668,37 @@ PG_API int32_t pg_swiglu_quantize(pg_ctx *ctx, const float *d_gate_up, int64_t r
     return launch_pdl_cluster(ctx, swiglu_quant_kernel<16>, g, b, 0, cs, d_gate_up, (int)F, d_q, d_scales, d_act);
 }
 
+// One rank's part of silu(gate) * up under column sharding: d_gate_up_local [rows, 2 Fl] = this rank's Fl gate columns,
+// then its Fl up columns (the same channel range of both halves).  The f32 results go to columns [col0, col0 + Fl) of
+// every rank's [rows, F_total] exchange buffer; pg_quantize_activations_exchange then quantises whole rows.
+PG_API int32_t pg_swiglu_exchange(pg_ctx *ctx, const float *d_gate_up_local, int64_t rows, int64_t F_local, pg_exchange *ex,
+                                  int64_t F_total, int64_t col0)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_gate_up_local && ex && ex->connected, "swiglu_exchange: null argument or unconnected exchange");
+    PG_REQUIRE(rows >= 0 && rows <= 0x7fffffff && F_local > 0 && F_local % 4 == 0 && F_total % 4 == 0 && col0 % 4 == 0 && col0 >= 0 &&
+                   col0 + F_local <= F_total,
+               "swiglu_exchange: column ranges must be multiples of 4 inside [0, F_total)");
+    PG_REQUIRE((size_t)rows * (size_t)F_total * sizeof(float) <= ex->y_bytes, "swiglu_exchange: rows do not fit the exchange buffer");
+    int64_t blocks = (rows * (F_local / 4) + 255) / 256;
+    blocks = blocks < 1 ? 1 : (blocks > 2 * (int64_t)ctx->sm_count ? 2 * (int64_t)ctx->sm_count : blocks);
+    return launch_pdl(ctx, swiglu_peer_kernel, dim3((unsigned)blocks), dim3(256), 0, d_gate_up_local, (int)rows, (int)F_local,
+                      pg_peer_out(ex, F_total, col0));
+}
+
 // qkv [B, (Hq + 2 Hkv) * hd] -> q_rot [B, Hq, hd]; k (rotated) and v written at position *d_pos of the caches
-// [B, Hkv, cap, hd].  cos/sin tables: [max_pos, hd/2].
+// [B, Hkv, cap, hd].  cos/sin tables: [max_pos, hd/2] with max_pos >= cap.  A position outside [0, cap) is not
+// written: the kernel records PG_ERR_INVALID in the context's status word instead.
 PG_API int32_t pg_rope_kv_append(pg_ctx *ctx, const float *d_qkv, const int32_t *d_pos, const float *d_cos, const float *d_sin,
                                  int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_q_rot, float *d_kcache,
                                  float *d_vcache)
 {
-    PG_REQUIRE(ctx && d_qkv && d_pos && d_cos && d_sin && d_q_rot && d_kcache && d_vcache, "rope_kv_append: null pointer");
-    PG_REQUIRE(hd % 2 == 0 && hd <= 2048 && B >= 0 && B <= 65535, "rope_kv_append: bad shape");
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_qkv && d_pos && d_cos && d_sin && d_q_rot && d_kcache && d_vcache, "rope_kv_append: null pointer");
+    PG_REQUIRE(hd % 2 == 0 && hd <= 2048 && B >= 0 && B <= 65535 && cap >= 0 && cap <= 0x7fffffff, "rope_kv_append: bad shape");
     if (B == 0) return PG_OK;
     return launch_pdl(ctx, rope_kv_append_kernel, dim3((unsigned)(Hq + 2 * Hkv), (unsigned)B), dim3((unsigned)(hd / 2)), 0, d_qkv, (const int *)d_pos,
-                      d_cos, d_sin, (int)Hq, (int)Hkv, (int)hd, (int)cap, d_q_rot, d_kcache, d_vcache);
+                      d_cos, d_sin, (int)Hq, (int)Hkv, (int)hd, (int)cap, d_q_rot, d_kcache, d_vcache, ctx->d_status);
 }
 
 // Attention of one new token per sequence over positions 0..*d_pos (the new one included).
@@ -566,19 +709,22 @@ PG_API int32_t pg_gqa_decode_splits(pg_ctx *ctx, int64_t B, int64_t Hq, int64_t 
     return cap <= 512 ? 1 : (cap <= 2048 ? 4 : 8);
 }
 
+// splits: 0 = pg_gqa_decode_splits' choice; peer: where the merged rows go when the heads are sharded over ranks
 static int32_t attention_decode(pg_ctx *ctx, const float *d_q_rot, float *d_kcache, float *d_vcache, const int32_t *d_pos,
                                 const float *d_cos, const float *d_sin, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
-                                float *d_work, float *d_out, int8_t *d_out_i8, float *d_out_scales)
+                                float *d_work, float *d_out, int8_t *d_out_i8, float *d_out_scales, int splits, const PgPeerOut *peer)
 {
     PG_REQUIRE(ctx && d_q_rot && d_kcache && d_vcache && d_pos && d_work, "gqa_attention_decode: null pointer");
-    PG_REQUIRE(d_out || d_out_i8, "gqa_attention_decode: no output");
+    PG_REQUIRE(d_out || d_out_i8 || peer, "gqa_attention_decode: no output");
     PG_REQUIRE((d_out_i8 == nullptr) == (d_out_scales == nullptr), "gqa_attention_decode: quantised output needs both buffers");
     PG_REQUIRE(hd == 128, "gqa_attention_decode: head_dim %lld is not supported (128 only)", (long long)hd);
     PG_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "gqa_attention_decode: Hkv must divide Hq");
+    PG_REQUIRE(cap > 0 && cap <= 0x7fffffff, "gqa_attention_decode: bad capacity");
     const int64_t G = Hq / Hkv;
     PG_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, "gqa_attention_decode: %lld query heads per KV head is not supported (1, 2, 4, 8)", (long long)G);
     if (B == 0) return PG_OK;
-    const int S = pg_gqa_decode_splits(ctx, B, Hq, Hkv, cap);
+    const int S = splits > 0 ? splits : pg_gqa_decode_splits(ctx, B, Hq, Hkv, cap);
+    PG_REQUIRE(S >= 1 && S <= 64, "gqa_attention_decode: %d slices per (sequence, KV head) (1..64)", S);
     const float scale = 1.0f / sqrtf((float)hd);
     float *part_o = d_work;
     float *part_ml = d_work + B * Hq * S * 128;
@@ -594,7 +740,7 @@ static int32_t attention_decode(pg_ctx *ctx, const float *d_q_rot, float *d_kcac
     {                                                                                                                           \
         if (smem > 48 * 1024) PG_CUDA(cudaFuncSetAttribute(gqa_decode_partial_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         rc = launch_pdl(ctx, gqa_decode_partial_kernel<GG>, grid, dim3(256), smem, d_q_rot, d_kcache, d_vcache, (const int *)d_pos, (int)Hq, \
-                        (int)Hkv, (int)cap, chunk, scale, part_o, part_ml);                                                     \
+                        (int)Hkv, (int)cap, chunk, scale, part_o, part_ml, ctx->d_status);                                      \
     }
         if (G == 1) PG_ATT(1) else PG_ATT(2)
 #undef PG_ATT
@@ -603,10 +749,12 @@ static int32_t attention_decode(pg_ctx *ctx, const float *d_q_rot, float *d_kcac
     // merge of the partials (+ the quantiser of the output projection's input): a cluster of CTAs per sequence
     int cs = 8;
     while (cs > 1 && (B * cs > 2 * (int64_t)ctx->sm_count || Hq % cs != 0)) cs >>= 1;
+    while (Hq / cs > 8 && cs < 8 && Hq % (cs * 2) == 0) cs <<= 1;   // at most 8 heads (1024 threads) per CTA
     const int64_t hpc = Hq / cs;
     if (hpc <= 8 && S <= 64)
         return launch_pdl_cluster(ctx, gqa_combine_quant_kernel, dim3((unsigned)(B * cs)), dim3(128, (unsigned)hpc), 0, cs, (const float *)part_o,
-                                  (const float *)part_ml, (int)Hq, S, d_out, d_out_i8, d_out_scales);
+                                  (const float *)part_ml, (int)Hq, S, d_out, d_out_i8, d_out_scales, peer ? *peer : NO_PEER_OUT);
+    PG_REQUIRE(!peer, "gqa_attention_decode: %lld heads per rank are too many for the sharded form", (long long)Hq);
     // many sequences with many heads: merge per head, quantise the rows afterwards
     float *merged = d_out;
     PG_REQUIRE(d_out != nullptr, "gqa_attention_decode: this shape needs the f32 output buffer as well");
@@ -616,14 +764,14 @@ static int32_t attention_decode(pg_ctx *ctx, const float *d_q_rot, float *d_kcac
     return pgk_quantize_activations(ctx, merged, B, Hq * 128, d_out_i8, d_out_scales);
 }
 
-
 PG_API int32_t pg_gqa_attention_decode(pg_ctx *ctx, const float *d_q_rot, const float *d_kcache, const float *d_vcache,
                                        const int32_t *d_pos, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap, float *d_work,
                                        float *d_out, int8_t *d_out_i8, float *d_out_scales)
 {
+    PG_ENTER(ctx);
     // the caches are only read on this path
     return attention_decode(ctx, d_q_rot, const_cast<float *>(d_kcache), const_cast<float *>(d_vcache), d_pos, nullptr, nullptr, B, Hq, Hkv, hd,
-                            cap, d_work, d_out, d_out_i8, d_out_scales);
+                            cap, d_work, d_out, d_out_i8, d_out_scales, 0, nullptr);
 }
 
 // pg_rope_kv_append + pg_gqa_attention_decode in one launch: d_qkv is the raw [B, (Hq + 2 Hkv) * hd] output of the fused
@@ -632,24 +780,82 @@ PG_API int32_t pg_gqa_attention_decode_fused(pg_ctx *ctx, const float *d_qkv, co
                                              float *d_kcache, float *d_vcache, int64_t B, int64_t Hq, int64_t Hkv, int64_t hd, int64_t cap,
                                              float *d_work, float *d_out, int8_t *d_out_i8, float *d_out_scales)
 {
+    PG_ENTER(ctx);
     PG_REQUIRE(d_cos && d_sin, "gqa_attention_decode_fused: null rotation tables");
-    return attention_decode(ctx, d_qkv, d_kcache, d_vcache, d_pos, d_cos, d_sin, B, Hq, Hkv, hd, cap, d_work, d_out, d_out_i8, d_out_scales);
+    return attention_decode(ctx, d_qkv, d_kcache, d_vcache, d_pos, d_cos, d_sin, B, Hq, Hkv, hd, cap, d_work, d_out, d_out_i8, d_out_scales, 0,
+                            nullptr);
+}
+
+// The fused form for heads sharded over ranks (whole KV heads with their query heads per rank): Hq and Hkv count THIS
+// rank's heads, d_qkv is its [B, (Hq + 2 Hkv) * hd] part of the projection, the caches hold its KV heads.  The merged f32
+// rows go to columns [col0, col0 + Hq * hd) of every rank's [B, n_total] exchange buffer (the output projection's
+// quantiser needs whole rows: pg_quantize_activations_exchange).  `splits` > 0 fixes the number of context slices per
+// (sequence, KV head) -- with the single-GPU value (pg_gqa_decode_splits of the unsharded shape) every partial sum is
+// formed in the same order as on one GPU and the rows come out bit-identical; 0 lets this rank's shape decide.
+// d_work: B * Hq * S * 130 floats for the S in effect.
+PG_API int32_t pg_gqa_attention_decode_fused_exchange(pg_ctx *ctx, const float *d_qkv, const int32_t *d_pos, const float *d_cos,
+                                                      const float *d_sin, float *d_kcache, float *d_vcache, int64_t B, int64_t Hq,
+                                                      int64_t Hkv, int64_t hd, int64_t cap, float *d_work, int32_t splits,
+                                                      pg_exchange *ex, int64_t n_total, int64_t col0)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_cos && d_sin, "gqa_attention_decode_fused_exchange: null rotation tables");
+    PG_REQUIRE(ex && ex->connected, "gqa_attention_decode_fused_exchange: the exchange is not connected");
+    PG_REQUIRE(col0 >= 0 && col0 + Hq * hd <= n_total && (size_t)B * (size_t)n_total * sizeof(float) <= ex->y_bytes,
+               "gqa_attention_decode_fused_exchange: columns outside the exchange buffer");
+    const PgPeerOut po = pg_peer_out(ex, n_total, col0);
+    return attention_decode(ctx, d_qkv, d_kcache, d_vcache, d_pos, d_cos, d_sin, B, Hq, Hkv, hd, cap, d_work, nullptr, nullptr, nullptr, splits,
+                            &po);
 }
 
 PG_API int32_t pg_embedding(pg_ctx *ctx, const float *d_table, const int32_t *d_tokens, int64_t B, int64_t dim, float *d_out)
 {
-    PG_REQUIRE(ctx && d_table && d_tokens && d_out && dim % 4 == 0, "embedding: bad arguments");
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_table && d_tokens && d_out && dim % 4 == 0, "embedding: bad arguments");
     if (B == 0) return PG_OK;
     return launch_pdl(ctx, embedding_kernel, dim3((unsigned)B), dim3(256), 0, d_table, (const int *)d_tokens, (int)dim, d_out);
 }
 
-// tokens[b] = argmax(logits[b, :]) (first maximum); d_pos (nullable) is advanced by one.
-PG_API int32_t pg_argmax_advance(pg_ctx *ctx, const float *d_logits, int64_t B, int64_t V, int32_t *d_tokens, int32_t *d_pos)
+// tokens[b] = argmax(logits[b, :]) (first maximum); d_pos (nullable) is advanced by one, but never beyond pos_limit
+// (pass the KV capacity; 0 = no limit): a decode loop that runs off the end of its cache stops advancing instead of
+// writing behind it.
+PG_API int32_t pg_argmax_advance(pg_ctx *ctx, const float *d_logits, int64_t B, int64_t V, int32_t *d_tokens, int32_t *d_pos, int64_t pos_limit)
 {
-    PG_REQUIRE(ctx && d_logits && d_tokens && V > 0, "argmax: bad arguments");
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_logits && d_tokens && V > 0 && V <= 0x7fffffff, "argmax: bad arguments");
     if (B == 0) return PG_OK;
     const int cs = row_cluster(ctx, B, V, 4096);
-    return launch_pdl_cluster(ctx, argmax_kernel, dim3((unsigned)(B * cs)), dim3(1024), 0, cs, d_logits, (int)V, (int *)d_tokens, (int *)d_pos);
+    return launch_pdl_cluster(ctx, argmax_kernel, dim3((unsigned)(B * cs)), dim3(1024), 0, cs, d_logits, (int)V, (int *)d_tokens, (int *)d_pos,
+                              (int)pos_limit, 0, NO_PEER_OUT);
+}
+
+// Greedy choice over a vocabulary sharded by column: this rank's [B, V_local] logits cover columns [v0, v0 + V_local).
+// Its per-sequence (maximum, index) pair (8 bytes) goes to every rank's exchange buffer ([B][world][2] floats, the
+// index as its bit pattern); pg_pick_embed then chooses.
+PG_API int32_t pg_argmax_exchange(pg_ctx *ctx, const float *d_logits_local, int64_t B, int64_t V_local, int64_t v0, pg_exchange *ex)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(d_logits_local && ex && ex->connected && V_local > 0 && V_local <= 0x7fffffff && v0 >= 0 && v0 + V_local <= 0x7fffffff,
+               "argmax_exchange: bad arguments");
+    PG_REQUIRE((size_t)B * ex->world * 2 * sizeof(float) <= ex->y_bytes, "argmax_exchange: the exchange buffer is smaller than [B][world][2] floats");
+    if (B == 0) return PG_OK;
+    const int cs = row_cluster(ctx, B, V_local, 4096);
+    return launch_pdl_cluster(ctx, argmax_kernel, dim3((unsigned)(B * cs)), dim3(1024), 0, cs, d_logits_local, (int)V_local, (int *)nullptr,
+                              (int *)nullptr, 0, (int)v0, pg_peer_out(ex, (int64_t)ex->world * 2, (int64_t)ex->rank * 2));
+}
+
+// Waits (bounded) for every rank's pair, stores tokens[b] = the first maximum over the whole vocabulary, advances
+// d_pos (nullable; never beyond pos_limit, 0 = no limit) and, when d_table is given, gathers the tokens' embedding rows
+// [B, dim] for the next step.
+PG_API int32_t pg_pick_embed(pg_ctx *ctx, pg_exchange *ex, int64_t B, int32_t *d_tokens, int32_t *d_pos, int64_t pos_limit,
+                             const float *d_table, int64_t dim, float *d_out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex && ex->connected && d_tokens, "pick_embed: null argument or unconnected exchange");
+    PG_REQUIRE(!d_table || (d_out && dim > 0 && dim % 4 == 0), "pick_embed: bad embedding arguments");
+    if (B == 0) return PG_OK;
+    return launch_pdl(ctx, pick_embed_kernel, dim3((unsigned)B), dim3(256), 0, (const float *)ex->y_local, ex->world, (int *)d_tokens, (int *)d_pos,
+                      (int)pos_limit, d_table, (int)dim, d_out, pg_peer_wait_of(ctx, ex));
 }
 
 }  // extern "C"

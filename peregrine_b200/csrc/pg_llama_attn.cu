@@ -39,7 +39,6 @@ constexpr int AT_WARPS = 12;
 constexpr int AT_THREADS = AT_WARPS * 32;
 constexpr int AT_SLOTS = 2;
 constexpr int AT_HD = 128;
-constexpr unsigned long long AT_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
 
 __device__ __forceinline__ unsigned long long at_globaltimer()
 {
@@ -67,7 +66,7 @@ __device__ __forceinline__ bool at_mbar_try(uint32_t bar, uint32_t parity)
         : "memory");
     return done != 0;
 }
-__device__ __forceinline__ bool at_mbar_wait(uint32_t bar, uint32_t parity, int32_t *status)
+__device__ __forceinline__ bool at_mbar_wait(uint32_t bar, uint32_t parity, int32_t *status, unsigned long long limit_ns)
 {
     unsigned long long t0 = 0;
     for (uint32_t it = 1;; ++it) {
@@ -76,7 +75,7 @@ __device__ __forceinline__ bool at_mbar_wait(uint32_t bar, uint32_t parity, int3
             const unsigned long long now = at_globaltimer();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > AT_WAIT_LIMIT_NS) {
+            } else if (now - t0 > limit_ns) {
                 atomicExch(status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
                 return false;
             }
@@ -129,7 +128,8 @@ template <int G, bool FUSED>
 __global__ void __launch_bounds__(AT_THREADS, 1)
     gqa_decode_stream_kernel(const float *__restrict__ q, float *__restrict__ kc, float *__restrict__ vc,
                              const int *__restrict__ pos_ptr, const float *__restrict__ cos_t, const float *__restrict__ sin_t, int B, int Hq,
-                             int Hkv, int cap, int S, float scale, float *__restrict__ part_o, float *__restrict__ part_ml, int32_t *status)
+                             int Hkv, int cap, int S, float scale, float *__restrict__ part_o, float *__restrict__ part_ml, int32_t *status,
+                             unsigned long long limit_ns)
 {
     constexpr int P = 32 / G;                 // positions per batch
     constexpr int SLOT = P * AT_HD * 4;       // bytes of K (or V) per batch
@@ -149,9 +149,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
     // the newest K/V row, q and the position come from the preceding kernels
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const int len = pg_ld_fresh(pos_ptr) + 1;
+    int len = pg_ld_fresh(pos_ptr) + 1;
+    if ((unsigned)(len - 1) >= (unsigned)cap) {
+        // the position lies outside the cache (and the rotation tables): record it and treat the context as empty, so
+        // that nothing is read or written past an allocation; every unit then reports an empty slice
+        if (threadIdx.x == 0) atomicExch(status, (int32_t)PG_ERR_INVALID);
+        len = 0;
+    }
     float4 rope_c = make_float4(1.f, 1.f, 1.f, 1.f), rope_s = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (FUSED) {       // the row of the cos / sin tables of the newest position, [max_pos, 64]
+    if (FUSED && len > 0) {       // the row of the cos / sin tables of the newest position, [max_pos, 64]
         rope_c = __ldg(reinterpret_cast<const float4 *>(cos_t + (int64_t)(len - 1) * (AT_HD / 2)) + (lane & 15));
         rope_s = __ldg(reinterpret_cast<const float4 *>(sin_t + (int64_t)(len - 1) * (AT_HD / 2)) + (lane & 15));
     }
@@ -219,7 +225,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 
         for (int bi = 0; bi < nb; bi++, fills++) {
             const uint32_t slot = fills % AT_SLOTS;
-            if (!at_mbar_wait(bars + slot * 8, (fills / AT_SLOTS) & 1u, status)) return;
+            if (!at_mbar_wait(bars + slot * 8, (fills / AT_SLOTS) & 1u, status, limit_ns)) return;
             const int valid = min(P, n - bi * P);
             if (appends && bi == nb - 1) {
                 // the bulk copy brought the cache's old bytes for the newest position: put the new row in its place
@@ -347,9 +353,10 @@ int32_t pgk_gqa_decode_stream(pg_ctx *ctx, const float *d_q, float *d_k, float *
 #define PG_AT_CASE(GG, FF)                                                                                                              \
     {                                                                                                                                   \
         cfg.dynamicSmemBytes = at_smem_bytes<GG>();                                                                                     \
-        PG_CUDA(cudaFuncSetAttribute(gqa_decode_stream_kernel<GG, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<GG>())); \
+        static std::atomic<uint64_t> smem_set{0};                                                                                       \
+        PG_CUDA(pg_max_smem_once(gqa_decode_stream_kernel<GG, FF>, at_smem_bytes<GG>(), ctx->device, smem_set));                        \
         PG_CUDA(cudaLaunchKernelEx(&cfg, gqa_decode_stream_kernel<GG, FF>, d_q, d_k, d_v, (const int *)d_pos, d_cos, d_sin, (int)B, (int)Hq, \
-                                   (int)Hkv, (int)cap, S, scale, part_o, part_ml, ctx->d_status));                                      \
+                                   (int)Hkv, (int)cap, S, scale, part_o, part_ml, ctx->d_status, ctx->wait_limit_ns));                  \
     }
     if (G == 4) {
         if (fused) PG_AT_CASE(4, true) else PG_AT_CASE(4, false)

@@ -8,14 +8,24 @@
 // peer pointers obtained through CUDA IPC), then raises one flag per destination; consumers wait on
 // their local flags.  No multimem, no TMA, no library kernel touches peer memory.
 //
-// Protocol, per exchange object (one per linear), all words in the symmetric block of each rank:
+// Two forms:
+//   * fused (pg_gemm_i8_exchange and the *_exchange glue entry points of pg_llama.cu): the producing kernel's own
+//     epilogue stores to the peers and its last CTA raises the flags; the consuming kernel (the next quantiser /
+//     RMSNorm of the step) spins on the flags at its top.  No extra launch per exchange.
+//   * separate (pg_exchange_store / pg_exchange_wait): a copy kernel and a one-warp wait kernel, for slices that
+//     some other kernel produced.
+//
+// Protocol, per exchange object, all words in the control block of each rank (pg_internal.cuh, PG_CTL_*):
 //   flag[src]   written remotely by rank `src`: the number of the last exchange it has delivered
-//   sent        local count of exchanges this rank has produced (bumped by the producer kernel)
-//   waited      local count of exchanges this rank has consumed (bumped by the wait kernel)
+//   sent        local count of exchanges this rank has produced (bumped by the producer's last CTA)
+//   waited      local count of exchanges this rank has consumed through pg_exchange_wait
 //   done        CTA counter of the producer kernel
-// Counting on the device (not in kernel arguments) keeps the kernels replayable from a graph.
-// The consumer's wait is bounded (about a second): on expiry it records PG_ERR_DEVICE_TIMEOUT in the
-// context's status word and returns, so a missing peer never hangs a GPU.
+// Counting on the device (not in kernel arguments) keeps the kernels replayable from a graph.  A fused consumer
+// waits for flag[src] >= sent: every rank enqueues the same sequence, so its own producer of the same exchange has
+// already run and counted.  An exchange object may be reused once every rank has consumed its previous result:
+// two other exchanges that all ranks take part in between two uses are enough (a layer has four).
+// Every wait is bounded (pg_ctx_set_wait_limit_ns, a second by default): on expiry the kernel records
+// PG_ERR_DEVICE_TIMEOUT in the context's status word and goes on, so a missing peer never hangs a GPU.
 #include <string.h>
 
 #include <new>
@@ -24,78 +34,48 @@
 
 namespace {
 
-constexpr int PG_MAX_PEERS = 8;
-constexpr unsigned long long PEER_WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;
-
-struct PeerDst {
-    float *y[PG_MAX_PEERS];          // [M, n_total] result buffer of each rank (own included)
-    uint32_t *ctl[PG_MAX_PEERS];     // control block of each rank: flag[8], sent, waited, done
-};
-
-__device__ __forceinline__ unsigned long long globaltimer_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 // grid-stride copy of the local slice [M, n_local] into column range [col0, col0 + n_local) of every
-// rank's [M, n_total]; the last CTA to finish publishes the exchange number to every rank.
-__global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *__restrict__ slice, int M, int64_t n_local,
-                                                                   int64_t n_total, int64_t col0, PeerDst dst, int world, int rank)
+// rank's [M, ld]; the last CTA to finish publishes the exchange number to every rank.
+__global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *slice, int M, int64_t n_local, const PgPeerOut dst, int vec)
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t total = (int64_t)M * n_local;
-    const bool vec = ((n_local | n_total | col0) & 3) == 0;
+    // the slice comes from the kernel before this one: read it through L2 (see pg_ld_fresh)
     if (vec) {
         const int64_t nv = total >> 2, rowv = n_local >> 2;
         for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nv; i += (int64_t)gridDim.x * 256) {
             const int64_t m = i / rowv, c = (i - m * rowv) << 2;
-            const float4 v = *reinterpret_cast<const float4 *>(slice + m * n_local + c);
-            for (int p = 0; p < world; p++) *reinterpret_cast<float4 *>(dst.y[p] + m * n_total + col0 + c) = v;
+            pg_peer_store4(dst, m, c, pg_ld_fresh(reinterpret_cast<const float4 *>(slice + m * n_local + c)));
         }
     } else {
         for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
             const int64_t m = i / n_local, c = i - m * n_local;
-            const float v = pg_ld_fresh(slice + i);
-            for (int p = 0; p < world; p++) dst.y[p][m * n_total + col0 + c] = v;
+            pg_peer_store(dst, m, c, pg_ld_fresh(slice + i));
         }
     }
-    // The CTA barrier orders every thread's peer stores before thread 0's system-scope fence, which
-    // (fences are cumulative) makes them visible to the other GPUs before the CTA is counted.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        uint32_t *ctl = dst.ctl[rank];
-        if (atomicAdd(&ctl[PG_MAX_PEERS + 2], 1u) == gridDim.x - 1) {
-            ctl[PG_MAX_PEERS + 2] = 0;
-            const uint32_t seq = ++ctl[PG_MAX_PEERS + 0];
-            __threadfence_system();
-            for (int p = 0; p < world; p++) {
-                uint32_t *f = dst.ctl[p] + rank;
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
-            }
-        }
-    }
+    pg_peer_publish(dst, threadIdx.x);
 }
 
 // one warp: lane r waits until rank r has delivered this rank's next exchange
-__global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t *ctl, int world, int32_t *status)
+__global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t *ctl, int world, int32_t *status, unsigned long long limit_ns)
 {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x;
     uint32_t want = 0;
-    if (lane == 0) want = ++ctl[PG_MAX_PEERS + 1];
+    if (lane == 0) {
+        want = __ldcg(ctl + PG_CTL_WAITED) + 1;
+        __stcg(ctl + PG_CTL_WAITED, want);
+    }
     want = __shfl_sync(0xffffffffu, want, 0);
     if (lane < world) {
-        const unsigned long long t0 = globaltimer_ns();
+        const unsigned long long t0 = pg_globaltimer_ns();
         for (uint32_t it = 0;; ++it) {
             uint32_t got;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(ctl + lane) : "memory");
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(ctl + PG_CTL_FLAG0 + lane) : "memory");
             if ((int32_t)(got - want) >= 0) break;
-            if ((it & 63) == 63 && globaltimer_ns() - t0 > PEER_WAIT_LIMIT_NS) {
+            if ((it & 63) == 63 && pg_globaltimer_ns() - t0 > limit_ns) {
                 atomicExch(status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
                 break;
             }
@@ -106,15 +86,29 @@ __global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t *ctl, int world,
 
 }  // namespace
 
-struct pg_exchange {
-    int world = 0, rank = 0;
-    float *y_local = nullptr;       // own [M_max, n_total] buffer (symmetric allocation)
-    uint32_t *ctl_local = nullptr;  // own control block (part of the same allocation)
-    void *base_local = nullptr;
-    size_t bytes = 0, y_bytes = 0;
-    void *peer_base[PG_MAX_PEERS] = {};
-    PeerDst dst = {};
-};
+PgPeerOut pg_peer_out(const pg_exchange *ex, int64_t ld, int64_t col0)
+{
+    PgPeerOut o = {};
+    for (int p = 0; p < ex->world; p++) {
+        o.y[p] = ex->y[p];
+        o.ctl[p] = ex->ctl[p];
+    }
+    o.world = ex->world;
+    o.rank = ex->rank;
+    o.ld = ld;
+    o.col0 = col0;
+    return o;
+}
+
+PgPeerWait pg_peer_wait_of(const pg_ctx *ctx, const pg_exchange *ex)
+{
+    PgPeerWait w = {};
+    w.ctl = ex ? ex->ctl_local : nullptr;
+    w.world = ex ? ex->world : 0;
+    w.status = ctx->d_status;
+    w.limit_ns = ctx->wait_limit_ns;
+    return w;
+}
 
 extern "C" {
 
@@ -123,23 +117,22 @@ extern "C" {
 // to pg_exchange_connect.
 PG_API int32_t pg_exchange_create(pg_ctx *ctx, int32_t rank, int32_t world, size_t y_bytes, void *handle_out, pg_exchange **out)
 {
-    PG_REQUIRE(ctx && out && handle_out, "exchange_create: null argument");
+    PG_ENTER(ctx);
+    PG_REQUIRE(out && handle_out, "exchange_create: null argument");
     *out = nullptr;
     PG_REQUIRE(world >= 1 && world <= PG_MAX_PEERS && rank >= 0 && rank < world, "exchange_create: rank %d / world %d (max %d)", rank, world,
                PG_MAX_PEERS);
-    int prev = -1;
-    cudaGetDevice(&prev);
-    if (prev != ctx->device) PG_CUDA(cudaSetDevice(ctx->device));
     pg_exchange *ex = new (std::nothrow) pg_exchange();
     if (!ex) PG_FAIL(PG_ERR_NOMEM, "out of host memory");
     ex->world = world;
     ex->rank = rank;
     ex->y_bytes = (y_bytes + 255) & ~(size_t)255;
-    ex->bytes = ex->y_bytes + 256;
+    ex->bytes = ex->y_bytes + PG_CTL_WORDS * sizeof(uint32_t);
     cudaError_t e = cudaMalloc(&ex->base_local, ex->bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->base_local, 0, ex->bytes);
     cudaIpcMemHandle_t h;
-    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ex->base_local);
+    memset(&h, 0, sizeof(h));
+    if (e == cudaSuccess && world > 1) e = cudaIpcGetMemHandle(&h, ex->base_local);
     if (e != cudaSuccess) {
         pg_set_error("exchange_create: %s", cudaGetErrorString(e));
         if (ex->base_local) cudaFree(ex->base_local);
@@ -156,10 +149,8 @@ PG_API int32_t pg_exchange_create(pg_ctx *ctx, int32_t rank, int32_t world, size
 // handles: world x 64 bytes in rank order (this rank's own entry is ignored).
 PG_API int32_t pg_exchange_connect(pg_ctx *ctx, pg_exchange *ex, const void *handles)
 {
-    PG_REQUIRE(ctx && ex && handles, "exchange_connect: null argument");
-    int prev = -1;
-    cudaGetDevice(&prev);
-    if (prev != ctx->device) PG_CUDA(cudaSetDevice(ctx->device));
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex && (handles || ex->world == 1), "exchange_connect: null argument");
     for (int p = 0; p < ex->world; p++) {
         void *base = ex->base_local;
         if (p != ex->rank) {
@@ -168,9 +159,25 @@ PG_API int32_t pg_exchange_connect(pg_ctx *ctx, pg_exchange *ex, const void *han
             PG_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
             ex->peer_base[p] = base;
         }
-        ex->dst.y[p] = reinterpret_cast<float *>(base);
-        ex->dst.ctl[p] = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(base) + ex->y_bytes);
+        ex->y[p] = reinterpret_cast<float *>(base);
+        ex->ctl[p] = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(base) + ex->y_bytes);
     }
+    ex->connected = true;
+    return PG_OK;
+}
+
+// Ranks inside one process: the peers' blocks are ordinary device pointers of this process.
+PG_API int32_t pg_exchange_connect_local(pg_ctx *ctx, pg_exchange *ex, pg_exchange *const *all)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex && all, "exchange_connect_local: null argument");
+    for (int p = 0; p < ex->world; p++) {
+        PG_REQUIRE(all[p] && all[p]->world == ex->world && all[p]->rank == p && all[p]->y_bytes == ex->y_bytes,
+                   "exchange_connect_local: entry %d is not rank %d of the same exchange", p, p);
+        ex->y[p] = all[p]->y_local;
+        ex->ctl[p] = all[p]->ctl_local;
+    }
+    ex->connected = true;
     return PG_OK;
 }
 
@@ -181,14 +188,18 @@ PG_API float *pg_exchange_result(const pg_exchange *ex) { return ex ? ex->y_loca
 PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local, int64_t n_total,
                                  int64_t col0)
 {
-    PG_REQUIRE(ctx && ex, "exchange_store: null argument");
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex != nullptr, "exchange_store: null argument");
     PG_REQUIRE(m >= 0 && n_local >= 0 && col0 >= 0 && col0 + n_local <= n_total, "exchange_store: bad column range");
     PG_REQUIRE((size_t)m * (size_t)n_total * sizeof(float) <= ex->y_bytes, "exchange_store: result does not fit the exchange buffer");
-    PG_REQUIRE(ex->dst.y[ex->world - 1] != nullptr, "exchange_store: pg_exchange_connect has not been called");
+    PG_REQUIRE(ex->connected, "exchange_store: pg_exchange_connect has not been called");
+    PG_REQUIRE(m * n_local == 0 || d_slice, "exchange_store: slice is null");
     const int64_t total = m * n_local;
     int64_t blocks = (total / 4 + 255) / 256;
     if (blocks < 1) blocks = 1;
     if (blocks > 2 * (int64_t)ctx->sm_count) blocks = 2 * (int64_t)ctx->sm_count;
+    // 16-byte accesses only where every row segment starts on a 16-byte boundary on both sides
+    const int vec = ((n_local | n_total | col0) & 3) == 0 && ((uintptr_t)d_slice & 15) == 0;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -198,7 +209,7 @@ PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_sl
     cfg.stream = ctx->stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    PG_CUDA(cudaLaunchKernelEx(&cfg, peer_allgather_store_kernel, d_slice, (int)m, n_local, n_total, col0, ex->dst, ex->world, ex->rank));
+    PG_CUDA(cudaLaunchKernelEx(&cfg, peer_allgather_store_kernel, d_slice, (int)m, n_local, pg_peer_out(ex, n_total, col0), vec));
     PG_LAUNCHED();
     return PG_OK;
 }
@@ -207,7 +218,8 @@ PG_API int32_t pg_exchange_store(pg_ctx *ctx, pg_exchange *ex, const float *d_sl
 // exchange on `ex`.  One wait per store, in the same order on every rank.
 PG_API int32_t pg_exchange_wait(pg_ctx *ctx, pg_exchange *ex)
 {
-    PG_REQUIRE(ctx && ex, "exchange_wait: null argument");
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex != nullptr, "exchange_wait: null argument");
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -217,7 +229,7 @@ PG_API int32_t pg_exchange_wait(pg_ctx *ctx, pg_exchange *ex)
     wc.stream = ctx->stream;
     wc.attrs = attr;
     wc.numAttrs = 1;
-    PG_CUDA(cudaLaunchKernelEx(&wc, peer_wait_kernel, ex->ctl_local, ex->world, ctx->d_status));
+    PG_CUDA(cudaLaunchKernelEx(&wc, peer_wait_kernel, ex->ctl_local, ex->world, ctx->d_status, ctx->wait_limit_ns));
     PG_LAUNCHED();
     return PG_OK;
 }
@@ -231,10 +243,36 @@ PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *
     return pg_exchange_wait(ctx, ex);
 }
 
+// One rank's part of a column-sharded integer GEMM with the all-gather inside it: the product of a_i8 [M, K] with
+// this rank's columns `w` ([K, n_local]) lands in columns [col0, col0 + n_local) of EVERY rank's [M, n_total] exchange
+// buffer and the exchange is published.  At decode sizes (M <= 16, K % 64 == 0) the product kernel's own epilogue does
+// the peer stores; other shapes run the ordinary product into `d_slice_tmp` ([M, n_local] floats of the caller's)
+// followed by the copy kernel.  Consumers wait with pg_exchange_wait or one of the *_exchange glue entry points.
+PG_API int32_t pg_gemm_i8_exchange(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k, const pg_qtensor *w,
+                                   pg_exchange *ex, int64_t n_total, int64_t col0, float *d_slice_tmp)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(w && ex, "gemm_i8_exchange: null argument");
+    PG_REQUIRE(ex->connected, "gemm_i8_exchange: pg_exchange_connect has not been called");
+    PG_REQUIRE(m >= 0 && k >= 0 && w->rows == k, "gemm_i8_exchange: w.rows (%lld) != k (%lld)", (long long)w->rows, (long long)k);
+    const int64_t n = w->cols;
+    PG_REQUIRE(col0 >= 0 && col0 + n <= n_total, "gemm_i8_exchange: columns [%lld, %lld) outside [0, %lld)", (long long)col0,
+               (long long)(col0 + n), (long long)n_total);
+    PG_REQUIRE((size_t)m * (size_t)n_total * sizeof(float) <= ex->y_bytes, "gemm_i8_exchange: result does not fit the exchange buffer");
+    PG_REQUIRE(m * k == 0 || (d_a_i8 && d_a_scales), "gemm_i8_exchange: activations are null");
+    const bool aligned = (((uintptr_t)d_a_i8 | (uintptr_t)w->d_data_i8_t) & 15) == 0;
+    if (m > 0 && n > 0 && aligned && pgk_gemm_i8_wstream_supports(m, k, n))
+        return pgk_gemm_i8_wstream_peer(ctx, d_a_i8, d_a_scales, m, k, w->d_data_i8_t, w->d_scales, n, pg_peer_out(ex, n_total, col0));
+    PG_REQUIRE(m * n == 0 || d_slice_tmp, "gemm_i8_exchange: this shape needs the slice buffer");
+    const int32_t rc = pg_gemm_i8(ctx, d_a_i8, d_a_scales, m, k, w, d_slice_tmp, nullptr, PG_ALGO_AUTO);
+    if (rc != PG_OK) return rc;
+    return pg_exchange_store(ctx, ex, d_slice_tmp, m, n, n_total, col0);
+}
+
 PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex)
 {
     if (!ex) return PG_OK;
-    PG_REQUIRE(ctx != nullptr, "null context");
+    PG_ENTER(ctx);
     cudaStreamSynchronize(ctx->stream);
     for (int p = 0; p < ex->world; p++)
         if (ex->peer_base[p]) cudaIpcCloseMemHandle(ex->peer_base[p]);

@@ -36,7 +36,8 @@ __device__ __forceinline__ float block_max(float v, float *smem)
 // Columns of a segment past THREADS*VPT*4 are re-read in the second pass.
 template <int VPT>
 __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *__restrict__ x, int64_t cols,
-                                                                    int8_t *__restrict__ q, float *__restrict__ scales)
+                                                                    int8_t *__restrict__ q, float *__restrict__ scales,
+                                                                    const PgPeerWait wt)
 {
     __shared__ float red[32];
     __shared__ float xm[8];
@@ -44,6 +45,7 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
     // independent prologue (the product kernel prefetches weights)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    pg_peer_wait(wt, threadIdx.x);                // x is an exchange buffer that other GPUs fill: wait for their flags
     const uint32_t cs = cl_size(), rank = cl_rank();
     const int64_t row = blockIdx.x / cs;
     const int64_t nvec = (cols >> 2) / cs;        // float4 per segment (the host picks cs so that this is exact)
@@ -179,9 +181,19 @@ __global__ void __launch_bounds__(256) matmul_f32_kernel(const float *__restrict
 
 int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales)
 {
+    return pgk_quantize_activations_wait(ctx, d_x, rows, cols, d_q, d_scales, nullptr);
+}
+
+// wait != nullptr: d_x is this rank's exchange buffer; the kernel first waits (bounded) for every rank's flags
+int32_t pgk_quantize_activations_wait(pg_ctx *ctx, const float *d_x, int64_t rows, int64_t cols, int8_t *d_q, float *d_scales,
+                                      const PgPeerWait *wait)
+{
     if (rows == 0) return PG_OK;
     PG_REQUIRE(rows <= 0x7fffffff, "quantize_activations: rows=%lld exceeds the grid limit", (long long)rows);
     const bool vec = (cols % 4 == 0) && (((uintptr_t)d_x & 15) == 0) && (((uintptr_t)d_q & 3) == 0);
+    PG_REQUIRE(!wait || (vec && cols > 0), "quantize_activations: rows taken from an exchange need cols %% 4 == 0 and aligned buffers");
+    PgPeerWait wt = {};
+    if (wait) wt = *wait;
     if (cols == 0) {
         // scale of an empty row is 1.0 (amax == 0)
         quantize_rows_scalar_kernel<<<(unsigned)rows, QR_THREADS, 0, ctx->stream>>>(d_x, 0, d_q, d_scales);
@@ -209,11 +221,11 @@ int32_t pgk_quantize_activations(pg_ctx *ctx, const float *d_x, int64_t rows, in
         cfg.numAttrs = cs > 1 ? 2 : 1;
         const int64_t seg = cols / cs;
         if (seg <= 4 * QR_THREADS)
-            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<1>, d_x, cols, d_q, d_scales));
+            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<1>, d_x, cols, d_q, d_scales, wt));
         else if (seg <= 4 * QR_THREADS * 4)
-            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<4>, d_x, cols, d_q, d_scales));
+            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<4>, d_x, cols, d_q, d_scales, wt));
         else
-            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<16>, d_x, cols, d_q, d_scales));
+            PG_CUDA(cudaLaunchKernelEx(&cfg, quantize_rows_kernel<16>, d_x, cols, d_q, d_scales, wt));
     }
     PG_LAUNCHED();
     return PG_OK;

@@ -130,12 +130,26 @@ class ColumnShardedLinear:
         return unshard_columns(parts, self.columns, self.n)
 
 
-class PeerExchange:
-    """All-gather of output slices by direct stores into the other GPUs' result buffers
-    (`pg_exchange_*`): no library collective in the step, so a whole sharded step can be recorded
-    into one CUDA graph.  Handles are swapped once through `torch.distributed` (any backend)."""
+class Exchange:
+    """One rank's end of an all-gather by direct stores into the other GPUs' result buffers (`pg_exchange_*`): a
+    buffer of `y_bytes` that every rank writes its part of, plus the flags that say whose part has arrived.  No
+    library collective runs in a step, so a whole sharded step can be recorded into one CUDA graph.  The 64-byte
+    handles are swapped once through `torch.distributed` (any backend); ranks that live in one process use
+    `connect_local`."""
 
-    def __init__(self, gpu, rank: int, world: int, m_max: int, n_total: int, group=None):
+    def __init__(self, gpu, rank: int, world: int, y_bytes: int):
+        import ctypes as C
+
+        from . import _lib
+
+        self.gpu, self.rank, self.world, self.y_bytes = gpu, rank, world, int(y_bytes)
+        self._ipc = (C.c_ubyte * 64)()
+        h = C.c_void_p()
+        _lib.check(gpu.lib.pg_exchange_create(gpu.handle, rank, world, self.y_bytes, self._ipc, C.byref(h)))
+        self.handle = h
+        self.result_ptr = gpu.lib.pg_exchange_result(h)
+
+    def connect(self, group=None) -> None:
         import ctypes as C
 
         import torch
@@ -143,24 +157,64 @@ class PeerExchange:
 
         from . import _lib
 
-        self.gpu, self.rank, self.world, self.n_total = gpu, rank, world, n_total
-        handle = (C.c_ubyte * 64)()
-        h = C.c_void_p()
-        _lib.check(gpu.lib.pg_exchange_create(gpu.handle, rank, world, m_max * n_total * 4, handle, C.byref(h)))
-        self.handle = h
-        mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8)
-        if world > 1:
-            dev = torch.device("cuda", gpu.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
-            allh = torch.empty(world * 64, dtype=torch.uint8, device=dev)
+        if self.world > 1:
+            mine = torch.tensor(list(bytes(self._ipc)), dtype=torch.uint8)
+            dev = torch.device("cuda", self.gpu.device) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+            allh = torch.empty(self.world * 64, dtype=torch.uint8, device=dev)
             dist.all_gather_into_tensor(allh, mine.to(dev), group=group)
             blob = bytes(allh.cpu().numpy().tobytes())
         else:
-            blob = bytes(handle)
+            blob = bytes(self._ipc)
         buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
-        _lib.check(gpu.lib.pg_exchange_connect(gpu.handle, h, buf))
-        if world > 1:
+        _lib.check(self.gpu.lib.pg_exchange_connect(self.gpu.handle, self.handle, buf))
+        if self.world > 1:
             dist.barrier(group=group)   # nobody stores into a peer before that peer exists
-        self.result_ptr = gpu.lib.pg_exchange_result(h)
+
+    @staticmethod
+    def connect_local(ranks: Sequence["Exchange"]) -> None:
+        """All ranks of the exchange live in this process: no IPC, the peers' buffers are plain device pointers."""
+        import ctypes as C
+
+        from . import _lib
+
+        arr = (C.c_void_p * len(ranks))(*[e.handle for e in ranks])
+        for e in ranks:
+            _lib.check(e.gpu.lib.pg_exchange_connect_local(e.gpu.handle, e.handle, arr))
+
+    def store(self, d_slice, m: int, n_local: int, n_total: int, col0: int) -> None:
+        """Hand this rank's [m, n_local] slice to every rank (columns col0.. of their [m, n_total]); do not wait."""
+        from . import _lib
+        from .runtime import _ptr
+
+        _lib.check(self.gpu.lib.pg_exchange_store(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, n_total, col0))
+
+    def wait(self) -> None:
+        """Bounded wait for every rank's slice of the oldest store not yet waited for."""
+        from . import _lib
+
+        _lib.check(self.gpu.lib.pg_exchange_wait(self.gpu.handle, self.handle))
+
+    def read(self, count: int, dtype=np.float32) -> np.ndarray:
+        from . import _lib
+        from .runtime import _ptr
+
+        out = np.empty(count, dtype)
+        _lib.check(self.gpu.lib.pg_mem_download(self.gpu.handle, _ptr(out), self.result_ptr, out.nbytes))
+        return out
+
+    def destroy(self) -> None:
+        if self.handle is not None and self.gpu.handle:
+            self.gpu.lib.pg_exchange_destroy(self.gpu.handle, self.handle)
+        self.handle = None
+
+
+class PeerExchange(Exchange):
+    """An `Exchange` sized for one [m_max, n_total] f32 result, connected on construction."""
+
+    def __init__(self, gpu, rank: int, world: int, m_max: int, n_total: int, group=None):
+        super().__init__(gpu, rank, world, m_max * n_total * 4)
+        self.n_total = n_total
+        self.connect(group)
 
     def allgather(self, d_slice, m: int, n_local: int, col0: int) -> None:
         """Enqueue on the context's stream; afterwards `result_ptr` holds the full [m, n_total] matrix."""
@@ -169,28 +223,8 @@ class PeerExchange:
 
         _lib.check(self.gpu.lib.pg_exchange_allgather(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, self.n_total, col0))
 
-    def store(self, d_slice, m: int, n_local: int, col0: int) -> None:
-        """The first half of `allgather`: hand this rank's slice to every rank, do not wait."""
-        from . import _lib
-        from .runtime import _ptr
-
-        _lib.check(self.gpu.lib.pg_exchange_store(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, self.n_total, col0))
-
-    def wait(self) -> None:
-        """The second half: bounded wait for every rank's slice of the oldest store not yet waited for."""
-        from . import _lib
-
-        _lib.check(self.gpu.lib.pg_exchange_wait(self.gpu.handle, self.handle))
+    def store(self, d_slice, m: int, n_local: int, col0: int) -> None:   # noqa: D401 (the fixed-width form)
+        Exchange.store(self, d_slice, m, n_local, self.n_total, col0)
 
     def read(self, m: int) -> np.ndarray:
-        from . import _lib
-        from .runtime import _ptr
-
-        out = np.empty((m, self.n_total), np.float32)
-        _lib.check(self.gpu.lib.pg_mem_download(self.gpu.handle, _ptr(out), self.result_ptr, out.nbytes))
-        return out
-
-    def destroy(self) -> None:
-        if self.handle is not None and self.gpu.handle:
-            self.gpu.lib.pg_exchange_destroy(self.gpu.handle, self.handle)
-        self.handle = None
+        return Exchange.read(self, m * self.n_total).reshape(m, self.n_total)

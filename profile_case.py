@@ -1,12 +1,12 @@
 """Runs one case of one kernel a few times, for profiling under `ncu` or quick timing.
 
-    python -m peregrine_b200.profile_case --op w8a8 --algo stream --m 16 --k 4096 --n 32768 --reps 3
-    python -m peregrine_b200.profile_case --op w8a8 --algo tcgen05 --m 2048 --k 4096 --n 4096
-    python -m peregrine_b200.profile_case --op gguf --kind q4_0 --m 1 --k 4096 --n 32768
-    python -m peregrine_b200.profile_case --op quant --m 8192 --k 4096
-    python -m peregrine_b200.profile_case --op llama --layers 2 --m 16 --context 2048 --reps 2
-    python -m peregrine_b200.profile_case --op huffman --k 4096 --n 14336 --streams 4 --reps 3
-    python -m peregrine_b200.profile_case --op host --reps 1500
+    python profile_case.py --op w8a8 --algo stream --m 16 --k 4096 --n 32768 --reps 3
+    python profile_case.py --op w8a8 --algo tcgen05 --m 2048 --k 4096 --n 4096
+    python profile_case.py --op gguf --kind q4_0 --m 1 --k 4096 --n 32768
+    python profile_case.py --op quant --m 8192 --k 4096
+    python profile_case.py --op llama --layers 2 --m 16 --context 2048 --reps 2
+    python profile_case.py --op huffman --k 4096 --n 14336 --streams 4 --reps 3
+    python profile_case.py --op host --reps 1500
 
 Inputs are seeded random values generated on the host; weights for `w8a8` are random int8 (no
 quantisation pass), so start-up stays short.  Prints the mean time per call in microseconds
@@ -20,9 +20,14 @@ import time
 
 import numpy as np
 
-from . import _lib
-from .gguf import BLOCK_BYTES, TYPE_BY_NAME, GgufWeight
-from .runtime import GpuContext
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from peregrine_b200 import _lib  # noqa: E402
+from peregrine_b200.gguf import BLOCK_BYTES, TYPE_BY_NAME, GgufWeight  # noqa: E402
+from peregrine_b200.runtime import GpuContext  # noqa: E402
 
 ALGOS = {"auto": _lib.ALGO_AUTO, "naive": _lib.ALGO_NAIVE, "stream": _lib.ALGO_STREAM, "tcgen05": _lib.ALGO_TCGEN05, "wstream": _lib.ALGO_WSTREAM}
 
@@ -31,7 +36,7 @@ def llama_case(a) -> None:
     """Eager decode steps (one launch per kernel, batch = --m) of a Llama-3-8B-shaped stack cut to --layers layers."""
     import torch
 
-    from .llama import LlamaConfig, LlamaInt8Decoder
+    from peregrine_b200.llama import LlamaConfig, LlamaInt8Decoder
 
     dev = torch.device("cuda", 0)
     cfg = LlamaConfig(layers=a.layers, batch=a.m, capacity=a.context + 64)
@@ -73,9 +78,9 @@ def huffman_case(a) -> None:
     """Loads a Huffman-coded [k, n] int8 weight (N(0, 0.02) quantised per column, --sparsity of it zeroed first) with
     pg_qtensor_from_huffman, beside the plain upload of the decoded bytes (pg_qtensor_from_i8).  Host clock around
     the whole call: upload from pageable memory, decode, transposition."""
-    from . import quant
-    from .huffman import HuffmanTensor, _stream_tables
-    from .runtime import _ptr
+    from peregrine_b200 import quant
+    from peregrine_b200.huffman import HuffmanTensor, _stream_tables
+    from peregrine_b200.runtime import _ptr
 
     gpu = GpuContext(0)
     g = np.random.Generator(np.random.PCG64(1))

@@ -9,8 +9,8 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _header_symbols():
-    text = open(os.path.join(ROOT, "include", "peregrine_b200.h")).read()
+def _header_symbols(name="peregrine_b200.h"):
+    text = open(os.path.join(ROOT, "include", name)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"PG_API\s+[\w\s\*]+?\b(pg_\w+)\s*\(", text)))
 
@@ -35,6 +35,16 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     # and the ctypes table covers every declaration
     assert sorted(_lib.SIGNATURES) == declared
+    # the tuning knobs have a header of their own; nothing named pg_* is exported without a declaration in one of the two
+    knobs = _header_symbols("peregrine_b200_tune.h")
+    assert sorted(_lib.TUNE_SIGNATURES) == knobs
+    for name in knobs:
+        assert hasattr(lib, name), f"{name} is declared in the tuning header but not exported"
+    import subprocess
+
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = sorted({line.split()[-1] for line in out.splitlines() if line.split() and line.split()[-1].startswith("pg_")})
+    assert exported == sorted(declared + knobs), sorted(set(exported) ^ set(declared + knobs))
 
 
 def test_errors_are_reported_not_thrown():

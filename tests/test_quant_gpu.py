@@ -347,10 +347,11 @@ def test_unaligned_k_uses_the_checker_kernel(pg, gpu, oracle):
         assert bits_equal(pg.quant.matmul_quantized(x, m, k, qt, gpu), out_o)
 
 
-def test_prefill_m512(pg, gpu, oracle_mt):
-    """Prefill config M=512, K=4096, N=4096: full i32 and f32 comparison with the CPU oracle."""
-    x, w = linear_inputs(512, 4096, 4096, 2000)
-    _check_product(pg, gpu, oracle_mt, x, w, 512, 4096, 4096, ["tcgen05"])
+@pytest.mark.parametrize("idx,n", [(0, 4096), (1, 14336)])
+def test_prefill_m512(pg, gpu, oracle_mt, idx, n):
+    """Prefill configs M=512, K=4096, N in {4096, 14336}: full i32 and f32 comparison with the CPU oracle."""
+    x, w = linear_inputs(512, 4096, n, 2000 + idx)
+    _check_product(pg, gpu, oracle_mt, x, w, 512, 4096, n, ["tcgen05"])
 
 
 @pytest.mark.parametrize("idx,m,n", [(2, 2048, 4096), (3, 2048, 14336), (4, 8192, 4096), (5, 8192, 14336)])
