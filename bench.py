@@ -218,6 +218,10 @@ def run_ours(args):
     stream = torch.cuda.Stream(device=dev)
     gpu = pg.GpuContext(local, stream.cuda_stream)
     lib = gpu.lib
+    if world > 1:
+        # a flag that another rank raises arrives within microseconds; a rank that waits a tenth of a second for one has lost
+        # its peer, and the run should end with the status word set rather than wait a second per kernel
+        _lib.check(lib.pg_ctx_set_wait_limit_ns(gpu.handle, 100_000_000))
     warmup = max(args.warmup, 3)
     # N > 1: "shard" splits every weight matrix by output column over the ranks and all-gathers the slices (strong
     # scaling of one sweep); "replicas" gives every rank the whole matrices and its own copy of the sweep, with no
@@ -279,10 +283,11 @@ def run_ours(args):
             else:
                 _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
         if peer:
-            # the nine products of the sweep are independent, so the (bounded) waits for the other ranks'
-            # slices come after the last product: the step ends when every rank holds all nine full results
-            for ex in exs:
-                ex.wait()
+            # the nine products of the sweep are independent, so the consumers (bounded waits for the other ranks' cells,
+            # results written out as plain [M, N] matrices) come after the last product: the step ends when every rank
+            # holds all nine full results
+            for ci, (mi, si) in enumerate(CASES):
+                exs[ci].gather(MS[mi], SHAPES[si][1])
 
     def step_eager():
         if peer:
@@ -299,6 +304,9 @@ def run_ours(args):
         step_eager()
     stream.synchronize()
     launches_per_step = int(lib.pg_launch_count() - n0)
+    st = gpu.device_status()
+    if st != 0:
+        raise SystemExit(f"rank {rank}: device status {st} after the first step (a bounded wait ran out): not measuring")
 
     # One submission per step at N = 1 (the library's own graph recorder).  With NCCL in the step the
     # launches stay eager: replaying a captured step that contained the all-gathers did not complete
@@ -365,7 +373,7 @@ def run_ours(args):
                     _lib.check(lib.pg_quantize_activations(gpu.handle, xs[ci].data_ptr(), MS[mi], k, qs[ci].data_ptr(), qss[ci].data_ptr()))
                     _lib.check(lib.pg_gemm_i8_exchange(gpu.handle, qs[ci].data_ptr(), qss[ci].data_ptr(), MS[mi], k, h, exs[ci].handle, n,
                                                        shard[si][0], ys[ci].data_ptr()))
-                    exs[ci].wait()
+                    exs[ci].gather(MS[mi], n)
                     _lib.check(lib.pg_mem_download(gpu.handle, ys_host[ci].data_ptr(), exs[ci].result_ptr, MS[mi] * n * 4))
                 else:
                     dist.all_gather_into_tensor(ys_full[ci], ys[ci])
@@ -730,6 +738,13 @@ def llama_decode_measurement(gpu, torch, stream, dev, hbm_peak, steps=128, warmu
         for _ in range(warmup):
             graph.launch()
         stream.synchronize()
+        st = gpu.device_status()
+        if st != 0:
+            raise SystemExit(f"rank {rank}: device status {st} in the warm-up steps of the decode stack (a bounded wait ran out): not measuring")
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
         model.set_position(ctx0)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

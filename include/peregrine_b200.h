@@ -267,15 +267,21 @@ PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex);
 PG_API int32_t pg_exchange_connect_local(pg_ctx *ctx, pg_exchange *ex, pg_exchange *const *all);
 /* The column-sharded integer GEMM with its all-gather inside: this rank's columns `w` ([K, n_local]) of the product
  * land in columns [col0, col0 + n_local) of EVERY rank's [M, n_total] exchange buffer, stored by the product kernel's
- * own epilogue (M <= 16, K % 64 == 0; plain stores over NVLink, all loads local), whose last CTA publishes the
- * exchange.  Other shapes run pg_gemm_i8 into d_slice_tmp ([M, n_local] floats, may be NULL for decode shapes) followed
- * by pg_exchange_store.  Wait with pg_exchange_wait or a consumer below.  Integer sums and the per-column epilogue
- * make the gathered matrix bit-identical to the unsharded product. */
+ * own epilogue (M <= 16, K % 64 == 0; plain stores over NVLink, all loads local).  Other shapes run pg_gemm_i8 into
+ * d_slice_tmp ([M, n_local] floats, may be NULL for decode shapes) followed by a copy kernel.  Integer sums and the
+ * per-column epilogue make the gathered matrix bit-identical to the unsharded product.  The exchange buffer holds
+ * y_bytes / 4 values (pg_exchange_create). */
 PG_API int32_t pg_gemm_i8_exchange(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k,
                                    const pg_qtensor *w, pg_exchange *ex, int64_t n_total, int64_t col0, float *d_slice_tmp);
-/* Consumers that begin with the (bounded) wait for every rank's flags, so an exchange costs no launch of its own:
- * the quantiser of src/quant.rs:97-109 over the gathered [rows, cols] matrix, and pg_add_rmsnorm_quantize with the
- * gathered matrix as the residual delta. */
+/* The slices travel as flagged cells (8 bytes per value: the value and the number of the exchange), which lets a
+ * consumer poll the very cells it reads: no fence, no flag, no launch per exchange.  Consumers (enqueue them behind this
+ * rank's own producer on the same exchange; their waits are bounded): pg_exchange_gather, which writes the gathered
+ * [rows, cols] matrix as plain floats to d_out (NULL: to pg_exchange_result); the quantiser of src/quant.rs:97-109 over
+ * the gathered matrix; pg_add_rmsnorm_quantize with the gathered matrix as the residual delta. */
+PG_API int32_t pg_exchange_gather(pg_ctx *ctx, pg_exchange *ex, int64_t rows, int64_t cols, float *d_out);
+/* the producer of such an exchange for a slice that lies in plain device memory (any kernel's output) */
+PG_API int32_t pg_exchange_store_cells(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local,
+                                       int64_t n_total, int64_t col0);
 PG_API int32_t pg_quantize_activations_exchange(pg_ctx *ctx, pg_exchange *ex, int64_t rows, int64_t cols, int8_t *d_q,
                                                 float *d_scales);
 PG_API int32_t pg_add_rmsnorm_quantize_exchange(pg_ctx *ctx, float *d_x, pg_exchange *ex_delta, const float *d_w, int64_t rows,

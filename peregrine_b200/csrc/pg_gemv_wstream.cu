@@ -128,9 +128,10 @@ __device__ __forceinline__ uint32_t ws_mapa(uint32_t local_addr, uint32_t cta)
 // CTA b (unit u = b / cs; U = number of clusters or CTAs): tiles  u + U * (slot + (16 / kw) * j).
 // Shared memory: activations (a_bytes, row stride a_stride) | rings | mbarriers | CL: exchange cells [2][16 / kw][512 B].
 // PEER: the kernel is one rank's part of a column-sharded product.  Its outputs go straight into every rank's [M, ld]
-// result buffer (plain stores to peer pointers over NVLink, columns col0 + n) and the kernel itself publishes the
-// exchange when its last CTA is done: no separate all-gather launch.  Only stores cross NVLink; every load, bulk
-// copies included, reads this GPU's own memory.
+// buffer of flagged cells (pg_internal.cuh: 8 bytes per value, the value with the number of the exchange, plain stores
+// to peer pointers over NVLink, columns col0 + n): no separate all-gather launch, no fence, and the consumers need no
+// flag beyond the cells themselves.  Only stores cross NVLink; every load, bulk copies included, reads this GPU's own
+// memory.
 template <bool HI, int SEG, bool CL, bool PEER>
 __global__ void __launch_bounds__(WS_THREADS, 1)
     gemv_wstream_kernel(const int8_t *__restrict__ a, const float *__restrict__ a_scales, int M, int K, const int8_t *__restrict__ bt,
@@ -219,6 +220,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     // load each, here, instead of one per output)
     const float as_lo = (r < M) ? pg_ld_fresh(a_scales + r) : 0.0f;
     const float as_hi = (HI && r + 8 < M) ? pg_ld_fresh(a_scales + r + 8) : 0.0f;
+    const uint32_t peer_seq = PEER ? pg_cell_seq(po) : 0u;   // after griddepcontrol.wait
     int acc[4] = {0, 0, 0, 0};
     int q = 0;
     // Rounds of the CTA: in round j a warp streams its part of its j-th tile, if it has one.  Warps without a tile in
@@ -291,18 +293,15 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
                 const int m = r + 8 * h;
                 if (m < M) {
                     if (PEER) {
-                        // two adjacent columns per lane: one 8-byte store per rank where the pair exists and is aligned
+                        // two adjacent columns per lane: one 16-byte store of two cells per rank where the pair exists and is aligned
                         const float as = h ? as_hi : as_lo;
                         const float v0 = (n < N) ? __fmul_rn(__fmul_rn(__int2float_rn(acc[2 * h]), as), __ldg(w_scales + n)) : 0.0f;
                         const float v1 = (n + 1 < N) ? __fmul_rn(__fmul_rn(__int2float_rn(acc[2 * h + 1]), as), __ldg(w_scales + n + 1)) : 0.0f;
-                        const int64_t at = (int64_t)m * po.ld + po.col0 + n;
                         if (n + 1 < N && ((po.ld | po.col0) & 1) == 0) {
-                            for (int p = 0; p < po.world; p++) *reinterpret_cast<float2 *>(po.y[p] + at) = make_float2(v0, v1);
+                            pg_cell_store2(po, peer_seq, m, n, v0, v1);
                         } else {
-                            if (n < N)
-                                for (int p = 0; p < po.world; p++) po.y[p][at] = v0;
-                            if (n + 1 < N)
-                                for (int p = 0; p < po.world; p++) po.y[p][at + 1] = v1;
+                            if (n < N) pg_cell_store(po, peer_seq, m, n, v0);
+                            if (n + 1 < N) pg_cell_store(po, peer_seq, m, n + 1, v1);
                         }
                     } else {
 #pragma unroll
@@ -319,7 +318,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         }
         acc[0] = acc[1] = acc[2] = acc[3] = 0;
     }
-    if (PEER) pg_peer_publish(po, threadIdx.x);
+    if (PEER) pg_cell_finish(po, peer_seq, threadIdx.x);
 }
 
 int g_force_kw = 0;    // tuning override, 0 = heuristic

@@ -192,21 +192,34 @@ struct pg_gguf_weight {
 };
 
 // ---- exchange between the GPUs of a node (csrc/pg_peer.cu) ----------------------------------------------------
-// One symmetric block per rank: a result buffer followed by control words.  Producers store their slice of a result
-// into EVERY rank's buffer with plain stores (peer pointers from CUDA IPC) and then raise flag[producer rank] in every
-// rank's control block to the number of the exchange; consumers spin, bounded, on the flags of their OWN block.
+// One symmetric block per rank: a plain result buffer, a buffer of flagged cells and control words.
+//
+// Flagged cells (the form the step kernels use): every f32 of the gathered matrix travels as an 8-byte cell
+// {value bits, number of the exchange}, written by the producing kernel's epilogue into EVERY rank's cell buffer with
+// one plain 8-byte store per cell (two cells per 16-byte store where aligned).  An 8-byte store arrives whole, so a
+// consumer that reads a cell and finds the number it expects has the value: no fence, no separate flag, no counter
+// crosses NVLink, and an exchange costs one store latency.  Consumers poll the cells they need (bounded).
+// The number of an exchange is kept on the device (PG_CTL_SENT, bumped by the producer's last CTA with a local atomic
+// counter), so the kernels replay from a graph; every rank enqueues the same sequence, so a consumer finds its own
+// producer's count in PG_CTL_SENT and waits for cells of exactly that number.
+//
+// Separate flags (pg_exchange_store / pg_exchange_wait, for slices some other kernel produced): plain floats into
+// every rank's result buffer, a system-scope fence, then flag[producer] raised on every rank; consumers spin, bounded,
+// on the flags of their own block.
 constexpr int PG_MAX_PEERS = 8;
-enum { PG_CTL_FLAG0 = 0, PG_CTL_SENT = 8, PG_CTL_WAITED = 9, PG_CTL_DONE = 10, PG_CTL_WORDS = 64 };
+enum { PG_CTL_FLAG0 = 0, PG_CTL_SENT = 8, PG_CTL_WAITED = 9, PG_CTL_DONE = 10, PG_CTL_CELL_SENT = 11, PG_CTL_CELL_DONE = 12, PG_CTL_WORDS = 64 };
 
 // what a producing kernel gets (by value, in its arguments)
 struct PgPeerOut {
-    float *y[PG_MAX_PEERS];          // result buffer of each rank (own included)
+    float *y[PG_MAX_PEERS];          // plain result buffer of each rank (own included)
+    uint2 *cells[PG_MAX_PEERS];      // cell buffer of each rank
     uint32_t *ctl[PG_MAX_PEERS];     // control block of each rank
     int32_t world, rank;
     int64_t ld, col0;                // row stride of the result (total columns) and this rank's first column
 };
-// what a consuming kernel gets: its own control block; ctl == nullptr means "nothing to wait for"
+// what a consuming kernel gets: its own cell buffer and control block; cells == nullptr means "nothing to wait for"
 struct PgPeerWait {
+    const uint2 *cells;
     const uint32_t *ctl;
     int32_t world;
     int32_t *status;
@@ -215,12 +228,14 @@ struct PgPeerWait {
 
 struct pg_exchange {
     int world = 0, rank = 0;
-    float *y_local = nullptr;       // own result buffer (start of the symmetric block)
-    uint32_t *ctl_local = nullptr;  // own control block (behind the result buffer)
+    float *y_local = nullptr;       // own plain result buffer (start of the symmetric block)
+    uint2 *cells_local = nullptr;   // own cell buffer (behind it)
+    uint32_t *ctl_local = nullptr;  // own control block (behind that)
     void *base_local = nullptr;
     size_t bytes = 0, y_bytes = 0;
     void *peer_base[PG_MAX_PEERS] = {};
     float *y[PG_MAX_PEERS] = {};
+    uint2 *cells[PG_MAX_PEERS] = {};
     uint32_t *ctl[PG_MAX_PEERS] = {};
     bool connected = false;
 };
@@ -234,31 +249,88 @@ __device__ __forceinline__ unsigned long long pg_globaltimer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Consumer side, called by every thread of the CTA (tid = linear thread index) after griddepcontrol.wait: threads
-// 0..world-1 wait until rank `tid` has delivered the exchange this rank's own producer kernel (earlier in the stream)
-// counted last.  Bounded: on expiry PG_ERR_DEVICE_TIMEOUT goes to the status word and the kernel carries on with
-// whatever the buffer holds.  Data behind the flags must be read through L2 (pg_ld_fresh / bulk copies).
-__device__ __forceinline__ void pg_peer_wait(const PgPeerWait &w, int tid)
+
+// ---- flagged cells: producer side ----
+// number of the exchange this kernel produces (read once per thread that stores, after griddepcontrol.wait)
+__device__ __forceinline__ uint32_t pg_cell_seq(const PgPeerOut &o) { return __ldcg(o.ctl[o.rank] + PG_CTL_CELL_SENT) + 1; }
+// one value to column `col` (local numbering) of row `m` of every rank
+__device__ __forceinline__ void pg_cell_store(const PgPeerOut &o, uint32_t seq, int64_t m, int64_t col, float v)
 {
-    if (w.ctl == nullptr) return;
-    if (tid < w.world) {
-        const uint32_t want = __ldcg(w.ctl + PG_CTL_SENT);
-        const unsigned long long t0 = pg_globaltimer_ns();
-        for (uint32_t it = 0;; ++it) {
-            uint32_t got;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(w.ctl + PG_CTL_FLAG0 + tid) : "memory");
-            if ((int32_t)(got - want) >= 0) break;
-            if ((it & 63) == 63 && pg_globaltimer_ns() - t0 > w.limit_ns) {
-                atomicExch(w.status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
-                break;
-            }
+    const int64_t at = m * o.ld + o.col0 + col;
+    for (int p = 0; p < o.world; p++)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(o.cells[p] + at), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+// two adjacent columns in one 16-byte store (each half carries its own number); the cell index must be even
+__device__ __forceinline__ void pg_cell_store2(const PgPeerOut &o, uint32_t seq, int64_t m, int64_t col, float v0, float v1)
+{
+    const int64_t at = m * o.ld + o.col0 + col;
+    for (int p = 0; p < o.world; p++)
+        asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(o.cells[p] + at), "r"(__float_as_uint(v0)), "r"(seq),
+                     "r"(__float_as_uint(v1))
+                     : "memory");
+}
+// Called once by every thread of EVERY CTA of the producing grid after its last cell store: the last CTA to be counted
+// (a local counter, nothing crosses NVLink) records the number for this rank's consumers.
+__device__ __forceinline__ void pg_cell_finish(const PgPeerOut &o, uint32_t seq, int tid)
+{
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t *ctl = o.ctl[o.rank];
+        const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+        __threadfence();
+        if (atomicAdd(&ctl[PG_CTL_CELL_DONE], 1u) == ctas - 1) {
+            ctl[PG_CTL_CELL_DONE] = 0;
+            __stcg(ctl + PG_CTL_CELL_SENT, seq);
         }
     }
-    __syncthreads();
 }
-// Producer side, called once by every thread of EVERY CTA of the grid after its last store into the peers' buffers.
-// The CTA barrier orders the CTA's stores before thread 0's system-scope fence (fences are cumulative); the last CTA
-// to be counted numbers the exchange and raises this rank's flag on every rank.
+
+// ---- flagged cells: consumer side ----
+// the number this rank's consumers wait for: its own producer's last exchange (the producer ran earlier in the stream)
+__device__ __forceinline__ uint32_t pg_cell_want(const PgPeerWait &w) { return __ldcg(w.ctl + PG_CTL_CELL_SENT); }
+__device__ __forceinline__ bool pg_cell_fresh(uint32_t got, uint32_t want) { return (int32_t)(got - want) >= 0; }
+// gives up after limit_ns: PG_ERR_DEVICE_TIMEOUT goes to the status word and the caller carries on with what it has
+__device__ __forceinline__ bool pg_cell_expired(unsigned long long &t0, uint32_t it, const PgPeerWait &w)
+{
+    if ((it & 63) != 63) return false;
+    const unsigned long long now = pg_globaltimer_ns();
+    if (t0 == 0) {
+        t0 = now;
+        return false;
+    }
+    if (now - t0 <= w.limit_ns) return false;
+    atomicExch(w.status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
+    return true;
+}
+// four consecutive values starting at cell `at` (a multiple of 2: 16-byte aligned)
+__device__ __forceinline__ float4 pg_cell_load4(const PgPeerWait &w, uint32_t want, int64_t at)
+{
+    unsigned long long t0 = 0;
+    uint4 a, b;
+    for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(w.cells + at) : "memory");
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(w.cells + at + 2) : "memory");
+        if (pg_cell_fresh(a.y, want) && pg_cell_fresh(a.w, want) && pg_cell_fresh(b.y, want) && pg_cell_fresh(b.w, want)) break;
+        if (pg_cell_expired(t0, it, w)) break;
+    }
+    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+__device__ __forceinline__ float pg_cell_load(const PgPeerWait &w, uint32_t want, int64_t at)
+{
+    unsigned long long t0 = 0;
+    uint2 a;
+    for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(a.x), "=r"(a.y) : "l"(w.cells + at) : "memory");
+        if (pg_cell_fresh(a.y, want)) break;
+        if (pg_cell_expired(t0, it, w)) break;
+    }
+    return __uint_as_float(a.x);
+}
+
+// ---- separate flags ----
+// Producer side, called once by every thread of EVERY CTA of the grid after its last plain store into the peers'
+// buffers.  The CTA barrier orders the CTA's stores before thread 0's system-scope fence (fences are cumulative); the
+// last CTA to be counted numbers the exchange and raises this rank's flag on every rank.
 __device__ __forceinline__ void pg_peer_publish(const PgPeerOut &o, int tid)
 {
     __syncthreads();
@@ -276,7 +348,7 @@ __device__ __forceinline__ void pg_peer_publish(const PgPeerOut &o, int tid)
         }
     }
 }
-// one value to column `col` (local numbering) of row `m` of every rank's buffer
+// one value to column `col` (local numbering) of row `m` of every rank's plain buffer
 __device__ __forceinline__ void pg_peer_store(const PgPeerOut &o, int64_t m, int64_t col, float v)
 {
     const int64_t at = m * o.ld + o.col0 + col;

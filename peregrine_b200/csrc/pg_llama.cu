@@ -68,7 +68,9 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
     __shared__ float xs[8], xm[8];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    pg_peer_wait(wt, threadIdx.x);   // delta may be an exchange buffer that other GPUs fill
+    // wt.cells != nullptr: delta is an exchange's buffer of flagged cells that all GPUs fill (bounded wait per load)
+    const bool dcells = wt.cells != nullptr;
+    const uint32_t want = dcells ? pg_cell_want(wt) : 0u;
     const uint32_t cs = cl_size(), rank = cl_rank();
     const int64_t row = blockIdx.x / cs;
     const int nseg = (dim >> 2) / (int)cs;       // float4 per segment
@@ -82,8 +84,9 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c < nseg) {
             v[i] = pg_ld_fresh(xr + c0 + c);
-            if (delta) {
-                const float4 d = pg_ld_fresh(reinterpret_cast<const float4 *>(delta + row * dim) + c0 + c);
+            if (delta || dcells) {
+                const float4 d = dcells ? pg_cell_load4(wt, want, row * dim + (int64_t)(c0 + c) * 4)
+                                        : pg_ld_fresh(reinterpret_cast<const float4 *>(delta + row * dim) + c0 + c);
                 v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
                 xr[c0 + c] = v[i];
             }
@@ -407,8 +410,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
             }
         if (po.world > 0) {
             // an all-NaN (or empty) slice never wins: -inf with the slice's first index
-            pg_peer_store(po, b, 0, (idx == 0x7fffffff) ? -INFINITY : best);
-            pg_peer_store(po, b, 1, __int_as_float((idx == 0x7fffffff) ? v0 : idx + v0));
+            pg_cell_store2(po, pg_cell_seq(po), b, 0, (idx == 0x7fffffff) ? -INFINITY : best,
+                           __int_as_float((idx == 0x7fffffff) ? v0 : idx + v0));
         } else {
             tokens[b] = (idx == 0x7fffffff) ? 0 : idx;   // all-NaN row: the reference keeps index 0
             if (b == 0 && pos_ptr) {
@@ -417,29 +420,29 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
             }
         }
     }
-    if (po.world > 0) pg_peer_publish(po, threadIdx.x);
+    if (po.world > 0) pg_cell_finish(po, pg_cell_seq(po), threadIdx.x);
 }
 
 // One CTA per sequence: waits for every rank's (maximum, index) pair of the sharded vocabulary, takes the first
 // maximum in index order (ranks own ascending column ranges, so rank order is index order; strict '>' as in
 // examples/llama/main.rs:15-26), stores the token, advances the position (CTA 0) and gathers the token's embedding
 // row (src/nn.rs:217-227) for the next step.  pairs: [B][world][2].
-__global__ void __launch_bounds__(256) pick_embed_kernel(const float *pairs, int world, int *__restrict__ tokens, int *pos_ptr, int pos_limit,
+__global__ void __launch_bounds__(256) pick_embed_kernel(int world, int *__restrict__ tokens, int *pos_ptr, int pos_limit,
                                                          const float *__restrict__ table, int dim, float *__restrict__ out,
                                                          const PgPeerWait wt)
 {
     __shared__ int s_tok;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    pg_peer_wait(wt, threadIdx.x);
     const int b = blockIdx.x;
     if (threadIdx.x == 0) {
+        const uint32_t want = pg_cell_want(wt);
         float best = -INFINITY;
         int idx = 0;
         bool any = false;
         for (int r = 0; r < world; r++) {
-            const float v = pg_ld_fresh(pairs + ((int64_t)b * world + r) * 2);
-            const int i = __float_as_int(pg_ld_fresh(pairs + ((int64_t)b * world + r) * 2 + 1));
+            const float v = pg_cell_load(wt, want, ((int64_t)b * world + r) * 2);
+            const int i = __float_as_int(pg_cell_load(wt, want, ((int64_t)b * world + r) * 2 + 1));
             if (v > best) {
                 best = v;
                 idx = i;
@@ -471,13 +474,15 @@ __global__ void __launch_bounds__(256) swiglu_peer_kernel(const float *__restric
     asm volatile("griddepcontrol.wait;" ::: "memory");
     auto silu_mul = [](float g, float u) { return __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u); };
     const int nv = Fl >> 2;
+    const uint32_t seq = pg_cell_seq(po);
     for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)rows * nv; i += (int64_t)gridDim.x * 256) {
         const int64_t row = i / nv, c = i - row * nv;
         const float4 g = pg_ld_fresh(reinterpret_cast<const float4 *>(gu + row * 2 * Fl) + c);
         const float4 u = pg_ld_fresh(reinterpret_cast<const float4 *>(gu + row * 2 * Fl + Fl) + c);
-        pg_peer_store4(po, row, c * 4, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)));
+        pg_cell_store2(po, seq, row, c * 4, silu_mul(g.x, u.x), silu_mul(g.y, u.y));
+        pg_cell_store2(po, seq, row, c * 4 + 2, silu_mul(g.z, u.z), silu_mul(g.w, u.w));
     }
-    pg_peer_publish(po, threadIdx.x);
+    pg_cell_finish(po, seq, threadIdx.x);
 }
 
 // Merge of the S partial attention outputs of every (sequence, query head), optionally followed by the per-row int8
@@ -528,8 +533,9 @@ __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__
     if (out) out[at] = o;
     if (peer.world > 0) {
         // column-sharded heads: this rank's Hq heads are columns [col0, col0 + Hq * 128) of every rank's attention row
-        pg_peer_store(peer, b, (int64_t)qh * 128 + d, o);
-        pg_peer_publish(peer, threadIdx.y * 128 + threadIdx.x);
+        const uint32_t seq = pg_cell_seq(peer);
+        pg_cell_store(peer, seq, b, (int64_t)qh * 128 + d, o);
+        pg_cell_finish(peer, seq, threadIdx.y * 128 + threadIdx.x);
         return;                                   // the quantiser needs the whole row: it runs after the exchange
     }
     if (!q8) return;                              // uniform over the cluster: nobody waits at the barrier below
@@ -639,7 +645,7 @@ PG_API int32_t pg_add_rmsnorm_quantize_exchange(pg_ctx *ctx, float *d_x, pg_exch
     PG_ENTER(ctx);
     PG_REQUIRE(ex_delta && ex_delta->connected, "add_rmsnorm_quantize_exchange: the exchange is not connected");
     PG_REQUIRE((size_t)rows * (size_t)dim * sizeof(float) <= ex_delta->y_bytes, "add_rmsnorm_quantize_exchange: rows do not fit the exchange buffer");
-    return add_rmsnorm_quantize(ctx, d_x, ex_delta->y_local, d_w, rows, dim, eps, d_q, d_scales, d_normed, pg_peer_wait_of(ctx, ex_delta));
+    return add_rmsnorm_quantize(ctx, d_x, nullptr, d_w, rows, dim, eps, d_q, d_scales, d_normed, pg_peer_wait_of(ctx, ex_delta));
 }
 
 // quant::quantize_activations (src/quant.rs:97-109) on the [rows, cols] matrix an exchange gathers: waits (bounded) for
@@ -651,7 +657,7 @@ PG_API int32_t pg_quantize_activations_exchange(pg_ctx *ctx, pg_exchange *ex, in
     PG_REQUIRE(rows >= 0 && cols > 0 && (size_t)rows * (size_t)cols * sizeof(float) <= ex->y_bytes,
                "quantize_activations_exchange: rows do not fit the exchange buffer");
     const PgPeerWait wt = pg_peer_wait_of(ctx, ex);
-    return pgk_quantize_activations_wait(ctx, ex->y_local, rows, cols, d_q, d_scales, &wt);
+    return pgk_quantize_activations_wait(ctx, reinterpret_cast<const float *>(ex->cells_local), rows, cols, d_q, d_scales, &wt);
 }
 
 // gate_up [rows, 2F] -> q [rows, F] i8 + scales [rows] of silu(gate) * up; `act` (nullable) receives the f32 rows.
@@ -854,7 +860,7 @@ PG_API int32_t pg_pick_embed(pg_ctx *ctx, pg_exchange *ex, int64_t B, int32_t *d
     PG_REQUIRE(ex && ex->connected && d_tokens, "pick_embed: null argument or unconnected exchange");
     PG_REQUIRE(!d_table || (d_out && dim > 0 && dim % 4 == 0), "pick_embed: bad embedding arguments");
     if (B == 0) return PG_OK;
-    return launch_pdl(ctx, pick_embed_kernel, dim3((unsigned)B), dim3(256), 0, (const float *)ex->y_local, ex->world, (int *)d_tokens, (int *)d_pos,
+    return launch_pdl(ctx, pick_embed_kernel, dim3((unsigned)B), dim3(256), 0, ex->world, (int *)d_tokens, (int *)d_pos,
                       (int)pos_limit, d_table, (int)dim, d_out, pg_peer_wait_of(ctx, ex));
 }
 

@@ -4,28 +4,22 @@
 // all of Y.  (API precedent in the reference: Communicator::allgather, src/comm/communicator.rs:162-191,
 // a CPU shared-memory ring.)  At decode sizes the slices are 16 KB - 1 MB, where a library collective
 // costs mostly launch latency and cannot be recorded into this library's step graph.  Here each rank
-// instead writes its slice straight into every rank's [M, N] result buffer (plain st.global to
-// peer pointers obtained through CUDA IPC), then raises one flag per destination; consumers wait on
-// their local flags.  No multimem, no TMA, no library kernel touches peer memory.
+// instead writes its slice straight into every rank's buffer (plain stores to peer pointers obtained
+// through CUDA IPC).  No multimem, no TMA, no library kernel touches peer memory; only stores cross NVLink.
 //
-// Two forms:
-//   * fused (pg_gemm_i8_exchange and the *_exchange glue entry points of pg_llama.cu): the producing kernel's own
-//     epilogue stores to the peers and its last CTA raises the flags; the consuming kernel (the next quantiser /
-//     RMSNorm of the step) spins on the flags at its top.  No extra launch per exchange.
-//   * separate (pg_exchange_store / pg_exchange_wait): a copy kernel and a one-warp wait kernel, for slices that
-//     some other kernel produced.
+// Two forms (the protocols are described with the structures in pg_internal.cuh):
+//   * flagged cells (pg_gemm_i8_exchange and the *_exchange glue entry points of pg_llama.cu): the producing
+//     kernel's own epilogue stores {value, number of the exchange} cells into every rank; the consuming kernel (the
+//     next quantiser / RMSNorm of the step, or pg_exchange_gather) polls the cells it reads.  No extra launch, no
+//     fence and no flag per exchange: one store latency.  (With a system-scope fence, a flag per rank and an
+//     acquire-poll the same exchange took 12-15 us on two B200s, as much as the product it followed.)
+//   * separate flags (pg_exchange_store / pg_exchange_wait): a copy kernel and a one-warp wait kernel, for slices
+//     that some other kernel produced into plain memory.
 //
-// Protocol, per exchange object, all words in the control block of each rank (pg_internal.cuh, PG_CTL_*):
-//   flag[src]   written remotely by rank `src`: the number of the last exchange it has delivered
-//   sent        local count of exchanges this rank has produced (bumped by the producer's last CTA)
-//   waited      local count of exchanges this rank has consumed through pg_exchange_wait
-//   done        CTA counter of the producer kernel
-// Counting on the device (not in kernel arguments) keeps the kernels replayable from a graph.  A fused consumer
-// waits for flag[src] >= sent: every rank enqueues the same sequence, so its own producer of the same exchange has
-// already run and counted.  An exchange object may be reused once every rank has consumed its previous result:
-// two other exchanges that all ranks take part in between two uses are enough (a layer has four).
-// Every wait is bounded (pg_ctx_set_wait_limit_ns, a second by default): on expiry the kernel records
-// PG_ERR_DEVICE_TIMEOUT in the context's status word and goes on, so a missing peer never hangs a GPU.
+// An exchange object may be reused once every rank has consumed its previous result: two other exchanges that all
+// ranks take part in between two uses are enough (a decode layer has four).  Every wait is bounded
+// (pg_ctx_set_wait_limit_ns, a second by default): on expiry the kernel records PG_ERR_DEVICE_TIMEOUT in the
+// context's status word and goes on, so a missing peer never hangs a GPU.
 #include <string.h>
 
 #include <new>
@@ -55,6 +49,33 @@ __global__ void __launch_bounds__(256) peer_allgather_store_kernel(const float *
         }
     }
     pg_peer_publish(dst, threadIdx.x);
+}
+
+// the same copy into every rank's flagged cells (for a slice that an ordinary kernel produced)
+__global__ void __launch_bounds__(256) peer_cells_store_kernel(const float *slice, int M, int64_t n_local, const PgPeerOut dst)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t seq = pg_cell_seq(dst);
+    const int64_t total = (int64_t)M * n_local;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int64_t m = i / n_local, c = i - m * n_local;
+        pg_cell_store(dst, seq, m, c, pg_ld_fresh(slice + i));
+    }
+    pg_cell_finish(dst, seq, threadIdx.x);
+}
+
+// waits (bounded, per cell) for every rank's cells of this rank's last exchange and writes the plain [rows, cols] matrix
+__global__ void __launch_bounds__(256) peer_cells_gather_kernel(float *out, int64_t total, const PgPeerWait wt)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t want = pg_cell_want(wt);
+    const int64_t nv = total >> 2;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < nv; i += (int64_t)gridDim.x * 256)
+        reinterpret_cast<float4 *>(out)[i] = pg_cell_load4(wt, want, i * 4);
+    for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256)
+        out[i] = pg_cell_load(wt, want, i);
 }
 
 // one warp: lane r waits until rank r has delivered this rank's next exchange
@@ -91,6 +112,7 @@ PgPeerOut pg_peer_out(const pg_exchange *ex, int64_t ld, int64_t col0)
     PgPeerOut o = {};
     for (int p = 0; p < ex->world; p++) {
         o.y[p] = ex->y[p];
+        o.cells[p] = ex->cells[p];
         o.ctl[p] = ex->ctl[p];
     }
     o.world = ex->world;
@@ -103,6 +125,7 @@ PgPeerOut pg_peer_out(const pg_exchange *ex, int64_t ld, int64_t col0)
 PgPeerWait pg_peer_wait_of(const pg_ctx *ctx, const pg_exchange *ex)
 {
     PgPeerWait w = {};
+    w.cells = ex ? ex->cells_local : nullptr;
     w.ctl = ex ? ex->ctl_local : nullptr;
     w.world = ex ? ex->world : 0;
     w.status = ctx->d_status;
@@ -127,7 +150,7 @@ PG_API int32_t pg_exchange_create(pg_ctx *ctx, int32_t rank, int32_t world, size
     ex->world = world;
     ex->rank = rank;
     ex->y_bytes = (y_bytes + 255) & ~(size_t)255;
-    ex->bytes = ex->y_bytes + PG_CTL_WORDS * sizeof(uint32_t);
+    ex->bytes = 3 * ex->y_bytes + PG_CTL_WORDS * sizeof(uint32_t);   // plain floats | cells (8 bytes per float) | control words
     cudaError_t e = cudaMalloc(&ex->base_local, ex->bytes);
     if (e == cudaSuccess) e = cudaMemset(ex->base_local, 0, ex->bytes);
     cudaIpcMemHandle_t h;
@@ -141,7 +164,8 @@ PG_API int32_t pg_exchange_create(pg_ctx *ctx, int32_t rank, int32_t world, size
     }
     memcpy(handle_out, &h, sizeof(h));
     ex->y_local = reinterpret_cast<float *>(ex->base_local);
-    ex->ctl_local = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(ex->base_local) + ex->y_bytes);
+    ex->cells_local = reinterpret_cast<uint2 *>(reinterpret_cast<char *>(ex->base_local) + ex->y_bytes);
+    ex->ctl_local = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(ex->base_local) + 3 * ex->y_bytes);
     *out = ex;
     return PG_OK;
 }
@@ -160,7 +184,8 @@ PG_API int32_t pg_exchange_connect(pg_ctx *ctx, pg_exchange *ex, const void *han
             ex->peer_base[p] = base;
         }
         ex->y[p] = reinterpret_cast<float *>(base);
-        ex->ctl[p] = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(base) + ex->y_bytes);
+        ex->cells[p] = reinterpret_cast<uint2 *>(reinterpret_cast<char *>(base) + ex->y_bytes);
+        ex->ctl[p] = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(base) + 3 * ex->y_bytes);
     }
     ex->connected = true;
     return PG_OK;
@@ -175,6 +200,7 @@ PG_API int32_t pg_exchange_connect_local(pg_ctx *ctx, pg_exchange *ex, pg_exchan
         PG_REQUIRE(all[p] && all[p]->world == ex->world && all[p]->rank == p && all[p]->y_bytes == ex->y_bytes,
                    "exchange_connect_local: entry %d is not rank %d of the same exchange", p, p);
         ex->y[p] = all[p]->y_local;
+        ex->cells[p] = all[p]->cells_local;
         ex->ctl[p] = all[p]->ctl_local;
     }
     ex->connected = true;
@@ -243,6 +269,33 @@ PG_API int32_t pg_exchange_allgather(pg_ctx *ctx, pg_exchange *ex, const float *
     return pg_exchange_wait(ctx, ex);
 }
 
+// The producer of a flagged-cell exchange for a slice that lies in plain device memory (any kernel's output): copies
+// d_slice [M, n_local] into columns [col0, col0 + n_local) of every rank's [M, n_total] cells.  One per exchange and
+// rank, like pg_gemm_i8_exchange; consumers: pg_exchange_gather and the *_exchange entry points.
+PG_API int32_t pg_exchange_store_cells(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local, int64_t n_total,
+                                       int64_t col0)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex && ex->connected, "exchange_store_cells: null argument or unconnected exchange");
+    PG_REQUIRE(m >= 0 && m <= 0x7fffffff && n_local >= 0 && col0 >= 0 && col0 + n_local <= n_total, "exchange_store_cells: bad column range");
+    PG_REQUIRE((size_t)m * (size_t)n_total * sizeof(float) <= ex->y_bytes, "exchange_store_cells: result does not fit the exchange buffer");
+    PG_REQUIRE(m * n_local == 0 || d_slice, "exchange_store_cells: slice is null");
+    int64_t blocks = (m * n_local + 255) / 256;
+    blocks = blocks < 1 ? 1 : (blocks > 2 * (int64_t)ctx->sm_count ? 2 * (int64_t)ctx->sm_count : blocks);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PG_CUDA(cudaLaunchKernelEx(&cfg, peer_cells_store_kernel, d_slice, (int)m, n_local, pg_peer_out(ex, n_total, col0)));
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
 // One rank's part of a column-sharded integer GEMM with the all-gather inside it: the product of a_i8 [M, K] with
 // this rank's columns `w` ([K, n_local]) lands in columns [col0, col0 + n_local) of EVERY rank's [M, n_total] exchange
 // buffer and the exchange is published.  At decode sizes (M <= 16, K % 64 == 0) the product kernel's own epilogue does
@@ -266,7 +319,36 @@ PG_API int32_t pg_gemm_i8_exchange(pg_ctx *ctx, const int8_t *d_a_i8, const floa
     PG_REQUIRE(m * n == 0 || d_slice_tmp, "gemm_i8_exchange: this shape needs the slice buffer");
     const int32_t rc = pg_gemm_i8(ctx, d_a_i8, d_a_scales, m, k, w, d_slice_tmp, nullptr, PG_ALGO_AUTO);
     if (rc != PG_OK) return rc;
-    return pg_exchange_store(ctx, ex, d_slice_tmp, m, n, n_total, col0);
+    return pg_exchange_store_cells(ctx, ex, d_slice_tmp, m, n, n_total, col0);
+}
+
+// Consumer of a flagged-cell exchange for callers that want the gathered matrix as plain floats: waits (bounded, per
+// cell) for every rank's part of the exchange this rank produced last on `ex` (enqueue it behind this rank's own
+// producer) and writes [rows, cols] f32 to d_out, or to the exchange's own result buffer (pg_exchange_result) when
+// d_out is NULL.
+PG_API int32_t pg_exchange_gather(pg_ctx *ctx, pg_exchange *ex, int64_t rows, int64_t cols, float *d_out)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(ex && ex->connected, "exchange_gather: null argument or unconnected exchange");
+    PG_REQUIRE(rows >= 0 && cols >= 0 && (size_t)rows * (size_t)cols * sizeof(float) <= ex->y_bytes, "exchange_gather: result does not fit the exchange buffer");
+    float *out = d_out ? d_out : ex->y_local;
+    PG_REQUIRE(((uintptr_t)out & 15) == 0, "exchange_gather: the output must be 16-byte aligned");
+    const int64_t total = rows * cols;
+    if (total == 0) return PG_OK;
+    int64_t blocks = (total / 4 + 255) / 256;
+    blocks = blocks < 1 ? 1 : (blocks > 2 * (int64_t)ctx->sm_count ? 2 * (int64_t)ctx->sm_count : blocks);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PG_CUDA(cudaLaunchKernelEx(&cfg, peer_cells_gather_kernel, out, total, pg_peer_wait_of(ctx, ex)));
+    PG_LAUNCHED();
+    return PG_OK;
 }
 
 PG_API int32_t pg_exchange_destroy(pg_ctx *ctx, pg_exchange *ex)

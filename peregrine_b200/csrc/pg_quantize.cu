@@ -45,21 +45,26 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
     // independent prologue (the product kernel prefetches weights)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    pg_peer_wait(wt, threadIdx.x);                // x is an exchange buffer that other GPUs fill: wait for their flags
     const uint32_t cs = cl_size(), rank = cl_rank();
     const int64_t row = blockIdx.x / cs;
     const int64_t nvec = (cols >> 2) / cs;        // float4 per segment (the host picks cs so that this is exact)
     const float4 *xr = reinterpret_cast<const float4 *>(x + row * cols) + rank * nvec;
+    // wt.cells != nullptr: the rows are an exchange's flagged cells that all GPUs fill; a load returns once the cells
+    // carry the number of the exchange this rank's own producer counted last (bounded wait)
+    const bool cells = wt.cells != nullptr;
+    const uint32_t want = cells ? pg_cell_want(wt) : 0u;
+    const int64_t cell0 = row * cols + (int64_t)rank * nvec * 4;
+    auto load = [&](int64_t c) -> float4 { return cells ? pg_cell_load4(wt, want, cell0 + c * 4) : pg_ld_fresh(xr + c); };
     float4 v[VPT];
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
         const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
-        v[i] = (c < nvec) ? pg_ld_fresh(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[i] = (c < nvec) ? load(c) : make_float4(0.f, 0.f, 0.f, 0.f);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
     }
     for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) {
-        const float4 t = pg_ld_fresh(xr + c);
+        const float4 t = load(c);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
     }
     amax = cl_allreduce<true>(block_max(amax, red), xm, cs, rank);
@@ -79,7 +84,7 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
         const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
         if (c < nvec) qr[c] = pack(v[i]);
     }
-    for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) qr[c] = pack(pg_ld_fresh(xr + c));
+    for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) qr[c] = pack(load(c));
 }
 
 // Any cols / any alignment: scalar loads, two passes.

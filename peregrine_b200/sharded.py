@@ -188,6 +188,22 @@ class Exchange:
 
         _lib.check(self.gpu.lib.pg_exchange_store(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, n_total, col0))
 
+    def store_cells(self, d_slice, m: int, n_local: int, n_total: int, col0: int) -> None:
+        """The same hand-over in the flagged-cell form (what `pg_gemm_i8_exchange` does from inside the product);
+        consume with `gather` or one of the `pg_*_exchange` entry points."""
+        from . import _lib
+        from .runtime import _ptr
+
+        _lib.check(self.gpu.lib.pg_exchange_store_cells(self.gpu.handle, self.handle, _ptr(d_slice), m, n_local, n_total, col0))
+
+    def gather(self, rows: int, cols: int, d_out=None) -> None:
+        """Bounded wait for every rank's cells of the exchange this rank produced last; the plain [rows, cols] matrix goes
+        to `d_out` (default: the exchange's own result buffer, `result_ptr`)."""
+        from . import _lib
+        from .runtime import _ptr
+
+        _lib.check(self.gpu.lib.pg_exchange_gather(self.gpu.handle, self.handle, rows, cols, _ptr(d_out)))
+
     def wait(self) -> None:
         """Bounded wait for every rank's slice of the oldest store not yet waited for."""
         from . import _lib

@@ -46,15 +46,16 @@ def test_a_wait_that_runs_out_returns_and_leaves_the_context_usable(gpu, oracle)
         exs = [Exchange(gpu, r, 2, m * n * 4) for r in range(2)]
         Exchange.connect_local(exs)
         half = gpu.upload(np.arange(m * n // 2, dtype=np.float32))
-        exs[0].store(half, m, n // 2, n, 0)
+        exs[0].store_cells(half, m, n // 2, n, 0)
         d_q, d_s = gpu.alloc(m * n + 64, np.int8), gpu.alloc(m, np.float32)
         _lib.check(lib.pg_quantize_activations_exchange(gpu.handle, exs[0].handle, m, n, d_q.ptr, d_s.ptr))
         gpu.sync()
         assert gpu.device_status() == _lib.PG_ERR_DEVICE_TIMEOUT          # rank 1's flag never came
         # rank 1 delivers: the same consumer now passes without a word
         other = gpu.upload(np.arange(m * n // 2, dtype=np.float32) + 1000)
-        exs[1].store(other, m, n // 2, n, n // 2)
+        exs[1].store_cells(other, m, n // 2, n, n // 2)
         _lib.check(lib.pg_quantize_activations_exchange(gpu.handle, exs[0].handle, m, n, d_q.ptr, d_s.ptr))
+        exs[0].gather(m, n)
         gpu.sync()
         assert gpu.device_status() == 0
         full = exs[0].read(m * n).reshape(m, n)

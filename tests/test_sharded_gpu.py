@@ -56,7 +56,7 @@ def _worker(rank, world, port, out_dir):
         shard.to_gpu(gpu)
         exs = [sharded.PeerExchange(gpu, rank, world, m, n) for _ in range(2)]
         d_slice = gpu.alloc(m * (e - b), np.float32)
-        d_q = gpu.alloc(m * k + 64, np.int8)
+        d_q = gpu.alloc(m * max(k, n) + 64, np.int8)
         d_s = gpu.alloc(m, np.float32)
         for it in range(6):
             # new activations every time: a slice read stale (or a flag believed too early) would show
@@ -69,11 +69,12 @@ def _worker(rank, world, port, out_dir):
                 _lib.check(gpu.lib.pg_matmul_quantized(gpu.handle, d_x.ptr, m, k, shard._gpu, d_slice.ptr))
                 ex.allgather(d_slice, m, e - b, b)
             else:
-                # the product's own epilogue stores into every rank and publishes; the wait is a kernel of its own here
+                # the product's own epilogue stores flagged cells into every rank
                 _lib.check(gpu.lib.pg_quantize_activations(gpu.handle, d_x.ptr, m, k, d_q.ptr, d_s.ptr))
                 _lib.check(gpu.lib.pg_gemm_i8_exchange(gpu.handle, d_q.ptr, d_s.ptr, m, k, shard._gpu, ex.handle, n, b, None))
-                # consumer with the wait inside: quantise the gathered rows
+                # consumers with the wait inside: quantise the gathered rows; write them out as plain floats
                 _lib.check(gpu.lib.pg_quantize_activations_exchange(gpu.handle, ex.handle, m, n, d_q.ptr, d_s.ptr))
+                ex.gather(m, n)
             y = ex.read(m)
             assert gpu.device_status() == 0
             assert np.array_equal(y.view(np.uint32), want.view(np.uint32)), f"exchange {it}"
