@@ -302,18 +302,31 @@ __device__ __forceinline__ bool pg_cell_expired(unsigned long long &t0, uint32_t
     atomicExch(w.status, (int32_t)PG_ERR_DEVICE_TIMEOUT);
     return true;
 }
-// four consecutive values starting at cell `at` (a multiple of 2: 16-byte aligned)
-__device__ __forceinline__ float4 pg_cell_load4(const PgPeerWait &w, uint32_t want, int64_t at)
+// Four consecutive values starting at cell `at` (a multiple of 2: 16-byte aligned), in two steps so that a thread can
+// have the loads of several groups in flight before it looks at any of them (a loop that polls one group to the end
+// before it asks for the next one pays a full memory latency per group):
+//   pg_cell_issue4   the two 16-byte loads, no dependence on their results
+//   pg_cell_settle4  checks the numbers and polls again (bounded) only while a cell is still the previous exchange's
+__device__ __forceinline__ void pg_cell_issue4(const PgPeerWait &w, int64_t at, uint4 &a, uint4 &b)
+{
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(w.cells + at) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(w.cells + at + 2) : "memory");
+}
+__device__ __forceinline__ float4 pg_cell_settle4(const PgPeerWait &w, uint32_t want, int64_t at, uint4 a, uint4 b)
 {
     unsigned long long t0 = 0;
-    uint4 a, b;
     for (uint32_t it = 0;; ++it) {
-        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(w.cells + at) : "memory");
-        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(w.cells + at + 2) : "memory");
         if (pg_cell_fresh(a.y, want) && pg_cell_fresh(a.w, want) && pg_cell_fresh(b.y, want) && pg_cell_fresh(b.w, want)) break;
         if (pg_cell_expired(t0, it, w)) break;
+        pg_cell_issue4(w, at, a, b);
     }
     return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+__device__ __forceinline__ float4 pg_cell_load4(const PgPeerWait &w, uint32_t want, int64_t at)
+{
+    uint4 a, b;
+    pg_cell_issue4(w, at, a, b);
+    return pg_cell_settle4(w, want, at, a, b);
 }
 __device__ __forceinline__ float pg_cell_load(const PgPeerWait &w, uint32_t want, int64_t at)
 {

@@ -83,9 +83,11 @@ __global__ void __launch_bounds__(LT) add_rmsnorm_quant_kernel(float *__restrict
         const int c = i * LT + threadIdx.x;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (c < nseg) {
+            uint4 ca, cb;
+            if (dcells) pg_cell_issue4(wt, row * dim + (int64_t)(c0 + c) * 4, ca, cb);
             v[i] = pg_ld_fresh(xr + c0 + c);
             if (delta || dcells) {
-                const float4 d = dcells ? pg_cell_load4(wt, want, row * dim + (int64_t)(c0 + c) * 4)
+                const float4 d = dcells ? pg_cell_settle4(wt, want, row * dim + (int64_t)(c0 + c) * 4, ca, cb)
                                         : pg_ld_fresh(reinterpret_cast<const float4 *>(delta + row * dim) + c0 + c);
                 v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
                 xr[c0 + c] = v[i];

@@ -57,12 +57,33 @@ __global__ void __launch_bounds__(QR_THREADS) quantize_rows_kernel(const float *
     auto load = [&](int64_t c) -> float4 { return cells ? pg_cell_load4(wt, want, cell0 + c * 4) : pg_ld_fresh(xr + c); };
     float4 v[VPT];
     float amax = 0.0f;
+    if (cells) {
+        // up to four groups of cells per thread are requested before the first one is looked at
+        constexpr int BATCH = VPT < 4 ? VPT : 4;
 #pragma unroll
-    for (int i = 0; i < VPT; i++) {
-        const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
-        v[i] = (c < nvec) ? load(c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+        for (int i0 = 0; i0 < VPT; i0 += BATCH) {
+            uint4 ca[BATCH], cb[BATCH];
+#pragma unroll
+            for (int j = 0; j < BATCH; j++) {
+                const int64_t c = (int64_t)(i0 + j) * QR_THREADS + threadIdx.x;
+                if (c < nvec) pg_cell_issue4(wt, cell0 + c * 4, ca[j], cb[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < BATCH; j++) {
+                const int64_t c = (int64_t)(i0 + j) * QR_THREADS + threadIdx.x;
+                v[i0 + j] = (c < nvec) ? pg_cell_settle4(wt, want, cell0 + c * 4, ca[j], cb[j]) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+            const int64_t c = (int64_t)i * QR_THREADS + threadIdx.x;
+            v[i] = (c < nvec) ? pg_ld_fresh(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
+#pragma unroll
+    for (int i = 0; i < VPT; i++)
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
     for (int64_t c = (int64_t)VPT * QR_THREADS + threadIdx.x; c < nvec; c += QR_THREADS) {
         const float4 t = load(c);
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
@@ -209,7 +230,10 @@ int32_t pgk_quantize_activations_wait(pg_ctx *ctx, const float *d_x, int64_t row
         // of a cluster to cost less than one CTA's walk along the row (measured: at 4096 and 14336 columns one CTA wins)
         int cs = 8;
         const int64_t nvec = cols / 4;
-        while (cs > 1 && (rows * cs > 2 * (int64_t)ctx->sm_count || nvec % cs != 0 || nvec / cs < 2048)) cs >>= 1;
+        // (rows read from an exchange's cells are polled, which costs a memory latency per group of cells and thread:
+        // there a row is spread as widely as the cluster allows)
+        const int64_t min_seg = wait ? 256 : 2048;
+        while (cs > 1 && (rows * cs > 2 * (int64_t)ctx->sm_count || nvec % cs != 0 || nvec / cs < min_seg)) cs >>= 1;
         PG_REQUIRE(rows * cs <= 0x7fffffff, "quantize_activations: rows=%lld exceeds the grid limit", (long long)rows);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(rows * cs));

@@ -44,32 +44,67 @@ def llama_case(a) -> None:
     gen.manual_seed(1)
 
     class Lazy(dict):
+        """weights drawn on the device when asked for; the embedding (replicated on every rank) once"""
+
+        emb = None
+
         def __getitem__(self, key):
             if key == "embedding":
-                return torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=dev) * 0.02
+                if Lazy.emb is None:
+                    Lazy.emb = torch.randn(cfg.vocab, cfg.hidden, generator=gen, device=dev) * 0.02
+                return Lazy.emb
             if key.endswith("norm"):
                 return torch.ones(cfg.hidden, device=dev)
             shape = {"lm_head": (cfg.hidden, cfg.vocab), "qkv": (cfg.hidden, cfg.qkv_dim), "o": (cfg.hidden, cfg.hidden),
                      "gate_up": (cfg.hidden, 2 * cfg.ffn), "down": (cfg.ffn, cfg.hidden)}[key.split(".")[-1]]
             return torch.randn(*shape, generator=gen, device=dev) * 0.02
 
+        def columns(self, key, cols):
+            rows = {"lm_head": cfg.hidden, "qkv": cfg.hidden, "o": cfg.n_q_heads * cfg.head_dim, "gate_up": cfg.hidden,
+                    "down": cfg.ffn}[key.split(".")[-1]]
+            return torch.randn(rows, len(cols), generator=gen, device=dev) * 0.02
+
     gpu = GpuContext(0)
-    model = LlamaInt8Decoder(cfg, gpu, Lazy())
-    model.kcache[:, :, :, :a.context].normal_(generator=gen)
-    model.vcache[:, :, :, :a.context].normal_(generator=gen)
-    model.set_position(a.context)
-    model.set_tokens(np.arange(cfg.batch) * 977 % cfg.vocab)
-    model.embed()
-    model.enqueue_step()
+    if a.world > 1:
+        # every rank of a column-sharded step played on this one GPU, advanced in turn launch by launch (a launch that
+        # waits for the other ranks' cells is then always enqueued behind the launches that store them): the launch list
+        # of such a run shows what each rank's kernels cost at the sharded shapes, without the other GPUs
+        lazy = Lazy()
+        ranks = [LlamaInt8Decoder(cfg, gpu, lazy, rank=r, world=a.world, connect=False) for r in range(a.world)]
+        LlamaInt8Decoder.connect_local(ranks)
+        for m in ranks:
+            m.kcache[:, :, :, :a.context].normal_(generator=gen)
+            m.vcache[:, :, :, :a.context].normal_(generator=gen)
+            m.set_position(a.context)
+            m.set_tokens(np.arange(cfg.batch) * 977 % cfg.vocab)
+            m.embed()
+
+        def step():
+            for _ in zip(*[m.step_ops() for m in ranks]):
+                pass
+
+        model = ranks[0]
+    else:
+        model = LlamaInt8Decoder(cfg, gpu, Lazy())
+        ranks = [model]
+        model.kcache[:, :, :, :a.context].normal_(generator=gen)
+        model.vcache[:, :, :, :a.context].normal_(generator=gen)
+        model.set_position(a.context)
+        model.set_tokens(np.arange(cfg.batch) * 977 % cfg.vocab)
+        model.embed()
+        step = model.enqueue_step
+    step()
     gpu.sync()
     t0 = time.perf_counter()
     for _ in range(a.reps):
-        model.enqueue_step()
+        step()
     gpu.sync()
     us = (time.perf_counter() - t0) / a.reps * 1e6
     status = gpu.device_status()
-    print(f"op=llama layers={cfg.layers} batch={cfg.batch} context={a.context}: {us:.1f} us/step eager, device_status={status}")
-    model.free()
+    print(f"op=llama layers={cfg.layers} batch={cfg.batch} context={a.context} ranks on this GPU={a.world}: {us:.1f} us/step eager, "
+          f"device_status={status}")
+    for m in ranks:
+        m.free()
     if status != 0:
         raise SystemExit(1)
 
@@ -174,6 +209,7 @@ def main() -> None:
     ap.add_argument("--pair", type=int, default=0, help="tcgen05: 0 heuristic, 1 one CTA per tile, 2 CTA pairs")
     ap.add_argument("--layers", type=int, default=2, help="llama: decoder layers (Llama-3-8B shapes otherwise)")
     ap.add_argument("--context", type=int, default=2048, help="llama: KV positions already filled")
+    ap.add_argument("--world", type=int, default=1, help="llama: ranks of a column-sharded step, all played on this one GPU")
     a = ap.parse_args()
     if a.op == "llama":
         return llama_case(a)
