@@ -437,26 +437,36 @@ __global__ void __launch_bounds__(256) pick_embed_kernel(int world, int *__restr
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int b = blockIdx.x;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
+        // lane r polls rank r's pair (all pairs in flight at once); lane 0 then walks them in rank order
         const uint32_t want = pg_cell_want(wt);
+        const int r = threadIdx.x;
+        float v = -INFINITY;
+        int i = 0;
+        if (r < world) {
+            v = pg_cell_load(wt, want, ((int64_t)b * world + r) * 2);
+            i = __float_as_int(pg_cell_load(wt, want, ((int64_t)b * world + r) * 2 + 1));
+        }
         float best = -INFINITY;
         int idx = 0;
         bool any = false;
-        for (int r = 0; r < world; r++) {
-            const float v = pg_cell_load(wt, want, ((int64_t)b * world + r) * 2);
-            const int i = __float_as_int(pg_cell_load(wt, want, ((int64_t)b * world + r) * 2 + 1));
-            if (v > best) {
-                best = v;
-                idx = i;
+        for (int q = 0; q < world; q++) {
+            const float vq = __shfl_sync(0xffffffffu, v, q);
+            const int iq = __shfl_sync(0xffffffffu, i, q);
+            if (vq > best) {
+                best = vq;
+                idx = iq;
                 any = true;
             }
         }
         if (!any) idx = 0;   // every slice all-NaN or -inf: the reference's loop keeps index 0
-        tokens[b] = idx;
-        s_tok = idx;
-        if (b == 0 && pos_ptr) {
-            const int p = pg_ld_fresh(pos_ptr);
-            if (pos_limit <= 0 || p < pos_limit) *pos_ptr = p + 1;
+        if (threadIdx.x == 0) {
+            tokens[b] = idx;
+            s_tok = idx;
+            if (b == 0 && pos_ptr) {
+                const int p = pg_ld_fresh(pos_ptr);
+                if (pos_limit <= 0 || p < pos_limit) *pos_ptr = p + 1;
+            }
         }
     }
     __syncthreads();
@@ -524,12 +534,19 @@ __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__
     }
     __syncthreads();
     const float denom = den[threadIdx.y];
-    float acc = 0.0f;
-#pragma unroll 4
-    for (int s = 0; s < S; s++) {
-        const float e = wgt[threadIdx.y][s];
-        if (e != 0.0f) acc = fmaf(e, pg_ld_fresh(po + (int64_t)s * 128 + d), acc);
+    // eight running sums (slice s goes to sum s % 8), added up in a fixed order at the end: eight loads are in flight per
+    // thread instead of a chain of S, and the order of the additions depends on S alone, not on how the heads are
+    // spread over CTAs or ranks
+    float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = (s0 + j < S && wgt[threadIdx.y][s0 + j] != 0.0f) ? pg_ld_fresh(po + (int64_t)(s0 + j) * 128 + d) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (s0 + j < S) part[j] = fmaf(wgt[threadIdx.y][s0 + j], v[j], part[j]);
     }
+    const float acc = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
     const float o = (denom > 0.0f) ? __fdiv_rn(acc, denom) : 0.0f;
     const int64_t at = ((int64_t)b * Hq + qh) * 128 + d;
     if (out) out[at] = o;
@@ -847,7 +864,7 @@ PG_API int32_t pg_argmax_exchange(pg_ctx *ctx, const float *d_logits_local, int6
                "argmax_exchange: bad arguments");
     PG_REQUIRE((size_t)B * ex->world * 2 * sizeof(float) <= ex->y_bytes, "argmax_exchange: the exchange buffer is smaller than [B][world][2] floats");
     if (B == 0) return PG_OK;
-    const int cs = row_cluster(ctx, B, V_local, 4096);
+    const int cs = row_cluster(ctx, B, V_local, 1024);
     return launch_pdl_cluster(ctx, argmax_kernel, dim3((unsigned)(B * cs)), dim3(1024), 0, cs, d_logits_local, (int)V_local, (int *)nullptr,
                               (int *)nullptr, 0, (int)v0, pg_peer_out(ex, (int64_t)ex->world * 2, (int64_t)ex->rank * 2));
 }
