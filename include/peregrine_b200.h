@@ -172,6 +172,16 @@ PG_API int32_t pg_matmul_quantized_ex(pg_ctx *ctx, const float *d_x, int64_t m, 
 PG_API int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t k,
                                         const pg_qtensor *w, float *y);
 
+/* ---- quant::matmul_quantized_gpu (src/quant.rs:195-218) as the reference's GPU kernels compute it: matmul_dequant_i8 /
+ *      matmul_dequant_simd_i8 (src/metal/shaders.rs:2329-2465, selector src/metal/context.rs:2226-2306) ----
+ * y[M,N] = sum_k x[m,k] * (float(w_i8[k,n]) * w_scale[n]), f32 throughout: the activations are NOT quantised ("W8A32"),
+ * unlike the CPU path above.  sequential != 0: one thread per output, ascending k with separately rounded multiply and
+ * add (the order of the 16 x 16 kernel's loops; bit-exact against the CPU restatement); 0: the bandwidth-bound form
+ * (one pass over data_i8_t per eight rows, f32 sums in another order).  Enqueued, not synchronised, like the Metal
+ * dispatch (tests/quant_parity.rs:102-107). */
+PG_API int32_t pg_matmul_dequant_w8a32(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k, const pg_qtensor *w, float *d_y,
+                                       int32_t sequential);
+
 /* ---- the same product for callers that must not allocate (no counterpart in the reference) ----
  * For hosts that run inside a memory budget fixed before inference starts (a pre-sized arena per
  * model, a real-time loop in which cudaMalloc is forbidden): identical to pg_matmul_quantized, but

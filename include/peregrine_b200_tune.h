@@ -39,6 +39,9 @@ PG_API void pg_tune_gguf_rows(int r);
  * writes y itself / a copy kernel pushes y (0 = path off, negative = default) */
 PG_API void pg_tune_host_direct(int x_bytes, int y_bytes);
 PG_API void pg_tune_host_push(int y_bytes);
+/* diagnostic: one rank of a sharded step without its peers (stores stay local, no cell is waited for; results are
+ * meaningless, the time is one rank's kernels and launches alone) */
+PG_API void pg_tune_exchange_solo(int on);
 /* diagnostic: sweeps over the subsequence starts that the last Huffman decode of this process took */
 PG_API int pg_huffman_last_sweeps(void);
 

@@ -4,6 +4,7 @@
     gguf      mirror of the block codecs of peregrine::gguf  (src/gguf.rs:284-401)
     gguf_file the GGUF container, mirror of GgufFile  (src/gguf.rs:140-283, 403-567)
     llama     the Llama decode step on the int8 path  (src/models/llama)
+    llama_gguf  Llama::from_gguf for that step: config keys, tensor names, transposition, Q|K|V and gate|up fusion
     serial    the quantised serial formats  (src/serial.rs:124-222, 315-443)
     huffman   Huffman-coded int8 weights, mirror of HuffmanTable / HuffmanTensor  (src/huffman.rs:19-476)
     runtime   GpuContext / GpuBuffer / init_gpu / with_gpu  (the reference's `metal` seam)

@@ -74,6 +74,7 @@ SIGNATURES = {
     "pg_matmul_quantized": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "pg_matmul_quantized_ex": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i32]),
     "pg_matmul_quantized_host": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "pg_matmul_dequant_w8a32": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _i32]),
     "pg_matmul_quantized_static": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "pg_static_scratch_bytes": (_i64, []),
     "pg_gemm_i8": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i32]),
@@ -133,6 +134,7 @@ TUNE_SIGNATURES = {
     "pg_tune_gguf_rows": (None, [_int]),
     "pg_tune_host_direct": (None, [_int, _int]),
     "pg_tune_host_push": (None, [_int]),
+    "pg_tune_exchange_solo": (None, [_int]),
     "pg_huffman_last_sweeps": (_int, []),
 }
 

@@ -28,6 +28,7 @@ SOURCES = [
     "pg_gguf.cu",
     "pg_gguf_mma.cu",
     "pg_noalloc.cu",
+    "pg_w8a32.cu",
     "pg_peer.cu",
     "pg_llama.cu", "pg_llama_attn.cu",
     "pg_huffman.cu",
@@ -52,7 +53,8 @@ def _nvcc() -> str:
 
 
 def _sources():
-    deps = [os.path.join(CSRC, "pg_internal.cuh"), os.path.join(ROOT, "include", "peregrine_b200.h"), os.path.abspath(__file__)]
+    deps = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cuh")]
+    deps += [os.path.join(ROOT, "include", f) for f in ("peregrine_b200.h", "peregrine_b200_tune.h")] + [os.path.abspath(__file__)]
     return [os.path.join(CSRC, s) for s in SOURCES], deps
 
 

@@ -107,9 +107,25 @@ __global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t *ctl, int world,
 
 }  // namespace
 
+// Diagnostic (pg_tune_exchange_solo): a rank of a sharded step run WITHOUT its peers -- producers store into their own
+// buffer only, consumers take every cell as delivered.  The results are meaningless; the step's time is what one rank's
+// kernels and launches cost at the sharded shapes with nothing crossing NVLink and nobody waited for.
+static int g_exchange_solo = 0;
+extern "C" PG_API void pg_tune_exchange_solo(int on) { g_exchange_solo = on; }
+
 PgPeerOut pg_peer_out(const pg_exchange *ex, int64_t ld, int64_t col0)
 {
     PgPeerOut o = {};
+    if (g_exchange_solo) {
+        o.y[0] = ex->y_local;
+        o.cells[0] = ex->cells_local;
+        o.ctl[0] = ex->ctl_local;
+        o.world = 1;
+        o.rank = 0;
+        o.ld = ld;
+        o.col0 = col0;
+        return o;
+    }
     for (int p = 0; p < ex->world; p++) {
         o.y[p] = ex->y[p];
         o.cells[p] = ex->cells[p];
@@ -129,7 +145,7 @@ PgPeerWait pg_peer_wait_of(const pg_ctx *ctx, const pg_exchange *ex)
     w.ctl = ex ? ex->ctl_local : nullptr;
     w.world = ex ? ex->world : 0;
     w.status = ctx->d_status;
-    w.limit_ns = ctx->wait_limit_ns;
+    w.limit_ns = g_exchange_solo ? 0ull : ctx->wait_limit_ns;   // solo: limit 0 marks "take every cell as delivered"
     return w;
 }
 
@@ -195,8 +211,8 @@ PG_API int32_t pg_exchange_connect(pg_ctx *ctx, pg_exchange *ex, const void *han
 PG_API int32_t pg_exchange_connect_local(pg_ctx *ctx, pg_exchange *ex, pg_exchange *const *all)
 {
     PG_ENTER(ctx);
-    PG_REQUIRE(ex && all, "exchange_connect_local: null argument");
-    for (int p = 0; p < ex->world; p++) {
+    PG_REQUIRE(ex && (all || g_exchange_solo), "exchange_connect_local: null argument");
+    for (int p = 0; all && p < ex->world; p++) {
         PG_REQUIRE(all[p] && all[p]->world == ex->world && all[p]->rank == p && all[p]->y_bytes == ex->y_bytes,
                    "exchange_connect_local: entry %d is not rank %d of the same exchange", p, p);
         ex->y[p] = all[p]->y_local;

@@ -127,9 +127,15 @@ def matmul_quantized(a_data, m: int, k: int, w: QuantizedTensor, gpu: Optional[G
     return y
 
 
-def matmul_quantized_gpu(gpu: GpuContext, a_data, m: int, k: int, w: QuantizedTensor) -> GpuBuffer:
+def matmul_quantized_gpu(gpu: GpuContext, a_data, m: int, k: int, w: QuantizedTensor, dequant: bool = False,
+                         sequential: bool = False) -> GpuBuffer:
     """Uploads A, enqueues the product and returns the device buffer WITHOUT synchronising;
-    the weights must already be on the GPU ("weights not on GPU" otherwise, src/quant.rs:208)."""
+    the weights must already be on the GPU ("weights not on GPU" otherwise, src/quant.rs:208).
+
+    By default the product is the CPU path's W8A8 (quantised activations, integer sums), which is what the parity
+    target of this library is.  dequant=True gives what the reference's own GPU kernels compute behind this function
+    (src/metal/shaders.rs:2329-2465): f32 activations times weights dequantised on the fly ("W8A32");
+    sequential=True takes the one-thread-per-output form of it, which adds in the order of the reference's loops."""
     if w.rows != k:
         raise _lib.InvalidArgument(_lib.PG_ERR_INVALID, f"matmul_quantized_gpu: w.rows ({w.rows}) != k ({k})")
     a = _f32(a_data, m * k, "matmul_quantized_gpu")
@@ -138,7 +144,10 @@ def matmul_quantized_gpu(gpu: GpuContext, a_data, m: int, k: int, w: QuantizedTe
     a_buf = gpu.upload(a)
     n = w.col_range[1] - w.col_range[0]
     out = gpu.alloc(m * n, np.float32)
-    _lib.check(gpu.lib.pg_matmul_quantized(gpu.handle, a_buf.ptr, m, k, w._gpu, out.ptr))
+    if dequant:
+        _lib.check(gpu.lib.pg_matmul_dequant_w8a32(gpu.handle, a_buf.ptr, m, k, w._gpu, out.ptr, 1 if sequential else 0))
+    else:
+        _lib.check(gpu.lib.pg_matmul_quantized(gpu.handle, a_buf.ptr, m, k, w._gpu, out.ptr))
     out._keepalive = a_buf  # A must outlive the enqueued kernels
     return out
 

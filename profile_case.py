@@ -65,6 +65,37 @@ def llama_case(a) -> None:
             return torch.randn(rows, len(cols), generator=gen, device=dev) * 0.02
 
     gpu = GpuContext(0)
+    if a.world > 1 and a.solo:
+        # rank 0 of a.world alone: its kernels at the sharded shapes, recorded into one graph, nothing exchanged
+        gpu.lib.pg_tune_exchange_solo(1)
+        model = LlamaInt8Decoder(cfg, gpu, Lazy(), rank=0, world=a.world, connect=False)
+        for e in model.ex.values():
+            _lib.check(gpu.lib.pg_exchange_connect_local(gpu.handle, e.handle, None))   # solo: no peers to name
+        ranks = [model]
+        model.kcache[:, :, :, :a.context].normal_(generator=gen)
+        model.vcache[:, :, :, :a.context].normal_(generator=gen)
+        model.set_position(a.context)
+        model.set_tokens(np.arange(cfg.batch) * 977 % cfg.vocab)
+        model.embed()
+        graph = model.record()
+        for _ in range(5):
+            graph.launch()
+        gpu.sync()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        model.set_position(a.context)
+        torch.cuda.synchronize()
+        stream = torch.cuda.ExternalStream(gpu.stream)
+        ev0.record(stream)
+        for _ in range(a.reps):
+            graph.launch()
+        ev1.record(stream)
+        gpu.sync()
+        us = ev0.elapsed_time(ev1) / a.reps * 1e3
+        print(f"op=llama layers={cfg.layers} batch={cfg.batch} context={a.context} rank 0 of {a.world} alone (no exchange): "
+              f"{us:.1f} us/step from a graph of {graph.kernels} kernels")
+        gpu.device_status()
+        gpu.lib.pg_tune_exchange_solo(0)
+        return
     if a.world > 1:
         # every rank of a column-sharded step played on this one GPU, advanced in turn launch by launch (a launch that
         # waits for the other ranks' cells is then always enqueued behind the launches that store them): the launch list
@@ -209,6 +240,7 @@ def main() -> None:
     ap.add_argument("--pair", type=int, default=0, help="tcgen05: 0 heuristic, 1 one CTA per tile, 2 CTA pairs")
     ap.add_argument("--layers", type=int, default=2, help="llama: decoder layers (Llama-3-8B shapes otherwise)")
     ap.add_argument("--context", type=int, default=2048, help="llama: KV positions already filled")
+    ap.add_argument("--solo", action="store_true", help="llama with --world: rank 0 alone, nothing exchanged (timing diagnostic)")
     ap.add_argument("--world", type=int, default=1, help="llama: ranks of a column-sharded step, all played on this one GPU")
     a = ap.parse_args()
     if a.op == "llama":
