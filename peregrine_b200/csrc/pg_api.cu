@@ -123,7 +123,6 @@ int32_t pg_ctx_destroy(pg_ctx *ctx)
     if (ctx->staging) cudaFree(ctx->staging);
     if (ctx->splitk) cudaFree(ctx->splitk);
     for (void *p : ctx->retired) cudaFree(p);
-    if (ctx->h_done) cudaFreeHost((void *)ctx->h_done);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);

@@ -146,19 +146,6 @@ struct pg_ctx {
     // (or with the context), so that replaying an older graph never touches freed memory.
     int live_graphs = 0;
     std::vector<void *> retired;
-    // page-locked host buffers seen by the *_host calls: host pointer -> device view (cudaPointerGetAttributes costs
-    // microseconds per call; a buffer's registration does not change while the caller keeps using it)
-    struct HostView {
-        const void *host = nullptr;
-        void *dev = nullptr;
-    };
-    HostView host_views[8];
-    int host_view_next = 0;
-    // completion word of the *_host calls: a word of mapped page-locked memory that the last kernel of a call writes
-    // and the host polls, instead of a stream synchronisation
-    volatile uint32_t *h_done = nullptr;
-    uint32_t *d_done = nullptr;   // the device's view of h_done
-    uint32_t done_seq = 0;
 };
 
 struct pg_graph {
