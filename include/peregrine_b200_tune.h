@@ -32,9 +32,9 @@ PG_API void pg_tune_wstream_cluster(int cs);
 /* tcgen05 product: tile width in columns (32, 64, 128, 256; 0 = choice); CTA pairs: 0 = choice, 1 = never, 2 = always */
 PG_API void pg_tune_tcgen05_bn(int bn);
 PG_API void pg_tune_tcgen05_pair(int mode);
-/* GGUF product: 1 = always the CUDA-core kernel; row groups per tile of the tensor-core kernel (0 = choice) */
+/* GGUF weights uploaded while this is 1 keep the plain block planes and take the CUDA-core product kernel (otherwise
+ * Q4_0 / Q8_0 weights with K % 256 == 0 are laid out for, and served by, the streaming tensor-core kernel) */
 PG_API void pg_tune_gguf_simple(int on);
-PG_API void pg_tune_gguf_rows(int r);
 /* pg_matmul_quantized_host with page-locked buffers: up to how many bytes the quantiser reads x itself / the product
  * writes y itself / a copy kernel pushes y (0 = path off, negative = default) */
 PG_API void pg_tune_host_direct(int x_bytes, int y_bytes);

@@ -26,7 +26,7 @@ SOURCES = [
     "pg_gemm_tcgen05.cu",
     "pg_gemm_tcgen05_2cta.cu",
     "pg_gguf.cu",
-    "pg_gguf_mma.cu",
+    "pg_gguf_stream.cu",
     "pg_noalloc.cu",
     "pg_w8a32.cu",
     "pg_peer.cu",

@@ -710,7 +710,7 @@ int32_t pg_gguf_upload(pg_ctx *ctx, int32_t type, const uint8_t *raw, size_t raw
     w->n = nr;
     w->k = k;
     const size_t blocks = (size_t)nr * nblk;
-    const size_t qbytes = blocks * (type == PG_GGUF_Q8_0 ? 32 : 16);
+    const size_t qbytes = pgk_gguf_qs_bytes(type, nr, k, nullptr);
     void *d_raw = nullptr;
     cudaError_t e = cudaMalloc((void **)&w->d_qs, qbytes + 64);
     if (e == cudaSuccess) e = cudaMalloc((void **)&w->d_d, blocks * 2 + 64);

@@ -77,20 +77,33 @@ __global__ void __launch_bounds__(256) f16_to_f32_kernel(const uint16_t *__restr
 }
 
 // raw [N][K/32][block] -> qs plane + scale planes.
-// With `interleave`, each 64-byte group of quants (4 Q4_0 blocks / 2 Q8_0 blocks) is stored so that
-// its 16-byte chunk t holds what lane t of a tensor-core fragment needs: word t of each of the four
-// Q4_0 blocks, or bytes 8t..8t+7 of each of the two Q8_0 blocks.
-__device__ __forceinline__ int64_t qs_index(int type, int interleave, int64_t b, int byte)
+// Plain planes: qs [N][K/32][16 or 32 quant bytes], d [N][K/32] f16 (Q4_1: also m).
+// Tiled layout of the streaming tensor-core kernel (Q4_0 / Q8_0, K % 256 == 0): one contiguous "fill" per (tile of 16 rows,
+// slice of 8 blocks), FILL = 16 * SEG + 256 bytes with SEG = 8 * {16, 32} quant bytes per row:
+//   row r of the tile at r * SEG, as 16-byte pieces; piece p of a row holds what lane t = p % 4 of a tensor-core fragment
+//   needs of block group p / 4 -- Q4_0: word t (elements 8t..8t+7) of the group's four blocks; Q8_0: bytes 8t..8t+7 of
+//   the group's two blocks -- and is stored at position p ^ ((r & 1) << 2), so that the eight lanes of a quarter warp
+//   (two rows, four pieces each) hit all 32 banks when the fill lies in shared memory as it lies in global memory;
+//   then the scales: row r's eight f16 at 16 * SEG + r * 16.
+__device__ __forceinline__ int64_t tiled_index(int type, int64_t row, int64_t nslices, int blk_in_row, int byte, bool scale)
 {
+    const int seg = (type == PG_GGUF_Q8_0) ? 256 : 128;
+    const int64_t fill = 16 * seg + 256;
+    const int64_t base = ((row >> 4) * nslices + (blk_in_row >> 3)) * fill;
+    const int r = (int)(row & 15), bl = blk_in_row & 7;
+    if (scale) return base + 16 * seg + r * 16 + bl * 2;
+    int piece, within;
     if (type == PG_GGUF_Q8_0) {
-        if (!interleave) return b * 32 + byte;
-        return (b >> 1) * 64 + (byte >> 3) * 16 + (b & 1) * 8 + (byte & 7);
+        piece = (bl >> 1) * 4 + (byte >> 3);
+        within = (bl & 1) * 8 + (byte & 7);
+    } else {
+        piece = (bl >> 2) * 4 + (byte >> 2);
+        within = (bl & 3) * 4 + (byte & 3);
     }
-    if (!interleave) return b * 16 + byte;
-    return (b >> 2) * 64 + (byte >> 2) * 16 + (b & 3) * 4 + (byte & 3);
+    return base + (int64_t)r * seg + ((piece ^ ((r & 1) << 2)) * 16) + within;
 }
 
-__global__ void __launch_bounds__(256) repack_kernel(int type, int interleave, const uint8_t *__restrict__ raw, int64_t num_blocks,
+__global__ void __launch_bounds__(256) repack_kernel(int type, int tiled, const uint8_t *__restrict__ raw, int64_t num_blocks, int nblk_row,
                                                       uint8_t *__restrict__ qs, uint16_t *__restrict__ dd, uint16_t *__restrict__ mm)
 {
     const int lane = threadIdx.x & 31;
@@ -99,11 +112,19 @@ __global__ void __launch_bounds__(256) repack_kernel(int type, int interleave, c
     const int bs = block_bytes(type);
     for (int64_t b = warp0; b < num_blocks; b += nwarps) {
         const uint8_t *p = raw + b * bs;
+        if (tiled) {
+            const int64_t row = b / nblk_row;
+            const int bir = (int)(b - row * nblk_row);
+            const int64_t nslices = nblk_row >> 3;
+            if (lane < 2) qs[tiled_index(type, row, nslices, bir, 0, true) + lane] = p[lane];
+            if (type == PG_GGUF_Q8_0 || lane < 16) qs[tiled_index(type, row, nslices, bir, lane, false)] = p[2 + lane];
+            continue;
+        }
         if (lane == 0) dd[b] = (uint16_t)(p[0] | (p[1] << 8));
         if (type == PG_GGUF_Q8_0) {
-            qs[qs_index(type, interleave, b, lane)] = p[2 + lane];
+            qs[b * 32 + lane] = p[2 + lane];
         } else if (type == PG_GGUF_Q4_0) {
-            if (lane < 16) qs[qs_index(type, interleave, b, lane)] = p[2 + lane];
+            if (lane < 16) qs[b * 16 + lane] = p[2 + lane];
         } else {
             if (lane == 1) mm[b] = (uint16_t)(p[2] | (p[3] << 8));
             if (lane < 16) qs[b * 16 + lane] = p[4 + lane];
@@ -117,7 +138,7 @@ __global__ void __launch_bounds__(256) repack_kernel(int type, int interleave, c
 // each activation row forms the block's partial sum in f32 before applying the block scale:
 // y += d * sum_i x_i q_i  (+ m * sum_i x_i for Q4_1).  Lanes are then summed by shuffles.
 template <int TYPE, int R, int MC>
-__global__ void __launch_bounds__(256) matmul_gguf_kernel(const float *__restrict__ x, int m0, int M, int K, int interleave,
+__global__ void __launch_bounds__(256) matmul_gguf_kernel(const float *__restrict__ x, int m0, int M, int K,
                                                            const uint8_t *__restrict__ qs, const uint16_t *__restrict__ dd,
                                                            const uint16_t *__restrict__ mm, int64_t N, float *__restrict__ y)
 {
@@ -143,32 +164,18 @@ __global__ void __launch_bounds__(256) matmul_gguf_kernel(const float *__restric
             mn[j] = 0.0f;
             if (TYPE == PG_GGUF_Q8_0) {
                 uint32_t wds[8];
-                if (!interleave) {
-                    const uint4 *p = reinterpret_cast<const uint4 *>(qs + blk * 32);
-                    const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
-                    wds[0] = v0.x; wds[1] = v0.y; wds[2] = v0.z; wds[3] = v0.w;
-                    wds[4] = v1.x; wds[5] = v1.y; wds[6] = v1.z; wds[7] = v1.w;
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(qs + (blk >> 1) * 64 + c * 16 + (blk & 1) * 8));
-                        wds[2 * c] = v.x;
-                        wds[2 * c + 1] = v.y;
-                    }
-                }
+                const uint4 *p = reinterpret_cast<const uint4 *>(qs + blk * 32);
+                const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
+                wds[0] = v0.x; wds[1] = v0.y; wds[2] = v0.z; wds[3] = v0.w;
+                wds[4] = v1.x; wds[5] = v1.y; wds[6] = v1.z; wds[7] = v1.w;
 #pragma unroll
                 for (int wd = 0; wd < 8; wd++)
 #pragma unroll
                     for (int e = 0; e < 4; e++) q[j][wd * 4 + e] = (float)(int8_t)((wds[wd] >> (8 * e)) & 0xff);
             } else {
                 uint32_t wds[4];
-                if (!interleave) {
-                    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(qs + blk * 16));
-                    wds[0] = v.x; wds[1] = v.y; wds[2] = v.z; wds[3] = v.w;
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; c++) wds[c] = __ldg(reinterpret_cast<const uint32_t *>(qs + (blk >> 2) * 64 + c * 16 + (blk & 3) * 4));
-                }
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(qs + blk * 16));
+                wds[0] = v.x; wds[1] = v.y; wds[2] = v.z; wds[3] = v.w;
 #pragma unroll
                 for (int wd = 0; wd < 4; wd++)
 #pragma unroll
@@ -227,7 +234,7 @@ int32_t launch_matmul(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_we
     const int64_t warps = (w->n + R - 1) / R;
     const int64_t blocks = (warps + 7) / 8;
     for (int64_t m0 = 0; m0 < m; m0 += MC) {
-        matmul_gguf_kernel<TYPE, R, MC><<<(unsigned)blocks, 256, 0, ctx->stream>>>(d_x, (int)m0, (int)m, (int)w->k, w->interleaved, w->d_qs, w->d_d,
+        matmul_gguf_kernel<TYPE, R, MC><<<(unsigned)blocks, 256, 0, ctx->stream>>>(d_x, (int)m0, (int)m, (int)w->k, w->d_qs, w->d_d,
                                                                                   w->d_m, w->n, d_y);
         PG_LAUNCHED();
     }
@@ -254,27 +261,40 @@ int32_t pgk_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float
     return PG_OK;
 }
 
+static int g_gguf_force_simple = 0;
+extern "C" PG_API void pg_tune_gguf_simple(int on) { g_gguf_force_simple = on; }
+
+size_t pgk_gguf_qs_bytes(int32_t type, int64_t rows, int64_t k, int *tiled)
+{
+    const int64_t nblk = k / 32;
+    // the streaming tensor-core kernel's layout whenever that kernel can take the weight
+    const bool t = (type == PG_GGUF_Q4_0 || type == PG_GGUF_Q8_0) && k >= 256 && (k % 256 == 0) && !g_gguf_force_simple;
+    if (tiled) *tiled = t ? 1 : 0;
+    if (t) return (size_t)((rows + 15) / 16) * (size_t)(nblk / 8) * (size_t)(16 * (type == PG_GGUF_Q8_0 ? 256 : 128) + 256);
+    return (size_t)rows * nblk * (type == PG_GGUF_Q8_0 ? 32 : 16);
+}
+
+// w->d_qs must hold pgk_gguf_qs_bytes(...) bytes
 int32_t pgk_gguf_repack(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t n, int64_t k, pg_gguf_weight *w)
 {
     const int64_t num_blocks = n * (k / 32);
     if (num_blocks == 0) return PG_OK;
     int64_t blocks = (num_blocks + 7) / 8;
     if (blocks > (int64_t)ctx->sm_count * 64) blocks = (int64_t)ctx->sm_count * 64;
-    // the tensor-core kernel's layout whenever that kernel can take the weight (its shape test)
-    w->interleaved = (type == PG_GGUF_Q4_0 || type == PG_GGUF_Q8_0) && k >= 256 && (k % 256 == 0);
-    repack_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(type, w->interleaved, d_raw, num_blocks, w->d_qs, w->d_d, w->d_m);
+    int tiled = 0;
+    const size_t qbytes = pgk_gguf_qs_bytes(type, n, k, &tiled);
+    w->tiled = tiled;
+    if (tiled && (n & 15)) PG_CUDA(cudaMemsetAsync(w->d_qs, 0, qbytes, ctx->stream));   // rows past N of the last tile
+    repack_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(type, tiled, d_raw, num_blocks, (int)(k / 32), w->d_qs, w->d_d, w->d_m);
     PG_LAUNCHED();
     return PG_OK;
 }
-
-static int g_gguf_force_simple = 0;
-extern "C" PG_API void pg_tune_gguf_simple(int on) { g_gguf_force_simple = on; }
 
 int32_t pgk_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y)
 {
     if (m == 0 || w->n == 0) return PG_OK;
     PG_REQUIRE(((uintptr_t)d_x & 15) == 0, "matmul_gguf: x must be 16-byte aligned");
-    if (!g_gguf_force_simple && pgk_matmul_gguf_mma_supports(w, m) && ((uintptr_t)d_x & 15) == 0) return pgk_matmul_gguf_mma(ctx, d_x, m, w, d_y);
+    if (w->tiled) return pgk_matmul_gguf_stream(ctx, d_x, m, w, d_y);
     switch (w->type) {
         case PG_GGUF_Q8_0: return launch_matmul<PG_GGUF_Q8_0>(ctx, d_x, m, w, d_y);
         case PG_GGUF_Q4_0: return launch_matmul<PG_GGUF_Q4_0>(ctx, d_x, m, w, d_y);

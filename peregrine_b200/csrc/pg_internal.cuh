@@ -175,7 +175,10 @@ struct pg_gguf_weight {
     uint8_t *d_qs = nullptr;
     uint16_t *d_d = nullptr;
     uint16_t *d_m = nullptr;
-    int interleaved = 0;        // quants stored in the tensor-core kernel's chunk order (see repack_kernel)
+    // tiled = 1 (Q4_0 / Q8_0 with K % 256 == 0): d_qs holds the streaming kernel's layout instead of the planes above --
+    // one contiguous "fill" per (tile of 16 rows, slice of 8 blocks): 16 rows x {128, 256} quant bytes, then 16 rows x
+    // eight f16 scales (csrc/pg_gguf.cu: repack_kernel).  Rows past N are zero.
+    int tiled = 0;
 };
 
 // ---- exchange between the GPUs of a node (csrc/pg_peer.cu) ----------------------------------------------------
@@ -434,9 +437,11 @@ int32_t pgk_dequant_blocks(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int6
 int32_t pgk_f16_to_f32(pg_ctx *ctx, const uint16_t *d_bits, int64_t count, float *d_out);
 int32_t pgk_gguf_repack(pg_ctx *ctx, int32_t type, const uint8_t *d_raw, int64_t n, int64_t k, pg_gguf_weight *w);
 int32_t pgk_matmul_gguf(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
-// pg_gguf_mma.cu
-bool pgk_matmul_gguf_mma_supports(const pg_gguf_weight *w, int64_t m);
-int32_t pgk_matmul_gguf_mma(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
+// pg_gguf_stream.cu
+bool pgk_matmul_gguf_stream_supports(const pg_gguf_weight *w, int64_t m);
+int32_t pgk_matmul_gguf_stream(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w, float *d_y);
+// bytes of d_qs for `rows` rows of `k` columns, and whether the tiled layout applies
+size_t pgk_gguf_qs_bytes(int32_t type, int64_t rows, int64_t k, int *tiled);
 
 // ------------------------------------------------------- device helpers ----
 // Rust `(v.round().clamp(-127.0, 127.0)) as i8`: roundf is half away from zero; the
