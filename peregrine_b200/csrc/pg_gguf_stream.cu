@@ -418,7 +418,6 @@ int32_t gs_launch(pg_ctx *ctx, const float *d_x, int M, int m0, int rows, const 
     // warps per tile: as few as still give about three quarters of the GPU's warps a part of a tile
     int kw = 1;
     while (kw < 8 && tiles * kw * 4 < (int64_t)ctx->sm_count * W * 3) kw *= 2;
-    const int groups = W / kw;
     // tiles go round the CTAs first (tile = CTA + grid * group), so with every SM in the grid a CTA has at most one busy group
     // more than another: 896 tiles on 148 SMs are 6 or 7 busy groups of 8 per CTA, not 8 on 112 SMs and 36 SMs idle
     // (this kernel is bound by instruction issue: 15.0 against 15.9 us at N 14336, K 4096, one row)

@@ -47,6 +47,26 @@ def test_library_exports_every_declared_symbol():
     assert exported == sorted(declared + knobs), sorted(set(exported) ^ set(declared + knobs))
 
 
+def test_rust_binding_covers_the_header():
+    """rust/peregrine-b200-sys/src/lib.rs (generated, uncompiled) names every function of both headers with as many
+    parameters as the C declaration has, and regenerating it changes nothing."""
+    import importlib.util
+
+    path = os.path.join(ROOT, "rust", "peregrine-b200-sys")
+    rs = open(os.path.join(path, "src", "lib.rs")).read()
+    rust = {m.group(1): m.group(2) for m in re.finditer(r"pub fn (pg_\w+)\(([^)]*)\)", rs, flags=re.S)}
+    spec = importlib.util.spec_from_file_location("gen_bindings", os.path.join(path, "gen_bindings.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    for header in ("peregrine_b200.h", "peregrine_b200_tune.h"):
+        funcs, _ = gen.parse(os.path.join(ROOT, "include", header))
+        assert sorted(f[0] for f in funcs) == _header_symbols(header)
+        for name, params, _ret in funcs:
+            assert name in rust, f"{name} missing from the Rust binding"
+            n_rust = len([a for a in rust[name].split(",") if a.strip()])
+            assert n_rust == len(params), f"{name}: {n_rust} parameters in Rust, {len(params)} in C"
+
+
 def test_errors_are_reported_not_thrown():
     from peregrine_b200 import _lib
 
