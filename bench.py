@@ -441,10 +441,12 @@ def run_ours(args):
         achieved = kern_bytes / (k_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "gemv_wstream_kernel", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": achieved / hbm_peak,
-                    # dram__bytes_read + dram__bytes_write of one ncu capture of this kernel (K 4096, N 32768, M 16:
-                    # 139.3 MB for 136.5 MB algorithmic), scaled by the bytes
-                    # an average launch of the sweep moves (traffic grows in proportion to K*N)
-                    "traffic": 1.02 * kern_bytes / 9, "traffic_source": "ncu capture scaled by algorithmic bytes",
+                    # DRAM bytes (read + write) of this kernel under ncu: 139.3 MB for 136.5 MB algorithmic at K 4096,
+                    # N 32768, M 16 (1.02 x), and 58.9 MB for 59.8 MB at K 4096, N 14336, M 16, a case of this sweep
+                    # (0.99 x: part of y is still in L2 when the kernel ends).  The larger ratio, scaled by the bytes an
+                    # average launch of the sweep moves (traffic grows in proportion to K * N)
+                    "traffic": 1.02 * kern_bytes / 9,
+                    "traffic_source": "ncu captures of gemv_wstream_kernel (profiles/), ratio to algorithmic bytes 0.99-1.02, scaled",
                     "peak_source": peak_src,
                     "bytes_per_launch_avg": kern_bytes / 9, "us_per_launch_avg": k_ms * 1e3 / 9,
                     "how": f"{reps} replays of a graph holding only the nine product launches, CUDA events on the launch stream"}

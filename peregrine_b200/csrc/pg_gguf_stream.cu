@@ -14,6 +14,9 @@
 //     not fit) and the block's f16 scale is applied to the one result.  Q4_0's offset, sum((q - 8) xi) =
 //     sum(q xi) - 8 sum(xi), enters as the accumulator input of the digit-0 MMA;
 //   * per slice the sums are multiplied by 2^-s and added to the tile's f32 accumulators.
+//   * one or two activation rows: the three digits of a row travel as three COLUMNS of one B operand (column 3 m + l), so a
+//     block is ONE MMA; the per-digit sums are scaled and accumulated in f32 as they are and joined (x 1, 256, 65536) once
+//     per tile.  (12.0 / 13.7 us against 15.0 / 15.8 us for Q4_0 / Q8_0 at N 14336, K 4096, one row.)
 // Against the reference's sequential f32 loop this differs in summation order and in the 2^-22 (of the slice maximum)
 // rounding of the activations: tolerance 1e-5 of max|y|.  A slice holding a non-finite activation makes that activation
 // row's outputs NaN (the reference gives inf or NaN there).
@@ -53,12 +56,13 @@ constexpr int GS_MAX_SLICES = 64;
 // boundaries are not what the eight-row case pays for.)
 constexpr int GS_US_BYTES = GS_MAX_SLICES * 8 * 4 * 2;   // [slice][8] 2^-s, then [slice][8] NaN-or-zero markers
 
-template <int TYPE, int W>
+template <int TYPE, int W, bool SMALL>
 struct GsCfg {
     static constexpr int WARPS = W, THREADS = W * 32;
     static constexpr int PLANES_BYTES = 48 * 1024;                           // [block][plane][row][t][8 B]: rows * blocks <= 512
     static constexpr int ROW_SLICES = PLANES_BYTES / 768;                    // rows * slices of a chunk
-    static constexpr int OFF_BYTES = (TYPE == PG_GGUF_Q4_0) ? PLANES_BYTES / 24 : 0;   // Q4_0: [block][row] -8 * sum(xi)
+    // Q4_0: [block][row] -8 * sum(xi); SMALL: [block][4 * rows] -8 * sum(digit) per (row, digit) column
+    static constexpr int OFF_BYTES = (TYPE == PG_GGUF_Q4_0) ? (SMALL ? PLANES_BYTES / 6 : PLANES_BYTES / 24) : 0;
     static constexpr int QB = (TYPE == PG_GGUF_Q4_0) ? 16 : 32;            // quant bytes per block
     static constexpr int SEG = GS_SLICE * QB;                                // quant bytes per row and fill
     static constexpr int SCALE_OFF = 16 * SEG;                               // [16 rows][16 B]
@@ -141,7 +145,9 @@ __device__ __forceinline__ void gs_mma(int (&d)[4], uint32_t a0, uint32_t a1, ui
 // its lane i holds elements 8i..8i+7 of the slice = elements 8t..8t+7 (t = i % 4) of block i / 4: exactly what fragment
 // lane (row, t) of that block needs.  B operand order inside a block (the order in which the weight side presents k):
 //   Q8_0: b0 = elements 8t+0..3, b1 = elements 8t+4..7;  Q4_0: b0 = elements 8t+{0,2,4,6}, b1 = elements 8t+{1,3,5,7}.
-template <int TYPE, int W>
+// SMALL (one or two activation rows): the three digits of a row are three COLUMNS of one B operand (column 3 m + l), so a
+// block needs one MMA instead of three: planes [block][3 * rows columns][t][8 B], offsets [block][4 * rows] per column.
+template <int TYPE, int W, bool SMALL>
 __device__ __forceinline__ void gs_build_planes(const float *__restrict__ x, int M, int m0, int rows, int cslices, int nblk_row, int blk0,
                                                 unsigned char *planes, int *off, float *us, float *ps)
 {
@@ -212,9 +218,19 @@ __device__ __forceinline__ void gs_build_planes(const float *__restrict__ x, int
             const uint32_t sel = l == 0 ? 0x0040u : (l == 1 ? 0x0051u : 0x0062u);
             const uint32_t b0 = __byte_perm(__byte_perm(h0[0], h0[1], sel), __byte_perm(h0[2], h0[3], sel), 0x5410) ^ 0x80808080u;
             const uint32_t b1 = __byte_perm(__byte_perm(h1[0], h1[1], sel), __byte_perm(h1[2], h1[3], sel), 0x5410) ^ 0x80808080u;
-            *reinterpret_cast<uint2 *>(planes + ((size_t)(jb * 3 + l) * (rows * 4) + (m * 4 + t)) * 8) = make_uint2(b0, b1);
+            if (SMALL) {
+                *reinterpret_cast<uint2 *>(planes + ((size_t)(jb * 3 * rows + m * 3 + l) * 4 + t) * 8) = make_uint2(b0, b1);
+                if (TYPE == PG_GGUF_Q4_0) {
+                    int ds = __dp4a((int)b0, 0x01010101, __dp4a((int)b1, 0x01010101, 0));   // sum of this lane's eight digits
+                    ds += __shfl_xor_sync(0xffffffffu, ds, 1);
+                    ds += __shfl_xor_sync(0xffffffffu, ds, 2);
+                    if (t == 0) off[jb * 4 * rows + m * 3 + l] = -8 * ds;
+                }
+            } else {
+                *reinterpret_cast<uint2 *>(planes + ((size_t)(jb * 3 + l) * (rows * 4) + (m * 4 + t)) * 8) = make_uint2(b0, b1);
+            }
         }
-        if (TYPE == PG_GGUF_Q4_0 && t == 0) off[jb * rows + m] = -8 * sum;
+        if (!SMALL && TYPE == PG_GGUF_Q4_0 && t == 0) off[jb * rows + m] = -8 * sum;
         if (lane == 0) {
             us[s * 8 + m] = scalbnf(1.0f, e - 21);
             ps[s * 8 + m] = poison;
@@ -225,12 +241,12 @@ __device__ __forceinline__ void gs_build_planes(const float *__restrict__ x, int
 
 // Shared memory: planes | Q4_0: offsets | us, ps | rings [warp][slot] | partial sums | mbarriers [warp][slot] | abort flag
 // Warp w: tile slot w / kw, K part w % kw (8 / kw slices of every chunk).  CTA b, slot s: tiles b + grid * (s + (16 / kw) * j).
-template <int TYPE, int W>
+template <int TYPE, int W, bool SMALL>
 __global__ void __launch_bounds__(W * 32, 1)
     gguf_stream_kernel(const float *__restrict__ x, const uint8_t *__restrict__ qs, int64_t N, int nblk_row, int M, int m0, int rows,
                        int cslices, float *__restrict__ y, int kw, int32_t *status, unsigned long long limit_ns)
 {
-    using C = GsCfg<TYPE, W>;
+    using C = GsCfg<TYPE, W, SMALL>;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -265,6 +281,10 @@ __global__ void __launch_bounds__(W * 32, 1)
     const int64_t nslices = nblk_row >> 3;
     uint32_t fills = 0;                                     // ring fills consumed so far (= issued, at chunk boundaries)
     bool ok = true;
+    // SMALL: B column of this lane (clamped to an existing one), first of its two offset columns, rows of its two C columns
+    const int ncols = 3 * rows;
+    const int bcol = g < ncols ? g : 0, ocol = 2 * t < 4 * rows ? 2 * t : 0;
+    const int ma = min((2 * t) / 3, rows - 1), mb = min((2 * t + 1) / 3, rows - 1);
 
     for (int chunk = 0; chunk < nchunks; chunk++) {
         const int blk0 = chunk * cblocks;
@@ -287,7 +307,7 @@ __global__ void __launch_bounds__(W * 32, 1)
             if (q < total) issue(q);
         if (chunk == 0) asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations come from the preceding kernel
         if (chunk > 0) __syncthreads();                     // everybody is done with the previous chunk's planes
-        gs_build_planes<TYPE, W>(x, M, m0, rows, cslices, nblk_row, blk0, planes, off, us, ps);
+        gs_build_planes<TYPE, W, SMALL>(x, M, m0, rows, cslices, nblk_row, blk0, planes, off, us, ps);
         __syncthreads();
 
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -324,50 +344,92 @@ __global__ void __launch_bounds__(W * 32, 1)
                                 r1lo = wb[2 * bi];
                                 r1hi = wb[2 * bi + 1];
                             }
-                            // B operand: this lane's activation row is g; rows that do not exist contribute zeros
-                            const uint32_t pstride = (uint32_t)rows * 32;
-                            const uint32_t pb = planes_s + (uint32_t)((s * GS_SLICE + jb) * 3) * pstride + lane * 8;
-                            uint2 x0 = make_uint2(0u, 0u), x1 = x0, x2 = x0;
-                            if (g < rows) {
-                                x0 = gs_lds64(pb);
-                                x1 = gs_lds64(pb + pstride);
-                                x2 = gs_lds64(pb + 2 * pstride);
-                            }
-                            int o0 = 0, o1 = 0;
-                            if (TYPE == PG_GGUF_Q4_0) {
-                                const uint32_t ob = off_s + (uint32_t)((s * GS_SLICE + jb) * rows + 2 * t) * 4;
-                                if (2 * t < rows) o0 = *reinterpret_cast<const int *>(gs_smem + ob);
-                                if (2 * t + 1 < rows) o1 = *reinterpret_cast<const int *>(gs_smem + ob + 4);
-                            }
-                            int c0[4], c1[4], c2[4];
-                            gs_mma<TYPE>(c0, r0lo, r1lo, r0hi, r1hi, x0.x, x0.y, o0, o1);
-                            gs_mma<TYPE>(c1, r0lo, r1lo, r0hi, r1hi, x1.x, x1.y, 0, 0);
-                            gs_mma<TYPE>(c2, r0lo, r1lo, r0hi, r1hi, x2.x, x2.y, 0, 0);
                             const uint32_t p0 = scw0[jb >> 1], p1 = scw1[jb >> 1];
                             const __half2 h0 = *reinterpret_cast<const __half2 *>(&p0), h1 = *reinterpret_cast<const __half2 *>(&p1);
                             const float d0 = (jb & 1) ? __high2float(h0) : __low2float(h0);
                             const float d1 = (jb & 1) ? __high2float(h1) : __low2float(h1);
+                            if (SMALL) {
+                                // B operand: column g = digit g % 3 of activation row g / 3 (columns past 3 * rows: any data)
+                                const uint32_t pb = planes_s + (uint32_t)((s * GS_SLICE + jb) * ncols + bcol) * 32 + t * 8;
+                                const uint2 xd = gs_lds64(pb);
+                                uint2 o = make_uint2(0u, 0u);
+                                if (TYPE == PG_GGUF_Q4_0) o = gs_lds64(off_s + (uint32_t)((s * GS_SLICE + jb) * 4 * rows + ocol) * 4);
+                                int c[4];
+                                gs_mma<TYPE>(c, r0lo, r1lo, r0hi, r1hi, xd.x, xd.y, (int)o.x, (int)o.y);
 #pragma unroll
-                            for (int v = 0; v < 4; v++) {
-                                const int hi = c2[v] * 256 + c1[v];
-                                float cf;
-                                if (TYPE == PG_GGUF_Q4_0)
-                                    cf = __int2float_rn((int)((uint32_t)hi * 256u + (uint32_t)c0[v]));   // |sum((q - 8) xi)| <= 2^30
-                                else
-                                    cf = fmaf(__int2float_rn(hi), 256.0f, __int2float_rn(c0[v]));
-                                as[v] = fmaf(v < 2 ? d0 : d1, cf, as[v]);
+                                for (int v = 0; v < 4; v++) as[v] = fmaf(v < 2 ? d0 : d1, __int2float_rn(c[v]), as[v]);
+                            } else {
+                                // B operand: this lane's activation row is g; rows that do not exist contribute zeros
+                                const uint32_t pstride = (uint32_t)rows * 32;
+                                const uint32_t pb = planes_s + (uint32_t)((s * GS_SLICE + jb) * 3) * pstride + lane * 8;
+                                uint2 x0 = make_uint2(0u, 0u), x1 = x0, x2 = x0;
+                                if (g < rows) {
+                                    x0 = gs_lds64(pb);
+                                    x1 = gs_lds64(pb + pstride);
+                                    x2 = gs_lds64(pb + 2 * pstride);
+                                }
+                                int o0 = 0, o1 = 0;
+                                if (TYPE == PG_GGUF_Q4_0) {
+                                    const uint32_t ob = off_s + (uint32_t)((s * GS_SLICE + jb) * rows + 2 * t) * 4;
+                                    if (2 * t < rows) o0 = *reinterpret_cast<const int *>(gs_smem + ob);
+                                    if (2 * t + 1 < rows) o1 = *reinterpret_cast<const int *>(gs_smem + ob + 4);
+                                }
+                                int c0[4], c1[4], c2[4];
+                                gs_mma<TYPE>(c0, r0lo, r1lo, r0hi, r1hi, x0.x, x0.y, o0, o1);
+                                gs_mma<TYPE>(c1, r0lo, r1lo, r0hi, r1hi, x1.x, x1.y, 0, 0);
+                                gs_mma<TYPE>(c2, r0lo, r1lo, r0hi, r1hi, x2.x, x2.y, 0, 0);
+#pragma unroll
+                                for (int v = 0; v < 4; v++) {
+                                    const int hi = c2[v] * 256 + c1[v];
+                                    float cf;
+                                    if (TYPE == PG_GGUF_Q4_0)
+                                        cf = __int2float_rn((int)((uint32_t)hi * 256u + (uint32_t)c0[v]));   // |sum((q - 8) xi)| <= 2^30
+                                    else
+                                        cf = fmaf(__int2float_rn(hi), 256.0f, __int2float_rn(c0[v]));
+                                    as[v] = fmaf(v < 2 ? d0 : d1, cf, as[v]);
+                                }
                             }
                         }
                     }
                     // the slice's sums back on the activations' scale; NaN for a row whose slice held a non-finite value
-                    const uint2 u = gs_lds64(us_s + (uint32_t)(s * 8 + 2 * t) * 4), pz = gs_lds64(ps_s + (uint32_t)(s * 8 + 2 * t) * 4);
-                    acc[0] += as[0] * __uint_as_float(u.x) + __uint_as_float(pz.x);
-                    acc[1] += as[1] * __uint_as_float(u.y) + __uint_as_float(pz.y);
-                    acc[2] += as[2] * __uint_as_float(u.x) + __uint_as_float(pz.x);
-                    acc[3] += as[3] * __uint_as_float(u.y) + __uint_as_float(pz.y);
+                    if (SMALL) {
+                        // this lane's columns 2t, 2t+1 belong to activation rows ma, mb
+                        const float ua = *reinterpret_cast<const float *>(gs_smem + us_s + (uint32_t)(s * 8 + ma) * 4);
+                        const float ub = *reinterpret_cast<const float *>(gs_smem + us_s + (uint32_t)(s * 8 + mb) * 4);
+                        const float za = *reinterpret_cast<const float *>(gs_smem + ps_s + (uint32_t)(s * 8 + ma) * 4);
+                        const float zb = *reinterpret_cast<const float *>(gs_smem + ps_s + (uint32_t)(s * 8 + mb) * 4);
+                        acc[0] += as[0] * ua + za;
+                        acc[1] += as[1] * ub + zb;
+                        acc[2] += as[2] * ua + za;
+                        acc[3] += as[3] * ub + zb;
+                    } else {
+                        const uint2 u = gs_lds64(us_s + (uint32_t)(s * 8 + 2 * t) * 4), pz = gs_lds64(ps_s + (uint32_t)(s * 8 + 2 * t) * 4);
+                        acc[0] += as[0] * __uint_as_float(u.x) + __uint_as_float(pz.x);
+                        acc[1] += as[1] * __uint_as_float(u.y) + __uint_as_float(pz.y);
+                        acc[2] += as[2] * __uint_as_float(u.x) + __uint_as_float(pz.x);
+                        acc[3] += as[3] * __uint_as_float(u.y) + __uint_as_float(pz.y);
+                    }
                     __syncwarp();                           // every lane has read the slot
                     if (q + C::SLOTS < total) issue(q + C::SLOTS);
                 }
+            }
+            if (SMALL) {
+                // join the digits: row 0 = columns 0, 1, 2 (lane t = 0: acc[0], acc[1]; t = 1: acc[0]), row 1 = columns 3, 4, 5
+                // (t = 1: acc[1]; t = 2: acc[0], acc[1]); the results go where the store below expects rows 0 and 1: lane t = 0
+                const int q4 = lane & ~3;
+                float r0[2], r1[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {               // weight rows g and g + 8
+                    const float a0 = acc[2 * h], a1 = acc[2 * h + 1];
+                    const float t1a0 = __shfl_sync(0xffffffffu, a0, q4 + 1), t1a1 = __shfl_sync(0xffffffffu, a1, q4 + 1);
+                    const float t2a0 = __shfl_sync(0xffffffffu, a0, q4 + 2), t2a1 = __shfl_sync(0xffffffffu, a1, q4 + 2);
+                    r0[h] = fmaf(t1a0, 65536.0f, fmaf(a1, 256.0f, a0));
+                    r1[h] = fmaf(t2a1, 65536.0f, fmaf(t2a0, 256.0f, t1a1));
+                }
+                acc[0] = r0[0];
+                acc[1] = r1[0];
+                acc[2] = r0[1];
+                acc[3] = r1[1];
             }
             // the kw warps of the tile add up in the first one (fixed order); two buffers by tile parity, so that one barrier
             // per tile is enough
@@ -405,12 +467,12 @@ __global__ void __launch_bounds__(W * 32, 1)
     }
 }
 
-template <int TYPE, int W>
+template <int TYPE, int W, bool SMALL>
 int32_t gs_launch(pg_ctx *ctx, const float *d_x, int M, int m0, int rows, const pg_gguf_weight *w, float *d_y)
 {
-    using C = GsCfg<TYPE, W>;
+    using C = GsCfg<TYPE, W, SMALL>;
     static_assert(C::SMEM <= 227 * 1024, "shared memory budget");
-    auto kern = gguf_stream_kernel<TYPE, W>;
+    auto kern = gguf_stream_kernel<TYPE, W, SMALL>;
     static std::atomic<uint64_t> smem_set{0};
     PG_CUDA(pg_max_smem_once(kern, C::SMEM, ctx->device, smem_set));
     const int nblk = (int)(w->k / 32);
@@ -446,7 +508,7 @@ int32_t gs_run(pg_ctx *ctx, const float *d_x, int64_t m, const pg_gguf_weight *w
     const int M = (int)m;
     for (int m0 = 0; m0 < M; m0 += 8) {
         const int rows = std::min(8, M - m0);
-        const int32_t rc = gs_launch<TYPE, 16>(ctx, d_x, M, m0, rows, w, d_y);
+        const int32_t rc = rows <= 2 ? gs_launch<TYPE, 16, true>(ctx, d_x, M, m0, rows, w, d_y) : gs_launch<TYPE, 16, false>(ctx, d_x, M, m0, rows, w, d_y);
         if (rc != PG_OK) return rc;
     }
     return PG_OK;
