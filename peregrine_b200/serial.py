@@ -23,6 +23,7 @@ it asserts (`expected dtype=1`, `quantized tensors must be 2D`) this raises `Ser
 from __future__ import annotations
 
 import ctypes as C
+import os
 import struct
 from typing import BinaryIO, List, Optional, Sequence, Tuple
 
@@ -214,6 +215,60 @@ def convert_weights_int8(input_path: str, output_path: str, gpu: Optional[GpuCon
                 f.write(data.astype("<f4", copy=False).tobytes())
 
 
+def _walk(path: str, typed: bool) -> bool:
+    """True when the file's records, read as typed (a dtype byte after every name) or as plain f32 records, follow one
+    another consistently and end exactly at the end of the file.  Only headers are read."""
+    size = os.path.getsize(path)
+    try:
+        with open(path, "rb") as f:
+            (count,) = struct.unpack("<I", _read_exact(f, 4))
+            for _ in range(count):
+                (name_len,) = struct.unpack("<I", _read_exact(f, 4))
+                if name_len > size:
+                    return False
+                _read_exact(f, name_len).decode("utf-8")
+                dtype = _read_exact(f, 1)[0] if typed else 0
+                (ndim,) = struct.unpack("<I", _read_exact(f, 4))
+                if ndim > 8:
+                    return False
+                shape = struct.unpack(f"<{ndim}I", _read_exact(f, 4 * ndim))
+                n = int(np.prod(shape, dtype=np.int64)) if shape else 1
+                if dtype == 0:
+                    skip = 4 * n
+                elif dtype == 1 and ndim == 2:
+                    skip = n + 4 * shape[1]
+                elif dtype == 3 and ndim == 2:
+                    f.seek(256, 1)
+                    (streams,) = struct.unpack("<I", _read_exact(f, 4))
+                    if streams > size:
+                        return False
+                    f.seek(4 * streams, 1)
+                    skip = sum(struct.unpack(f"<{streams}I", _read_exact(f, 4 * streams))) + 4 * shape[1]
+                else:
+                    return False
+                if f.tell() + skip > size:
+                    return False
+                f.seek(skip, 1)
+            return f.tell() == size
+    except (ValueError, struct.error, UnicodeDecodeError):
+        return False
+
+
+def file_kind(path: str) -> str:
+    """"typed" (records with a dtype byte, scripts/convert_weights_int8.py) or "plain" (serial::save_model).  The two
+    layouts differ by one byte per record, so the whole chain of record headers is followed under each reading and must
+    end at the end of the file; the reference's script looks at one byte of each record instead and takes the rank of a
+    plain tensor for a dtype.  A file that fits neither reading, or both, is refused."""
+    typed, plain = _walk(path, True), _walk(path, False)
+    if typed == plain:
+        with open(path, "rb") as f:
+            empty = os.path.getsize(path) == 4 and f.read(4) == b"\0\0\0\0"
+        if empty:
+            return "plain"
+        raise SerialPanic(f"{path}: " + ("reads both as a typed and as a plain model file" if typed else "neither a typed nor a plain model file"))
+    return "typed" if typed else "plain"
+
+
 def convert_huffman(input_path: str, output_path: str, num_streams: int = 4, limit_lengths: bool = False,
                     gpu: Optional[GpuContext] = None) -> None:
     """scripts/convert_huffman.py: a typed file (or a plain f32 model file) -> a file of Huffman records for its 2-D
@@ -223,23 +278,17 @@ def convert_huffman(input_path: str, output_path: str, num_streams: int = 4, lim
     from .huffman import HuffmanTensor
     from .quant import quantize_weights
 
-    with open(input_path, "rb") as f:
-        head = f.read(16)
-    (count,) = struct.unpack("<I", head[:4])
-    (name_len,) = struct.unpack("<I", head[4:8]) if count else (0,)
-    with open(input_path, "rb") as f:
-        f.seek(8 + name_len)
-        tag = f.read(5)
-    # After the first name a plain f32 file holds the rank as a u32 (bytes r 0 0 0), a typed file the dtype byte and then
-    # the rank (bytes d r 0 0 0): the second byte is zero in the one and the rank in the other.  (The script looks at the
-    # first byte only and so takes the rank of a plain 2-D tensor for a dtype.)
-    typed = count > 0 and len(tag) == 5 and tag[1] != 0
+    kind = file_kind(input_path)
     records: List[Tuple[str, QuantizedTensor]] = []
-    if typed:
+    if kind == "typed":
         for name, item in load_typed_model(input_path, gpu):
             if isinstance(item, QuantizedTensor):
                 records.append((name, item))
-            elif not isinstance(item, tuple):
+            elif isinstance(item, tuple):
+                shape, data = item
+                if len(shape) == 2:               # an f32 record of a typed file: quantised like a plain file's tensor
+                    records.append((name, quantize_weights(data, shape[0], shape[1], gpu)))
+            else:
                 raise ValueError(f"Unsupported dtype for conversion: tensor '{name}'")
     else:
         for name, shape, data in load_model(input_path):

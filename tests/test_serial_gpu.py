@@ -50,3 +50,39 @@ def test_product_from_a_tensor_read_back(pg, gpu, oracle_mt, m, k, n):
     assert bits_equal(pg.quant.matmul_quantized(x, m, k, b, gpu), out_o)
     a.free_gpu()
     b.free_gpu()
+
+
+def test_convert_huffman_from_a_mixed_typed_file(pg, gpu, oracle_mt, tmp_path):
+    """A typed file as scripts/convert_weights_int8.py writes it, with an f32 scalar first, an f32 matrix (a 2-D tensor
+    whose name has no ".weight": the int8 converter leaves it f32), an i8 record and an f32 vector: the Huffman file must
+    hold the i8 tensor as it is and the f32 matrix quantised per column, and leave the scalar and the vector out."""
+    import struct
+
+    g = np.random.Generator(np.random.PCG64(77))
+    k, n = 48, 40
+    w_i8 = (g.standard_normal((k, n)) * 0.05).astype(np.float32)
+    w_f32 = (g.standard_normal((24, 16)) * 0.05).astype(np.float32)
+    ref_i8 = oracle_mt.quantize_weights(w_i8, k, n)
+    ref_f32 = oracle_mt.quantize_weights(w_f32, 24, 16)
+
+    def f32_record(name, shape, data):
+        nb = name.encode()
+        return (struct.pack("<I", len(nb)) + nb + b"\x00" + struct.pack("<I", len(shape)) + struct.pack(f"<{len(shape)}I", *shape) +
+                np.asarray(data, "<f4").tobytes())
+
+    src = tmp_path / "mixed.bin"
+    with open(src, "wb") as f:
+        f.write(struct.pack("<I", 4))
+        f.write(f32_record("step", [], [3.0]))
+        f.write(f32_record("proj.kernel", [24, 16], w_f32))
+        pg.serial.write_quantized_tensor(f, "blk.weight", pg.quant.QuantizedTensor(ref_i8.data_i8, ref_i8.data_i8_t, ref_i8.scales, k, n))
+        f.write(f32_record("blk.bias", [n], np.zeros(n)))
+    assert pg.serial.file_kind(str(src)) == "typed"
+    out = tmp_path / "mixed_huff.bin"
+    pg.serial.convert_huffman(str(src), str(out), 3, limit_lengths=True, gpu=gpu)
+    got = pg.serial.load_typed_model(str(out), gpu)
+    assert [name for name, _ in got] == ["proj.kernel", "blk.weight"]
+    for (name, ht), ref in zip(got, (ref_f32, ref_i8)):
+        qt = ht.decode_to_quantized(gpu)
+        assert np.array_equal(np.asarray(qt.data_i8).reshape(-1), ref.data_i8.reshape(-1)), name
+        assert bits_equal(qt.scales, ref.scales), name
