@@ -196,6 +196,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 {
     using C = Cfg<BN, AR>;
     constexpr int STAGES = C::STAGES;
+    // Programmatic dependent launch: the next kernel may start its prologue now, and this one started while its
+    // predecessor (the activation quantiser) was still running.  What the predecessor wrote -- the activations and their
+    // scales -- is touched only behind griddepcontrol.wait; the weights are requested before it.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -239,15 +243,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // the weight tiles of the first stages of this CTA's first tile, before the predecessor has finished
+            int early = 0;
+            if ((int)blockIdx.x < total_tiles) {
+                const int n0 = ((int)blockIdx.x / tiles_m) * BN;
+                early = kblocks < STAGES ? kblocks : STAGES;
+                for (int kb = 0; kb < early; kb++) {
+                    mbar_arrive_expect_tx(bar_full + 8 * kb, C::STAGE);
+                    tma_load_2d(base + kb * C::STAGE + C::STAGE_A, &tmap_b, bar_full + 8 * kb, kb * BK, n0);
+                }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
                 const int m0 = (t % tiles_m) * BM;
                 const int n0 = (t / tiles_m) * BN;
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status))) break;
                     const uint32_t sa = base + stage * C::STAGE;
-                    mbar_arrive_expect_tx(bar_full + 8 * stage, C::STAGE);
+                    if (early > 0) {
+                        early--;                            // announced and half filled above
+                    } else {
+                        mbar_arrive_expect_tx(bar_full + 8 * stage, C::STAGE);
+                        tma_load_2d(sa + C::STAGE_A, &tmap_b, bar_full + 8 * stage, kb * BK, n0);
+                    }
                     tma_load_2d(sa, &tmap_a, bar_full + 8 * stage, kb * BK, m0);
-                    tma_load_2d(sa + C::STAGE_A, &tmap_b, bar_full + 8 * stage, kb * BK, n0);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -301,6 +320,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;  // TMEM lane quarter this warp may read
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // a_scales come from the predecessor; y may still be read by it
         uint32_t acc = 0, acc_phase = 0;
         const bool vec_ok = ((N & 3) == 0) && (((uintptr_t)y & 15) == 0) && (((uintptr_t)acc_out & 15) == 0) &&
                             (((uintptr_t)w_scales & 15) == 0);
@@ -423,8 +443,18 @@ int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, 
     PG_CUDA(pg_max_smem_once(kern, (int)C::SMEM, ctx->device, smem_set));
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kern<<<grid, NUM_THREADS, C::SMEM, ctx->stream>>>(ta, *reinterpret_cast<CUtensorMap *>(w->tmap_b), d_as, w->d_scales, M, N, K,
-                                                     d_y, d_acc, ctx->d_status);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PG_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, *reinterpret_cast<CUtensorMap *>(w->tmap_b), d_as, (const float *)w->d_scales, M, N, K,
+                               d_y, d_acc, ctx->d_status));
     PG_LAUNCHED();
     return PG_OK;
 }

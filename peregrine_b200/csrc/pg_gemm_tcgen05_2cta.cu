@@ -162,6 +162,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 const float *__restrict__ a_scales, const float *__restrict__ w_scales, int M, int N, int K,
                                 float *__restrict__ y, int32_t *__restrict__ acc_out, int32_t *status)
 {
+    // programmatic dependent launch: see gemm_i8_tcgen05_kernel; the predecessor's output (activations, their scales) is
+    // touched only behind griddepcontrol.wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -212,6 +215,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // this CTA's half of the weight tiles of the first stages of the first tile, before the predecessor has finished
+            // (a stage's barrier may get the bytes of the other CTA before the leader has announced them: the transaction
+            // count is signed inside a phase, and the phase cannot complete before the leader's arrival)
+            int early = 0;
+            if (pair < total_tiles) {
+                const int n0 = (pair / tiles_m) * TN + (int)rank * TNH;
+                early = kblocks < STAGES ? kblocks : STAGES;
+                for (int kb = 0; kb < early; kb++) {
+                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * kb, 2 * STAGE);
+                    tma_load_2d_pair(base + kb * STAGE + STAGE_A, &tmap_b, mapa(bar_full + 8 * kb, 0), kb * BK, n0);
+                }
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int t = pair; ok && t < total_tiles; t += npairs) {
                 const int m0 = (t % tiles_m) * (2 * TM) + (int)rank * TM;
                 const int n0 = (t / tiles_m) * TN + (int)rank * TNH;
@@ -219,9 +235,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status))) break;
                     const uint32_t sa = base + stage * STAGE;
                     const uint32_t full_leader = mapa(bar_full + 8 * stage, 0);
-                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * STAGE);  // the bytes of both CTAs
+                    if (early > 0) {
+                        early--;                            // announced and half filled above
+                    } else {
+                        if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * STAGE);  // the bytes of both CTAs
+                        tma_load_2d_pair(sa + STAGE_A, &tmap_b, full_leader, kb * BK, n0);
+                    }
                     tma_load_2d_pair(sa, &tmap_a, full_leader, kb * BK, m0);
-                    tma_load_2d_pair(sa + STAGE_A, &tmap_b, full_leader, kb * BK, n0);
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -272,6 +292,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     } else {
         // ---------------------------------------------------------------- epilogue (both CTAs)
         const int q = warp & 3;
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // a_scales come from the predecessor; y may still be read by it
         uint32_t acc = 0, acc_phase = 0;
         const bool vec_ok = ((N & 3) == 0) && (((uintptr_t)y & 15) == 0) && (((uintptr_t)acc_out & 15) == 0) &&
                             (((uintptr_t)w_scales & 15) == 0);
@@ -391,13 +412,15 @@ int32_t pgk_gemm_i8_tcgen05_2cta(pg_ctx *ctx, const int8_t *d_a, const float *d_
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     PG_CUDA(cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_2cta_kernel, ta, *reinterpret_cast<CUtensorMap *>(w->tmap_b), d_as,
                                (const float *)w->d_scales, M, N, K, d_y, d_acc, ctx->d_status));
     PG_LAUNCHED();

@@ -534,19 +534,29 @@ __global__ void __launch_bounds__(1024) gqa_combine_quant_kernel(const float *__
     }
     __syncthreads();
     const float denom = den[threadIdx.y];
-    // eight running sums (slice s goes to sum s % 8), added up in a fixed order at the end: eight loads are in flight per
-    // thread instead of a chain of S, and the order of the additions depends on S alone, not on how the heads are
-    // spread over CTAs or ranks
-    float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s0 = 0; s0 < S; s0 += 8) {
-        float v[8];
+    float acc = 0.0f;
+    if (S <= 16) {
+        // a short chain (13 slices at batch 16, context 2048 on one GPU): measured 3 us per layer faster than the form below
+#pragma unroll 4
+        for (int s = 0; s < S; s++) {
+            const float e = wgt[threadIdx.y][s];
+            if (e != 0.0f) acc = fmaf(e, pg_ld_fresh(po + (int64_t)s * 128 + d), acc);
+        }
+    } else {
+        // eight running sums (slice s goes to sum s % 8), added up in a fixed order at the end: eight loads are in flight
+        // per thread instead of a chain of S (a rank of a sharded step cuts its few heads into 27 to 34 slices), and the
+        // order of the additions depends on S alone, not on how the heads are spread over CTAs or ranks
+        float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int s0 = 0; s0 < S; s0 += 8) {
+            float v[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) v[j] = (s0 + j < S && wgt[threadIdx.y][s0 + j] != 0.0f) ? pg_ld_fresh(po + (int64_t)(s0 + j) * 128 + d) : 0.0f;
+            for (int j = 0; j < 8; j++) v[j] = (s0 + j < S && wgt[threadIdx.y][s0 + j] != 0.0f) ? pg_ld_fresh(po + (int64_t)(s0 + j) * 128 + d) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-            if (s0 + j < S) part[j] = fmaf(wgt[threadIdx.y][s0 + j], v[j], part[j]);
+            for (int j = 0; j < 8; j++)
+                if (s0 + j < S) part[j] = fmaf(wgt[threadIdx.y][s0 + j], v[j], part[j]);
+        }
+        acc = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
     }
-    const float acc = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
     const float o = (denom > 0.0f) ? __fdiv_rn(acc, denom) : 0.0f;
     const int64_t at = ((int64_t)b * Hq + qh) * 128 + d;
     if (out) out[at] = o;
