@@ -619,6 +619,44 @@ def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
                                                   "frac_of_4500_nominal": tops / 4500.0}
             lib.pg_qtensor_free(gpu.handle, h)
             del x, wq, y, q
+    # per-shape table of the decode and mid-batch products (quantiser + product, the library's own kernel choice): every
+    # shape with enough copies of its weights (>= 134 MB) walked in one graph, so that no copy is found in L2
+    table = {}
+    with torch.cuda.stream(stream):
+        for (k, n) in SHAPES:
+            ncopies = max(3, -(-134_000_000 // (k * n)))
+            sc = torch.rand(n, dtype=torch.float32, device=dev) * 1e-3
+            copies = []
+            for _ in range(ncopies):
+                wq = torch.randint(-127, 128, (n * k + 1024,), dtype=torch.int8, device=dev)
+                h = _lib.C.c_void_p()
+                _lib.check(lib.pg_qtensor_wrap(gpu.handle, None, wq.data_ptr(), sc.data_ptr(), k, n, _lib.C.byref(h)))
+                copies.append((h, wq))
+            for m in (1, 4, 16, 17, 64, 128):
+                x = torch.from_numpy(g.standard_normal((m, k), dtype=np.float32)).to(dev)
+                y = torch.empty(m, n, dtype=torch.float32, device=dev)
+                for h, _ in copies:
+                    _lib.check(lib.pg_matmul_quantized(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr()))
+                with gpu.record() as gg:
+                    for h, _ in copies:
+                        _lib.check(lib.pg_matmul_quantized(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr()))
+                gg.launch()
+                reps = 30
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    gg.launch()
+                e1.record(stream)
+                stream.synchronize()
+                gg.free()
+                us = e0.elapsed_time(e1) / (reps * ncopies) * 1e3
+                gbs = bytes_w8a8(m, k, n) / (us * 1e-6) / 1e9
+                table[f"M{m}_K{k}_N{n}"] = {"us": round(us, 2), "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm_peak, 3)}
+                del x, y
+            for h, _ in copies:
+                lib.pg_qtensor_free(gpu.handle, h)
+            del copies
+    out["w8a8_quantise_and_product_per_shape"] = table
     n, k = 14336, 4096
     for kind, bs in (("q4_0", 18), ("q8_0", 34)):
         # random quants under one sane f16 scale per block: the product's speed does not depend on the values

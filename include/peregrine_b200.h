@@ -64,12 +64,14 @@ typedef enum pg_gguf_type { PG_GGUF_Q4_0 = 2, PG_GGUF_Q4_1 = 3, PG_GGUF_Q8_0 = 8
 
 /* Kernel selection for pg_gemm_i8 / pg_matmul_quantized_algo. */
 typedef enum pg_gemm_algo {
-    PG_ALGO_AUTO = 0,      /* M <= 16 and K % 64 == 0: warp-stream kernel; 17 <= M <= 32 on narrow layers (and M <= 64
-                              where K % 64 != 0): per-lane streaming kernel; otherwise tcgen05; shapes none of them
-                              takes (K % 16 != 0, unaligned operands): the naive kernel */
+    PG_ALGO_AUTO = 0,      /* M <= 16 and K % 64 == 0: warp-stream kernel; 17 <= M <= 32 on narrow layers with K < 8192
+                              (and M <= 64 where K % 64 != 0): per-lane streaming kernel; otherwise tcgen05 (with K
+                              divided over CTAs where one row of tiles leaves SMs idle and K is long); shapes none of
+                              them takes (K % 16 != 0, unaligned operands): the naive kernel */
     PG_ALGO_NAIVE = 1,     /* one thread per output, dp4a; the on-device checker */
     PG_ALGO_STREAM = 2,    /* bandwidth-bound decode kernel (per-lane cp.async FIFO + int8 mma.sync), M <= 64 */
-    PG_ALGO_TCGEN05 = 3,   /* tcgen05.mma kind::i8, TMEM accumulators, TMA-fed */
+    PG_ALGO_TCGEN05 = 3,   /* tcgen05.mma kind::i8, TMEM accumulators, TMA-fed; at M <= 128 it may reserve a workspace for
+                              partial sums (context memory, grown outside graph recording like the scratch) */
     PG_ALGO_WSTREAM = 4    /* persistent decode kernel, M <= 16, K % 64 == 0: bulk copies into per-warp rings, activations
                               resident in shared memory, K split inside the CTA (and over a cluster when the
                               activations do not fit beside the rings), sums added in shared memory */

@@ -32,6 +32,8 @@ PG_API void pg_tune_wstream_cluster(int cs);
 /* tcgen05 product: tile width in columns (32, 64, 128, 256; 0 = choice); CTA pairs: 0 = choice, 1 = never, 2 = always */
 PG_API void pg_tune_tcgen05_bn(int bn);
 PG_API void pg_tune_tcgen05_pair(int mode);
+/* tcgen05 kernel at M <= 128: parts of K per tile; 0 heuristic, 1 never split, 2 / 4 / 8 that many */
+PG_API void pg_tune_tcgen05_split(int mode);
 /* GGUF weights uploaded while this is 1 keep the plain block planes and take the CUDA-core product kernel (otherwise
  * Q4_0 / Q8_0 weights with K % 256 == 0 are laid out for, and served by, the streaming tensor-core kernel) */
 PG_API void pg_tune_gguf_simple(int on);

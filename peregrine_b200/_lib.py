@@ -130,6 +130,7 @@ TUNE_SIGNATURES = {
     "pg_tune_wstream_cluster": (None, [_int]),
     "pg_tune_tcgen05_bn": (None, [_int]),
     "pg_tune_tcgen05_pair": (None, [_int]),
+    "pg_tune_tcgen05_split": (None, [_int]),
     "pg_tune_gguf_simple": (None, [_int]),
     "pg_tune_host_direct": (None, [_int, _int]),
     "pg_tune_host_push": (None, [_int]),

@@ -521,10 +521,11 @@ static int32_t gemm_dispatch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, 
             if (aligned && pgk_gemm_i8_wstream_supports(m, k, n))
                 return pgk_gemm_i8_wstream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
             // 17 <= M <= 64: the per-lane FIFO kernel's time grows with M (it is MMA-issue bound there: 25 / 33 / 56 us
-            // at M = 17 / 32 / 64 for K 4096, N 14336), the tcgen05 kernel's does not (23 us for any M <= 128), but it
-            // needs enough 64-column tiles to occupy the SMs (35 us at N = 4096, K = 14336, against 31 us at M <= 32).
+            // at M = 17 / 32 / 64 for K 4096, N 14336), the tcgen05 kernel's does not (16 us for any M <= 64).  On narrow
+            // layers with short K the two are level up to M = 32 (10.8 / 11.3 us against 11.3 / 11.5 us at K = N = 4096);
+            // with long K the tcgen05 kernel divides K over CTAs and wins (K 14336, N 4096: 22.6 against 30.8 us at M = 17).
             if (aligned && pgk_gemm_i8_stream_supports(m, k, n) &&
-                !(pgk_gemm_i8_tcgen05_supports(m, k, n) && m > 16 && (m > 32 || n >= 40ll * ctx->sm_count)))
+                !(pgk_gemm_i8_tcgen05_supports(m, k, n) && m > 16 && (m > 32 || n >= 40ll * ctx->sm_count || k >= 8192)))
                 return pgk_gemm_i8_stream(ctx, d_a, d_as, m, k, w->d_data_i8_t, w->d_scales, n, d_y, d_acc);
             if (aligned && pgk_gemm_i8_tcgen05_supports(m, k, n))
                 return pgk_gemm_i8_tcgen05(ctx, d_a, d_as, m, k, const_cast<pg_qtensor *>(w), d_y, d_acc);

@@ -192,7 +192,8 @@ template <int BN, int AR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                            const float *__restrict__ a_scales, const float *__restrict__ w_scales, int M, int N, int K,
-                           float *__restrict__ y, int32_t *__restrict__ acc_out, int32_t *status)
+                           float *__restrict__ y, int32_t *__restrict__ acc_out, int32_t *status, int splits, int32_t *__restrict__ ws,
+                           unsigned int *__restrict__ tickets)
 {
     using C = Cfg<BN, AR>;
     constexpr int STAGES = C::STAGES;
@@ -216,8 +217,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM;
     const int tiles_n = (N + BN - 1) / BN;
-    const int total_tiles = tiles_m * tiles_n;
     const int kblocks = (K + BK - 1) / BK;
+    // Split K (splits > 1, one row of tiles): a unit is (tile, part of the k-blocks); every part writes its s32 sums to a
+    // slab of its own in the workspace (plain 128-bit stores), and whichever part of a tile arrives last (a ticket per tile
+    // and accumulator-lane quarter) adds the slabs up, applies the scales and writes y.  Nobody waits for anybody, and
+    // integer sums are exact in any order.  (Adding the parts with red.global.add.s32 into one zeroed matrix was the first
+    // form: 15 to 60 us slower, four-byte reductions run at about 35 G/s.)
+    const int total_tiles = tiles_m * tiles_n * splits;   // units
+    const int kpb = (kblocks + splits - 1) / splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -246,18 +253,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // the weight tiles of the first stages of this CTA's first tile, before the predecessor has finished
             int early = 0;
             if ((int)blockIdx.x < total_tiles) {
-                const int n0 = ((int)blockIdx.x / tiles_m) * BN;
-                early = kblocks < STAGES ? kblocks : STAGES;
-                for (int kb = 0; kb < early; kb++) {
-                    mbar_arrive_expect_tx(bar_full + 8 * kb, C::STAGE);
-                    tma_load_2d(base + kb * C::STAGE + C::STAGE_A, &tmap_b, bar_full + 8 * kb, kb * BK, n0);
+                const int u = (int)blockIdx.x, tile = u / splits, kb0 = (u - tile * splits) * kpb;
+                const int n0 = (tile / tiles_m) * BN;
+                const int mine = min(kblocks, kb0 + kpb) - kb0;
+                early = mine < STAGES ? mine : STAGES;
+                for (int i = 0; i < early; i++) {
+                    mbar_arrive_expect_tx(bar_full + 8 * i, C::STAGE);
+                    tma_load_2d(base + i * C::STAGE + C::STAGE_A, &tmap_b, bar_full + 8 * i, (kb0 + i) * BK, n0);
                 }
             }
             asm volatile("griddepcontrol.wait;" ::: "memory");
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            for (int u = blockIdx.x; ok && u < total_tiles; u += gridDim.x) {
+                const int t = u / splits, kb0 = (u - t * splits) * kpb, kb1 = min(kblocks, kb0 + kpb);
                 const int m0 = (t % tiles_m) * BM;
                 const int n0 = (t / tiles_m) * BN;
-                for (int kb = 0; kb < kblocks; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status))) break;
                     const uint32_t sa = base + stage * C::STAGE;
                     if (early > 0) {
@@ -287,11 +297,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             uint32_t stage = 0, phase = 0;
             uint32_t acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            for (int u = blockIdx.x; ok && u < total_tiles; u += gridDim.x) {
+                const int kb0 = (u % splits) * kpb, kb1 = min(kblocks, kb0 + kpb);
                 if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, status))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < kblocks; kb++) {
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, status))) break;
                     tc_fence_after();
                     const uint32_t sa = base + stage * C::STAGE;
@@ -301,7 +312,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     for (int j = 0; j < BK / UMMA_K; j++) {
                         // +32 bytes of K inside the swizzle span = +2 in the 16-byte address field
                         umma_i8(d_tmem, da + (uint64_t)(j * (UMMA_K >> 4)), db + (uint64_t)(j * (UMMA_K >> 4)), idesc,
-                                (kb | j) != 0 ? 1u : 0u);
+                                (kb != kb0 || j != 0) ? 1u : 0u);
                     }
                     umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
                     if (++stage == STAGES) {
@@ -325,7 +336,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const bool vec_ok = ((N & 3) == 0) && (((uintptr_t)y & 15) == 0) && (((uintptr_t)acc_out & 15) == 0) &&
                             (((uintptr_t)w_scales & 15) == 0);
         bool ok = true;
-        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        for (int u = blockIdx.x; ok && u < total_tiles; u += gridDim.x) {
+            const int t = u / splits;
             const int m0 = (t % tiles_m) * BM;
             const int n0 = (t / tiles_m) * BN;
             ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status);
@@ -343,7 +355,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 tmem_ld32(taddr + c, v);
                 if (row_base >= M || n0 + c >= N) continue;   // uniform over the warp
                 const int64_t off0 = (int64_t)row_base * N + n0 + c;
-                if (vec_ok) {
+                if (splits > 1) {
+                    // (the host takes this path only when the vector conditions hold)
+                    pg_store_block_32x32(reinterpret_cast<uint32_t *>(ws + (int64_t)(u - t * splits) * M * N + off0), N, M - row_base,
+                                         N - (n0 + c), stage_buf, lane, v);
+                } else if (vec_ok) {
                     // coalesced: the warp exchanges the block through shared memory and writes whole row segments
                     if (acc_out) pg_store_block_32x32(reinterpret_cast<uint32_t *>(acc_out + off0), N, M - row_base, N - (n0 + c), stage_buf, lane, v);
                     if (y) {
@@ -376,6 +392,75 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1;
+            }
+            if (splits > 1 && row_base < M) {
+                // this warp's rows of the tile: last part in -> finish them
+                __syncwarp();
+                unsigned int old = 0;
+                if (lane == 0) {
+                    __threadfence();                        // the warp's slab stores (ordered before this lane by the warp barrier) first
+                    old = atomicAdd(tickets + t * 4 + q, 1u);
+                }
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == (unsigned int)(splits - 1)) {
+                    __threadfence();
+                    // lane: four columns (c4) of rows r4, r4 + 4, ... of each 32 x 32 block; the slabs are read sixteen 128-bit
+                    // loads at a time (two parts x eight rows) before anything is added or stored: one load after the
+                    // other, a tile's 128 loads per lane cost 20 us
+                    const int c4 = (lane & 7) * 4, r4 = lane >> 3;
+                    float ar[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int r = row_base + i * 4 + r4;
+                        ar[i] = (r < M && y) ? a_scales[r] : 0.0f;
+                    }
+                    const int64_t slab = (int64_t)M * N;
+                    for (int c = 0; c < BN && n0 + c < N; c += 32) {
+                        const int col = n0 + c + c4;
+                        if (col >= N) continue;
+                        const float4 wsc = __ldg(reinterpret_cast<const float4 *>(w_scales + col));
+                        int4 sum[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) sum[i] = make_int4(0, 0, 0, 0);
+                        for (int p = 0; p < splits; p += 2) {
+                            int4 part[16];
+#pragma unroll
+                            for (int h = 0; h < 2; h++)
+#pragma unroll
+                                for (int i = 0; i < 8; i++) {
+                                    const int r = row_base + i * 4 + r4;
+                                    part[h * 8 + i] = (r < M && p + h < splits)
+                                                          ? __ldcg(reinterpret_cast<const int4 *>(ws + (int64_t)(p + h) * slab + (int64_t)r * N + col))
+                                                          : make_int4(0, 0, 0, 0);
+                                }
+#pragma unroll
+                            for (int h = 0; h < 2; h++)
+#pragma unroll
+                                for (int i = 0; i < 8; i++) {
+                                    sum[i].x += part[h * 8 + i].x;
+                                    sum[i].y += part[h * 8 + i].y;
+                                    sum[i].z += part[h * 8 + i].z;
+                                    sum[i].w += part[h * 8 + i].w;
+                                }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const int r = row_base + i * 4 + r4;
+                            if (r >= M) continue;
+                            if (acc_out) *reinterpret_cast<int4 *>(acc_out + (int64_t)r * N + col) = sum[i];
+                            if (y) {
+                                float4 o;
+                                o.x = __fmul_rn(__fmul_rn(__int2float_rn(sum[i].x), ar[i]), wsc.x);
+                                o.y = __fmul_rn(__fmul_rn(__int2float_rn(sum[i].y), ar[i]), wsc.y);
+                                o.z = __fmul_rn(__fmul_rn(__int2float_rn(sum[i].z), ar[i]), wsc.z);
+                                o.w = __fmul_rn(__fmul_rn(__int2float_rn(sum[i].w), ar[i]), wsc.w);
+                                *reinterpret_cast<float4 *>(y + (int64_t)r * N + col) = o;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) tickets[t * 4 + q] = 0;
+                }
             }
         }
     }
@@ -425,8 +510,12 @@ int32_t encode_kmajor(CUtensorMap *map, const void *ptr, int64_t rows, int64_t k
     return PG_OK;
 }
 
+// tickets (one per tile and accumulator-lane quarter, zero between calls) | s32 sums [parts][M, N]
+constexpr size_t SPLIT_TICKET_BYTES = 64 * 1024;
+constexpr size_t SPLIT_MAX_BYTES = 64u << 20;
+
 template <int BN, int AR>
-int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, pg_qtensor *w, float *d_y, int32_t *d_acc)
+int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, pg_qtensor *w, float *d_y, int32_t *d_acc, int splits)
 {
     using C = Cfg<BN, AR>;
     const int N = (int)w->cols;
@@ -441,8 +530,14 @@ int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, 
     auto kern = gemm_i8_tcgen05_kernel<BN, AR>;
     static std::atomic<uint64_t> smem_set{0};
     PG_CUDA(pg_max_smem_once(kern, (int)C::SMEM, ctx->device, smem_set));
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    int32_t *ws = nullptr;
+    unsigned int *tickets = nullptr;
+    if (splits > 1) {
+        tickets = reinterpret_cast<unsigned int *>(ctx->splitk);
+        ws = reinterpret_cast<int32_t *>(reinterpret_cast<unsigned char *>(ctx->splitk) + SPLIT_TICKET_BYTES);
+    }
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -454,18 +549,20 @@ int32_t launch(pg_ctx *ctx, const int8_t *d_a, const float *d_as, int M, int K, 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     PG_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, *reinterpret_cast<CUtensorMap *>(w->tmap_b), d_as, (const float *)w->d_scales, M, N, K,
-                               d_y, d_acc, ctx->d_status));
+                               d_y, d_acc, ctx->d_status, splits, ws, tickets));
     PG_LAUNCHED();
     return PG_OK;
 }
 
 int g_force_bn = 0;
 int g_pair_mode = 0;  // 0 = heuristic, 1 = never use CTA pairs, 2 = always
+int g_split_mode = 0; // 0 = heuristic, 1 = never split K, 2/4/8 = that many parts
 
 }  // namespace
 
 extern "C" PG_API void pg_tune_tcgen05_bn(int bn) { g_force_bn = bn; }
 extern "C" PG_API void pg_tune_tcgen05_pair(int mode) { g_pair_mode = mode; }
+extern "C" PG_API void pg_tune_tcgen05_split(int mode) { g_split_mode = mode; }
 
 bool pgk_gemm_i8_tcgen05_supports(int64_t m, int64_t k, int64_t n)
 {
@@ -498,19 +595,47 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
     // N 6144: 64-column tiles), and the smallest A tile that holds M rows (a deeper ring: 102 -> 92 us at N 128256,
     // 22.7 -> 18.6 us at M 17, N 14336; no change at M 64, N 14336).
     const int ar = m <= 32 ? 32 : (m <= 64 ? 64 : BM);
+    int splits = 1;
     if (tiles_m == 1) {
+        // also over parts of K when the tiles alone leave SMs idle and K is long.  Model (nanoseconds, fitted to
+        // measurements at M 64): a unit costs its k-blocks x the larger of 250 (copy issue, barrier round trip, commit)
+        // and the fill time above; the whole cannot beat the weights at 5.3 TB/s; the parts of a tile meeting in L2 cost
+        // 3000 + 1750 per part (the last part reads the others' sums back: K 14336, N 4096, 128-column tiles: 34.4 us
+        // whole, 25.7 us in two parts, 24.1 us in four, of which 13.9 us are the main loop; K 4096, N 4096: 12.9 us
+        // whole, 14.6 / 16.8 us in two / four parts, so short K stays whole).
+        const int64_t kblocks = (k + BK - 1) / BK;
+        const bool can_split = g_split_mode != 1 && (n % 4 == 0) && (((uintptr_t)d_y | (uintptr_t)d_acc | (uintptr_t)w->d_scales) & 15) == 0 &&
+                               ((n + 31) / 32) * 4 * sizeof(unsigned int) <= SPLIT_TICKET_BYTES && n <= 32768;
         double best = 0.0;
         for (int cand = 32; cand <= 256; cand *= 2) {
-            const int64_t waves = ((n + cand - 1) / cand + ctx->sm_count - 1) / ctx->sm_count;
-            const double cost = (double)waves * 1.8 * (128 + cand);
-            if (best == 0.0 || cost < best) {
-                best = cost;
-                bn = cand;
+            for (int sp = 1; sp <= (can_split ? 8 : 1); sp *= 2) {
+                const int64_t kpb = (kblocks + sp - 1) / sp;
+                if (sp > 1 && (sp - 1) * kpb >= kblocks) continue;      // a part without k-blocks
+                if (sp > 1 && (size_t)sp * (size_t)m * (size_t)n * sizeof(int32_t) > SPLIT_MAX_BYTES) continue;
+                const int64_t units = ((n + cand - 1) / cand) * sp;
+                const int64_t waves = (units + ctx->sm_count - 1) / ctx->sm_count;
+                const double per_kb = std::max(250.0, 1.8 * (ar + cand));
+                const double cost = std::max((double)waves * (double)kpb * per_kb, (double)k * (double)n / 5300.0) + (sp > 1 ? 3000.0 + 1750.0 * sp : 0.0);
+                if (best == 0.0 || cost < best) {
+                    best = cost;
+                    bn = cand;
+                    splits = sp;
+                }
             }
+        }
+        if (g_split_mode >= 2 && can_split) splits = g_split_mode;
+        while (splits > 1 && (splits - 1) * ((kblocks + splits - 1) / splits) >= kblocks) splits /= 2;   // no part without k-blocks
+        while (splits > 1 && (size_t)splits * (size_t)m * (size_t)n * sizeof(int32_t) > SPLIT_MAX_BYTES) splits /= 2;
+        if (splits > 1) {
+            const size_t need = SPLIT_TICKET_BYTES + (size_t)splits * (size_t)m * (size_t)n * sizeof(int32_t);
+            if (need > ctx->splitk_bytes && ctx->no_growth)
+                splits = 1;     // a caller that may not allocate (pg_matmul_quantized_static): whole K per tile
+            else if (pg_splitk_reserve(ctx, need) != PG_OK)
+                return PG_ERR_NOMEM;
         }
     }
     if (g_force_bn) bn = g_force_bn;
-#define PG_TC_LAUNCH(BN_, AR_) return launch<BN_, AR_>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc)
+#define PG_TC_LAUNCH(BN_, AR_) return launch<BN_, AR_>(ctx, d_a, d_as, (int)m, (int)k, w, d_y, d_acc, splits)
 #define PG_TC_ROWS(BN_)                \
     do {                               \
         if (ar == 32) PG_TC_LAUNCH(BN_, 32); \

@@ -144,6 +144,7 @@ struct pg_ctx {
     // A recorded graph keeps the scratch / staging / split-K addresses it was recorded with.  While graphs of this
     // context are alive, a block that has to grow is not freed but parked here, and freed when the last graph goes
     // (or with the context), so that replaying an older graph never touches freed memory.
+    bool no_growth = false;         // set around a call that may not allocate: kernels choose forms that need no new workspace
     int live_graphs = 0;
     std::vector<void *> retired;
 };

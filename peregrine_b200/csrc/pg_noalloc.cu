@@ -75,5 +75,8 @@ extern "C" PG_API int32_t pg_matmul_quantized_static(pg_ctx *ctx, const float *d
     float *a_scales = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(base) + STATIC_Q_BYTES);
     const int32_t rq = pg_quantize_activations(ctx, d_x, m, k, a_i8, a_scales);
     if (rq != PG_OK) return rq;
-    return pg_gemm_i8(ctx, a_i8, a_scales, m, k, w, d_y, nullptr, PG_ALGO_AUTO);
+    ctx->no_growth = true;          // the split-K form of the tensor-core kernel would reserve a workspace
+    const int32_t rg = pg_gemm_i8(ctx, a_i8, a_scales, m, k, w, d_y, nullptr, PG_ALGO_AUTO);
+    ctx->no_growth = false;
+    return rg;
 }

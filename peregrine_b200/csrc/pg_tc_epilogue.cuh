@@ -38,3 +38,4 @@ __device__ __forceinline__ void pg_store_block_32x32(uint32_t *dst, int64_t ld, 
     }
     __syncwarp();
 }
+

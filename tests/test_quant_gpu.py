@@ -298,6 +298,42 @@ def test_mid_batch_dispatch(pg, gpu, oracle_mt, m, k, n):
     _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["naive"])
 
 
+@pytest.mark.parametrize("split", [0, 2, 4, 8])
+@pytest.mark.parametrize("m,k,n,bn", [(17, 14336, 4096, 0), (64, 4096, 4096, 0), (128, 4096, 520, 64), (33, 1040, 1000, 32), (100, 2048, 14336, 256),
+                                      (20, 384, 96, 0)])
+def test_tcgen05_k_split_over_ctas(pg, gpu, oracle_mt, m, k, n, bn, split):
+    """One row of tiles with K divided over CTAs: the parts add their s32 sums into the zeroed workspace, the last part
+    in applies the scales.  Every number of parts (0 = the library's own choice), ragged N and K, more parts than k-blocks
+    (384 bytes of K are three k-blocks), twice in a row and once more from a recorded graph: the workspace must be back
+    at zero after every call."""
+    x, w = linear_inputs(m, k, n, 4000 + m + n)
+    gpu.lib.pg_tune_tcgen05_split(split)
+    gpu.lib.pg_tune_tcgen05_bn(bn)
+    try:
+        _check_product(pg, gpu, oracle_mt, x, w, m, k, n, ["tcgen05", "tcgen05"])
+        ref = oracle_mt.quantize_weights(w, k, n)
+        out_o = oracle_mt.matmul_quantized(x, m, k, ref)
+        qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, k, n)
+        qt.to_gpu(gpu)
+        d_x = gpu.upload(x.reshape(-1))
+        d_y = gpu.alloc(m * n, np.float32)
+        call = lambda: pg._lib.check(gpu.lib.pg_matmul_quantized_ex(gpu.handle, d_x.ptr, m, k, qt._gpu, d_y.ptr, None, None, None, pg._lib.ALGO_TCGEN05))
+        call()
+        with gpu.record() as graph:
+            call()
+            call()
+        for _ in range(3):
+            graph.launch()
+        gpu.sync()
+        assert bits_equal(d_y.read().reshape(m, n), out_o)
+        graph.free()
+        qt.free_gpu()
+        assert gpu.device_status() == 0
+    finally:
+        gpu.lib.pg_tune_tcgen05_split(0)
+        gpu.lib.pg_tune_tcgen05_bn(0)
+
+
 @pytest.mark.parametrize("m,k,n", [(256, 128, 256), (512, 1024, 768), (300, 1040, 520), (1000, 4096, 1000), (129, 144, 257)])
 def test_tcgen05_cta_pairs(pg, gpu, oracle_mt, m, k, n):
     """cta_group::2: two CTAs share one 256 x 256 tile; full and ragged tiles in M, N and K."""
