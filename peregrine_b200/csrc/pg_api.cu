@@ -145,7 +145,11 @@ int32_t pg_ctx_device_status(pg_ctx *ctx, int32_t *status_out)
     int32_t v = 0;
     PG_CUDA(cudaMemcpyAsync(&v, ctx->d_status, sizeof(v), cudaMemcpyDeviceToHost, ctx->stream));
     PG_CUDA(cudaStreamSynchronize(ctx->stream));
-    if (v != 0) PG_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(v), ctx->stream));
+    if (v != 0) {
+        PG_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(v), ctx->stream));
+        // a kernel that gave up may have left tickets of the split-K workspace taken: back to zero for the next call
+        if (ctx->splitk) PG_CUDA(cudaMemsetAsync(ctx->splitk, 0, std::min(ctx->splitk_bytes, (size_t)64 * 1024), ctx->stream));
+    }
     if (status_out) *status_out = v;
     return PG_OK;
 }

@@ -628,10 +628,12 @@ int32_t pgk_gemm_i8_tcgen05(pg_ctx *ctx, const int8_t *d_a, const float *d_as, i
         while (splits > 1 && (size_t)splits * (size_t)m * (size_t)n * sizeof(int32_t) > SPLIT_MAX_BYTES) splits /= 2;
         if (splits > 1) {
             const size_t need = SPLIT_TICKET_BYTES + (size_t)splits * (size_t)m * (size_t)n * sizeof(int32_t);
-            if (need > ctx->splitk_bytes && ctx->no_growth)
-                splits = 1;     // a caller that may not allocate (pg_matmul_quantized_static): whole K per tile
-            else if (pg_splitk_reserve(ctx, need) != PG_OK)
-                return PG_ERR_NOMEM;
+            if (need > ctx->splitk_bytes && (ctx->no_growth || ctx->capturing)) {
+                splits = 1;     // a caller that may not allocate (pg_matmul_quantized_static), or a graph being recorded: whole K per tile
+            } else {
+                const int32_t rr = pg_splitk_reserve(ctx, need);
+                if (rr != PG_OK) return rr;
+            }
         }
     }
     if (g_force_bn) bn = g_force_bn;
