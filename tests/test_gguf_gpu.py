@@ -122,7 +122,9 @@ def _check_matmul(pg, gpu, orc, kind, n, k, m, seed):
 
 
 @pytest.mark.parametrize("kind", KINDS)
-@pytest.mark.parametrize("m,n,k", [(1, 64, 32), (1, 37, 96), (3, 130, 1024), (8, 257, 4096), (5, 1000, 160), (16, 48, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 32), (1, 37, 96), (3, 130, 1024), (8, 257, 4096), (5, 1000, 160), (16, 48, 2048),
+                                   # the streaming kernel's row groups: two rows, eight + one, eight + two, seven; K beyond one chunk of planes
+                                   (2, 300, 512), (9, 100, 1024), (10, 2400, 768), (7, 33, 2048), (2, 64, 16640), (1, 50, 16640), (4, 40, 8448)])
 def test_matmul_gguf_small(pg, gpu, oracle_mt, kind, m, n, k):
     _check_matmul(pg, gpu, oracle_mt, kind, n, k, m, 3000 + m + n)
 
