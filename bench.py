@@ -288,8 +288,8 @@ def run_ours(args):
             # the nine products of the sweep are independent, so the consumers (bounded waits for the other ranks' cells,
             # results written out as plain [M, N] matrices) come after the last product: the step ends when every rank
             # holds all nine full results
-            for ci, (mi, si) in enumerate(CASES):
-                exs[ci].gather(MS[mi], SHAPES[si][1])
+            # -- collected by ONE launch
+            PeerExchange.gather_many(exs, [MS[mi] for mi, si in CASES], [SHAPES[si][1] for mi, si in CASES])
 
     def step_eager():
         if peer:
@@ -477,7 +477,7 @@ def run_ours(args):
             "config": dict(WORKLOAD),
             "config_detail": {
                 "parallelism": (f"{world} replicas, one sweep each, no collective" if replicas else
-                                f"column-sharded x{world}" + ((", slices stored into every rank by the product's epilogue over NVLink, bounded flag waits"
+                                f"column-sharded x{world}" + ((", slices stored into every rank by the product's epilogue over NVLink as flagged cells; the nine gathered results collected by one launch at the end of the step (bounded waits)"
                                                                if peer else ", NCCL all-gather of output slices") if world > 1 else "")),
                 "l2": "inputs larger than L2: each case reads its own copy of the weights (3 copies per shape, 402 MB per step)",
                 "submission": "one CUDA graph per step" if graph is not None else "eager launches + NCCL",

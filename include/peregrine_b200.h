@@ -291,6 +291,10 @@ PG_API int32_t pg_gemm_i8_exchange(pg_ctx *ctx, const int8_t *d_a_i8, const floa
  * [rows, cols] matrix as plain floats to d_out (NULL: to pg_exchange_result); the quantiser of src/quant.rs:97-109 over
  * the gathered matrix; pg_add_rmsnorm_quantize with the gathered matrix as the residual delta. */
 PG_API int32_t pg_exchange_gather(pg_ctx *ctx, pg_exchange *ex, int64_t rows, int64_t cols, float *d_out);
+/* the same for up to 16 exchanges in one launch (independent products whose results nothing consumes one by one);
+ * rows[i] * cols[i] must be a multiple of four; d_outs or d_outs[i] NULL: that exchange's own result buffer */
+PG_API int32_t pg_exchange_gather_many(pg_ctx *ctx, pg_exchange *const *exs, const int64_t *rows, const int64_t *cols,
+                                       float *const *d_outs, int32_t count);
 /* the producer of such an exchange for a slice that lies in plain device memory (any kernel's output) */
 PG_API int32_t pg_exchange_store_cells(pg_ctx *ctx, pg_exchange *ex, const float *d_slice, int64_t m, int64_t n_local,
                                        int64_t n_total, int64_t col0);

@@ -78,6 +78,30 @@ __global__ void __launch_bounds__(256) peer_cells_gather_kernel(float *out, int6
         out[i] = pg_cell_load(wt, want, i);
 }
 
+// The same for several exchanges in one launch (results that nothing consumes one by one: the independent products of a
+// batch of requests).  The concatenation of the matrices is walked in units of four values; each matrix has a multiple
+// of four of them.
+constexpr int PG_GATHER_MAX = 16;
+struct PgGatherMany {
+    PgPeerWait wt[PG_GATHER_MAX];
+    float *out[PG_GATHER_MAX];
+    int64_t end4[PG_GATHER_MAX];    // running sum of the matrices' sizes, in units of four values
+    int count;
+};
+__global__ void __launch_bounds__(256) peer_cells_gather_many_kernel(const __grid_constant__ PgGatherMany p)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t all = p.end4[p.count - 1];
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < all; i += (int64_t)gridDim.x * 256) {
+        int e = 0;
+        while (i >= p.end4[e]) e++;
+        const int64_t at = (i - (e ? p.end4[e - 1] : 0)) * 4;
+        const uint32_t want = pg_cell_want(p.wt[e]);
+        *reinterpret_cast<float4 *>(p.out[e] + at) = pg_cell_load4(p.wt[e], want, at);
+    }
+}
+
 // one warp: lane r waits until rank r has delivered this rank's next exchange
 __global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t *ctl, int world, int32_t *status, unsigned long long limit_ns)
 {
@@ -363,6 +387,49 @@ PG_API int32_t pg_exchange_gather(pg_ctx *ctx, pg_exchange *ex, int64_t rows, in
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     PG_CUDA(cudaLaunchKernelEx(&cfg, peer_cells_gather_kernel, out, total, pg_peer_wait_of(ctx, ex)));
+    PG_LAUNCHED();
+    return PG_OK;
+}
+
+// pg_exchange_gather for up to 16 exchanges in one launch: exchange i's [rows[i], cols[i]] matrix goes to d_outs[i] (or, where
+// d_outs or d_outs[i] is NULL, to that exchange's own result buffer).  rows[i] * cols[i] must be a multiple of four.
+PG_API int32_t pg_exchange_gather_many(pg_ctx *ctx, pg_exchange *const *exs, const int64_t *rows, const int64_t *cols, float *const *d_outs,
+                                       int32_t count)
+{
+    PG_ENTER(ctx);
+    PG_REQUIRE(count >= 0 && count <= PG_GATHER_MAX, "exchange_gather_many: between 0 and %d exchanges per call", PG_GATHER_MAX);
+    PG_REQUIRE(count == 0 || (exs && rows && cols), "exchange_gather_many: null argument");
+    PgGatherMany p = {};
+    int64_t sum4 = 0;
+    for (int i = 0; i < count; i++) {
+        pg_exchange *ex = exs[i];
+        PG_REQUIRE(ex && ex->connected, "exchange_gather_many: exchange %d is null or unconnected", i);
+        PG_REQUIRE(rows[i] >= 0 && cols[i] >= 0 && (size_t)rows[i] * (size_t)cols[i] * sizeof(float) <= ex->y_bytes,
+                   "exchange_gather_many: result %d does not fit its exchange buffer", i);
+        const int64_t total = rows[i] * cols[i];
+        PG_REQUIRE(total % 4 == 0, "exchange_gather_many: matrix %d has %lld values, not a multiple of four", i, (long long)total);
+        float *out = (d_outs && d_outs[i]) ? d_outs[i] : ex->y_local;
+        PG_REQUIRE(((uintptr_t)out & 15) == 0, "exchange_gather_many: output %d must be 16-byte aligned", i);
+        if (total == 0) continue;
+        p.wt[p.count] = pg_peer_wait_of(ctx, ex);
+        p.out[p.count] = out;
+        sum4 += total / 4;
+        p.end4[p.count] = sum4;
+        p.count++;
+    }
+    if (p.count == 0) return PG_OK;
+    int64_t blocks = (sum4 + 255) / 256;
+    blocks = blocks > 4 * (int64_t)ctx->sm_count ? 4 * (int64_t)ctx->sm_count : blocks;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PG_CUDA(cudaLaunchKernelEx(&cfg, peer_cells_gather_many_kernel, p));
     PG_LAUNCHED();
     return PG_OK;
 }

@@ -114,3 +114,47 @@ def test_recorded_graph_survives_growth_of_the_scratch_memory(oracle):
     del filler
     qt.free_gpu()
     gpu.close()
+
+
+def test_several_exchanges_gathered_by_one_launch(gpu, oracle):
+    """pg_exchange_gather_many over three exchanges of different shapes (two ranks in this process): one launch writes all
+    three gathered matrices, twice in a row with new data (the second round must not be served the first round's cells),
+    into the exchanges' own buffers and into caller buffers; wrong arguments are refused."""
+    from peregrine_b200 import _lib
+    from peregrine_b200.sharded import Exchange
+
+    g = np.random.Generator(np.random.PCG64(9))
+    shapes = [(1, 4096), (4, 520), (16, 64)]
+    ranks = [[Exchange(gpu, r, 2, m * n * 4) for (m, n) in shapes] for r in range(2)]
+    for i in range(len(shapes)):
+        Exchange.connect_local([ranks[0][i], ranks[1][i]])
+    outs = [gpu.alloc(m * n, np.float32) for (m, n) in shapes]
+    for rnd in range(2):
+        want = []
+        for i, (m, n) in enumerate(shapes):
+            full = g.standard_normal((m, n), dtype=np.float32)
+            want.append(full)
+            cut = (n // 2) & ~3
+            for r, (c0, c1) in enumerate(((0, cut), (cut, n))):
+                part = gpu.upload(np.ascontiguousarray(full[:, c0:c1]).reshape(-1))
+                ranks[r][i].store_cells(part, m, c1 - c0, n, c0)
+        for r in range(2):
+            Exchange.gather_many(ranks[r], [m for m, _ in shapes], [n for _, n in shapes], outs if (r == 0 and rnd == 1) else None)
+        gpu.sync()
+        assert gpu.device_status() == 0
+        for i, (m, n) in enumerate(shapes):
+            for r in range(2):
+                if r == 0 and rnd == 1:
+                    got = outs[i].read().reshape(m, n)
+                else:
+                    got = ranks[r][i].read(m * n).reshape(m, n)
+                assert np.array_equal(got.view(np.uint32), want[i].view(np.uint32)), (rnd, i, r)
+    # a matrix whose size is not a multiple of four, and more exchanges than one launch takes
+    odd = [Exchange(gpu, r, 2, 3 * 5 * 4) for r in range(2)]
+    Exchange.connect_local(odd)
+    with pytest.raises(_lib.InvalidArgument, match="multiple of four"):
+        Exchange.gather_many([odd[0]], [3], [5])
+    with pytest.raises(_lib.InvalidArgument, match="between 0 and 16"):
+        Exchange.gather_many([odd[0]] * 17, [1] * 17, [4] * 17)
+    for e in odd + ranks[0] + ranks[1]:
+        e.destroy()

@@ -74,7 +74,10 @@ def _worker(rank, world, port, out_dir):
                 _lib.check(gpu.lib.pg_gemm_i8_exchange(gpu.handle, d_q.ptr, d_s.ptr, m, k, shard._gpu, ex.handle, n, b, None))
                 # consumers with the wait inside: quantise the gathered rows; write them out as plain floats
                 _lib.check(gpu.lib.pg_quantize_activations_exchange(gpu.handle, ex.handle, m, n, d_q.ptr, d_s.ptr))
-                ex.gather(m, n)
+                if it == 5:
+                    sharded.Exchange.gather_many([ex], [m], [n])      # the batched form of the same consumer
+                else:
+                    ex.gather(m, n)
             y = ex.read(m)
             assert gpu.device_status() == 0
             assert np.array_equal(y.view(np.uint32), want.view(np.uint32)), f"exchange {it}"
