@@ -67,6 +67,7 @@ def make_inputs(case_idx, m, k):
     return x
 
 
+RESULT_OUT = sys.stdout
 WORKLOAD = {"workload": "decode_gemv_sweep M{1,4,16} x (K,N){(4096,4096),(4096,14336),(14336,4096)}", "cases": 9}
 
 
@@ -194,7 +195,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_OUT, flush=True)
 
 
 # -------------------------------------------------------------------- our arm ----
@@ -214,8 +215,6 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        # NCCL writes its version banner and debug lines to stdout by default; stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     stream = torch.cuda.Stream(device=dev)
     gpu = pg.GpuContext(local, stream.cuda_stream)
@@ -540,7 +539,7 @@ def run_ours(args):
                 ex.destroy()
         dist.destroy_process_group()
     if line is not None:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=RESULT_OUT, flush=True)
 
 
 def extra_measurements(gpu, torch, stream, dev, hbm_peak, peaks):
@@ -844,6 +843,12 @@ def main():
                     help="N > 1, sharded: slices stored into every rank by the products' own epilogues, recorded in the step graph "
                          "(default), or eager NCCL all-gathers")
     args = ap.parse_args()
+    # stdout carries the one JSON line and nothing else: libraries that print there (NCCL's version banner) are sent to
+    # stderr by pointing file descriptor 1 at it; the line itself goes to a duplicate of the original stdout
+    global RESULT_OUT
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference(args)
     else:
