@@ -141,6 +141,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if "LOCAL_RANK" in os.environ and os.environ.get("OMP_NUM_THREADS") == "1":
+        # torch.distributed.run gives every rank one OpenMP thread unless told otherwise; the other ranks of this arm do no
+        # work, so rank 0 takes the host's cores (the setting is read when the OpenMP library loads, below)
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     from oracle.pgoracle import Oracle
 
     orc = Oracle(mt=True)
