@@ -41,6 +41,9 @@ PG_API void pg_tune_gguf_simple(int on);
  * writes y itself / a copy kernel pushes y (0 = path off, negative = default) */
 PG_API void pg_tune_host_direct(int x_bytes, int y_bytes);
 PG_API void pg_tune_host_push(int y_bytes);
+/* pg_matmul_quantized_host: replay a repeated call (same page-locked buffers, shape, weights) from a graph of its own
+ * launches; 1 (default) / 0 */
+PG_API void pg_tune_host_graph(int on);
 /* diagnostic: one rank of a sharded step without its peers (stores stay local, no cell is waited for; results are
  * meaningless, the time is one rank's kernels and launches alone) */
 PG_API void pg_tune_exchange_solo(int on);

@@ -135,6 +135,7 @@ TUNE_SIGNATURES = {
     "pg_tune_gguf_simple": (None, [_int]),
     "pg_tune_host_direct": (None, [_int, _int]),
     "pg_tune_host_push": (None, [_int]),
+    "pg_tune_host_graph": (None, [_int]),
     "pg_tune_exchange_solo": (None, [_int]),
     "pg_huffman_last_sweeps": (_int, []),
 }

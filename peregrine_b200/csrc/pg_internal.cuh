@@ -144,6 +144,18 @@ struct pg_ctx {
     // A recorded graph keeps the scratch / staging / split-K addresses it was recorded with.  While graphs of this
     // context are alive, a block that has to grow is not freed but parked here, and freed when the last graph goes
     // (or with the context), so that replaying an older graph never touches freed memory.
+    // pg_matmul_quantized_host with page-locked buffers: the launches of a call that comes back with the same buffers,
+    // shape and weights are recorded once and replayed as one graph (a third less submission work per blocking call)
+    struct HostCall {
+        const void *x = nullptr, *y = nullptr, *w = nullptr, *wt = nullptr, *ws = nullptr, *staging = nullptr, *scratch = nullptr, *splitk = nullptr;
+        int64_t m = 0, k = 0, n = 0;
+        unsigned long long limit = 0;
+        int mode = 0;
+        cudaGraphExec_t exec = nullptr;   // null: seen once, not yet recorded
+        uint64_t stamp = 0, kernels = 0;
+    };
+    std::vector<HostCall> host_calls;
+    uint64_t host_stamp = 0;
     bool no_growth = false;         // set around a call that may not allocate: kernels choose forms that need no new workspace
     int live_graphs = 0;
     std::vector<void *> retired;

@@ -517,6 +517,60 @@ def test_page_locked_host_buffers_give_the_same_bits(pg, gpu, oracle_mt, m, k, n
         qt.free_gpu()
 
 
+def test_repeated_host_calls_replayed_from_a_graph(pg, gpu, oracle_mt):
+    """A blocking host call that comes back with the same page-locked buffers, shape and weights is recorded the second
+    time and replayed afterwards: every call must still compute with what the buffers hold at that moment, count its
+    kernels, survive other calls in between, and stop using a recording when its weights are freed (a new tensor may
+    get the same address)."""
+    import torch
+
+    from peregrine_b200 import _lib
+
+    lib = gpu.lib
+    g = rng(31)
+    shapes = [(1, 4096, 512), (16, 1024, 320), (4, 14336, 64)]
+    refs, qts, xs, ys = [], [], [], []
+    for m, k, n in shapes:
+        x, w = linear_inputs(m, k, n, 800 + n)
+        ref = oracle_mt.quantize_weights(w, k, n)
+        qt = pg.quant.QuantizedTensor(ref.data_i8, ref.data_i8_t, ref.scales, k, n)
+        qt.to_gpu(gpu)
+        refs.append(ref)
+        qts.append(qt)
+        xs.append(torch.empty(m * k).pin_memory())
+        ys.append(torch.empty(m * n).pin_memory())
+    try:
+        for on in (1, 0, 1):
+            lib.pg_tune_host_graph(on)
+            for rnd in range(5):
+                for i, (m, k, n) in enumerate(shapes):
+                    x = g.standard_normal((m, k), dtype=np.float32)
+                    xs[i].copy_(torch.from_numpy(x.reshape(-1)))
+                    ys[i].fill_(float("nan"))
+                    before = lib.pg_launch_count()
+                    _lib.check(lib.pg_matmul_quantized_host(gpu.handle, xs[i].data_ptr(), m, k, qts[i]._gpu, ys[i].data_ptr()))
+                    assert lib.pg_launch_count() - before == 3, "quantiser, product, copy kernel"
+                    want = oracle_mt.matmul_quantized(x, m, k, refs[i])
+                    assert bits_equal(ys[i].numpy().reshape(m, n), want), (on, rnd, i)
+        # the weights of shape 0 go away; new weights of the same size (possibly at the same addresses) with other values
+        m, k, n = shapes[0]
+        qts[0].free_gpu()
+        x, w = linear_inputs(m, k, n, 999)
+        refs[0] = oracle_mt.quantize_weights(w, k, n)
+        qts[0] = pg.quant.QuantizedTensor(refs[0].data_i8, refs[0].data_i8_t, refs[0].scales, k, n)
+        qts[0].to_gpu(gpu)
+        for rnd in range(3):
+            x = g.standard_normal((m, k), dtype=np.float32)
+            xs[0].copy_(torch.from_numpy(x.reshape(-1)))
+            _lib.check(lib.pg_matmul_quantized_host(gpu.handle, xs[0].data_ptr(), m, k, qts[0]._gpu, ys[0].data_ptr()))
+            assert bits_equal(ys[0].numpy().reshape(m, n), oracle_mt.matmul_quantized(x, m, k, refs[0])), rnd
+        assert gpu.device_status() == 0
+    finally:
+        lib.pg_tune_host_graph(1)
+        for qt in qts:
+            qt.free_gpu()
+
+
 def test_random_shapes_every_kernel_agrees(pg, gpu):
     """150 seeded random (M, K, N) around every switch point of the automatic kernel choice: the chosen kernel, the
     one-thread-per-output checker and the blocking host call give the same accumulators and the same f32 bits."""
