@@ -184,13 +184,14 @@ def huffman_case(a) -> None:
 def host_case(a) -> None:
     """pg_matmul_quantized_host (host x in, host y out, blocking) over the nine decode cases of the benchmark, with
     page-locked buffers and each way of moving x and y: copy engines only, x read by the quantiser, y pushed by a copy
-    kernel, y written by the product itself.  Microseconds per call, host clock."""
+    kernel (launch by launch, and replayed from the recorded graph of a repeated call), y written by the product itself.  Microseconds per call, host clock."""
     import torch
 
     gpu = GpuContext(0)
     lib = gpu.lib
     g = np.random.Generator(np.random.PCG64(1))
-    modes = [("copies", (0, 0, 0)), ("x direct", (1 << 20, 0, 0)), ("x direct + y pushed (default)", (-1, -1, -1)),
+    modes = [("copies", (0, 0, 0)), ("x direct", (1 << 20, 0, 0)), ("x direct + y pushed", (-1, -1, -1)),
+             ("x direct + y pushed, replayed from a graph (default)", (-1, -1, -1)),
              ("x direct + y written by the product", (1 << 20, 1 << 20, 0))]
     total = {name: 0.0 for name, _ in modes}
     for k, n in ((4096, 4096), (4096, 14336), (14336, 4096)):
@@ -208,6 +209,7 @@ def host_case(a) -> None:
             for name, (bx, by, bp) in modes:
                 lib.pg_tune_host_direct(bx, by)
                 lib.pg_tune_host_push(bp)
+                lib.pg_tune_host_graph(1 if "replayed" in name else 0)
                 for _ in range(300):
                     lib.pg_matmul_quantized_host(gpu.handle, x.data_ptr(), m, k, h, y.data_ptr())
                 t0 = time.perf_counter()
@@ -220,6 +222,7 @@ def host_case(a) -> None:
         lib.pg_qtensor_free(gpu.handle, h)
     lib.pg_tune_host_direct(-1, -1)
     lib.pg_tune_host_push(-1)
+    lib.pg_tune_host_graph(1)
     print("sum over the nine cases, us: " + " | ".join(f"{k} {v:.1f}" for k, v in total.items()))
 
 
