@@ -172,8 +172,8 @@ PG_API int32_t pg_matmul_quantized_ex(pg_ctx *ctx, const float *d_x, int64_t m, 
                                       int8_t *d_a_i8, float *d_a_scales, int32_t algo);
 /* Host slices in, host result out: the exact shape of quant::matmul_quantized. Blocks.
  * Any host memory is accepted.  With page-locked, 16-byte aligned buffers of up to 1 MiB the kernels reach x and y
- * themselves (no copy engine), and a call that comes back with the same buffers, shape and weights is replayed as one
- * graph of its launches from the third time on; the result is the same bits on every route. */
+ * themselves (no copy engine), and a call that comes back with the same buffers, shape and weights is recorded the
+ * second time it is seen and replayed as one graph of its launches from then on; the same bits on every route. */
 PG_API int32_t pg_matmul_quantized_host(pg_ctx *ctx, const float *x, int64_t m, int64_t k,
                                         const pg_qtensor *w, float *y);
 
