@@ -282,9 +282,8 @@ def run_ours(args):
             if peer:
                 # the product's own epilogue stores this rank's columns into every rank's [M, N] buffer over NVLink and
                 # publishes the exchange: no all-gather launch
-                _lib.check(lib.pg_quantize_activations(gpu.handle, xs[ci].data_ptr(), MS[mi], k, qs[ci].data_ptr(), qss[ci].data_ptr()))
-                _lib.check(lib.pg_gemm_i8_exchange(gpu.handle, qs[ci].data_ptr(), qss[ci].data_ptr(), MS[mi], k, h, exs[ci].handle, n,
-                                                   shard[si][0], ys[ci].data_ptr()))
+                _lib.check(lib.pg_matmul_quantized_exchange(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, exs[ci].handle, n, shard[si][0],
+                                                            ys[ci].data_ptr()))
             else:
                 _lib.check(lib.pg_matmul_quantized(gpu.handle, xs[ci].data_ptr(), MS[mi], k, h, ys[ci].data_ptr()))
         if peer:

@@ -288,6 +288,11 @@ PG_API int32_t pg_exchange_connect_local(pg_ctx *ctx, pg_exchange *ex, pg_exchan
  * y_bytes / 4 values (pg_exchange_create). */
 PG_API int32_t pg_gemm_i8_exchange(pg_ctx *ctx, const int8_t *d_a_i8, const float *d_a_scales, int64_t m, int64_t k,
                                    const pg_qtensor *w, pg_exchange *ex, int64_t n_total, int64_t col0, float *d_slice_tmp);
+/* pg_matmul_quantized (f32 activations in) with the all-gather inside: quant::matmul_quantized (src/quant.rs:129-169) for a
+ * weight sharded by output column: the activation quantiser (into the context's scratch), then pg_gemm_i8_exchange; the
+ * gathered matrix is bit-identical to the unsharded call. */
+PG_API int32_t pg_matmul_quantized_exchange(pg_ctx *ctx, const float *d_x, int64_t m, int64_t k, const pg_qtensor *w, pg_exchange *ex,
+                                            int64_t n_total, int64_t col0, float *d_slice_tmp);
 /* The slices travel as flagged cells (8 bytes per value: the value and the number of the exchange), which lets a
  * consumer poll the very cells it reads: no fence, no flag, no launch per exchange.  Consumers (enqueue them behind this
  * rank's own producer on the same exchange; their waits are bounded): pg_exchange_gather, which writes the gathered

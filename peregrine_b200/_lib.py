@@ -101,6 +101,7 @@ SIGNATURES = {
     "pg_exchange_connect_local": (_i32, [_vp, _vp, C.POINTER(_vp)]),
     "pg_exchange_gather": (_i32, [_vp, _vp, _i64, _i64, _vp]),
     "pg_exchange_gather_many": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32]),
+    "pg_matmul_quantized_exchange": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
     "pg_exchange_store_cells": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64]),
     "pg_gemm_i8_exchange": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _i64, _vp]),
     "pg_quantize_activations_exchange": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),

@@ -158,3 +158,45 @@ def test_several_exchanges_gathered_by_one_launch(gpu, oracle):
         Exchange.gather_many([odd[0]] * 17, [1] * 17, [4] * 17)
     for e in odd + ranks[0] + ranks[1]:
         e.destroy()
+
+
+def test_sharded_product_from_f32_activations(gpu, oracle):
+    """pg_matmul_quantized_exchange over two ranks in this process: f32 activations in, gathered product out, bit for bit
+    the oracle's matmul_quantized (one to sixteen rows, K split over a cluster of CTAs, a zero row, an infinite activation)."""
+    import peregrine_b200 as pg
+    from peregrine_b200 import _lib
+    from peregrine_b200.sharded import Exchange
+
+    lib = gpu.lib
+    if True:
+        for m, k, n in ((1, 4096, 256), (2, 1024, 96), (3, 14336, 128), (4, 4096, 520), (4, 65536 - 64, 64), (1, 64, 8), (5, 4096, 128), (16, 2048, 64)):
+            x, w = linear_inputs(m, k, n, 60 + m + n)
+            if m == 3:
+                x[1] = 0.0                                   # a zero row: scale 1
+                x[2, 7] = np.float32(np.inf)
+            ref = oracle.quantize_weights(w, k, n)
+            want = oracle.matmul_quantized(x, m, k, ref)
+            exs = [Exchange(gpu, r, 2, m * n * 4) for r in range(2)]
+            Exchange.connect_local(exs)
+            cut = (n // 2) & ~7
+            d_x = gpu.upload(x.reshape(-1))
+            shards = []
+            for r, (c0, c1) in enumerate(((0, cut), (cut, n))):
+                sh = pg.quant.QuantizedTensor(None, np.ascontiguousarray(ref.data_i8_t[c0:c1]), np.ascontiguousarray(ref.scales[c0:c1]), k, c1 - c0)
+                sh.to_gpu(gpu)
+                shards.append(sh)
+                tmp = gpu.alloc(m * (c1 - c0), np.float32)
+                _lib.check(lib.pg_matmul_quantized_exchange(gpu.handle, d_x.ptr, m, k, sh._gpu, exs[r].handle, n, c0, tmp.ptr))
+            for r in range(2):
+                exs[r].gather(m, n)
+            gpu.sync()
+            assert gpu.device_status() == 0
+            for r in range(2):
+                got = exs[r].read(m * n).reshape(m, n)
+                # (a row with an infinite activation is NaN throughout: which NaN a multiplication returns is the processor's choice)
+                nan = np.isnan(want)
+                assert np.array_equal(np.isnan(got), nan) and np.array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32)), (m, k, n, r)
+            for sh in shards:
+                sh.free_gpu()
+            for e in exs:
+                e.destroy()

@@ -70,8 +70,12 @@ def _worker(rank, world, port, out_dir):
                 ex.allgather(d_slice, m, e - b, b)
             else:
                 # the product's own epilogue stores flagged cells into every rank
-                _lib.check(gpu.lib.pg_quantize_activations(gpu.handle, d_x.ptr, m, k, d_q.ptr, d_s.ptr))
-                _lib.check(gpu.lib.pg_gemm_i8_exchange(gpu.handle, d_q.ptr, d_s.ptr, m, k, shard._gpu, ex.handle, n, b, None))
+                if it == 4:
+                    # f32 activations in: quantiser and product with the exchange in one call
+                    _lib.check(gpu.lib.pg_matmul_quantized_exchange(gpu.handle, d_x.ptr, m, k, shard._gpu, ex.handle, n, b, d_slice.ptr))
+                else:
+                    _lib.check(gpu.lib.pg_quantize_activations(gpu.handle, d_x.ptr, m, k, d_q.ptr, d_s.ptr))
+                    _lib.check(gpu.lib.pg_gemm_i8_exchange(gpu.handle, d_q.ptr, d_s.ptr, m, k, shard._gpu, ex.handle, n, b, None))
                 # consumers with the wait inside: quantise the gathered rows; write them out as plain floats
                 _lib.check(gpu.lib.pg_quantize_activations_exchange(gpu.handle, ex.handle, m, n, d_q.ptr, d_s.ptr))
                 if it == 5:
